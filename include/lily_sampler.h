@@ -1,0 +1,278 @@
+/*
+ * lily_sampler.h -- C ABI of the B200 token sampler.
+ *
+ * A drop-in for the sampling step of lily's decode loop: every entry point
+ * below names the item of the reference project it replaces (paths relative
+ * to that project). Host code in any language binds these symbols; nothing
+ * in the signatures is a C++ or torch type.
+ *
+ * Conventions (they mirror the reference's, src/kernels/sample.rs:251-266,
+ * docs/architecture.md:133-138, src/metal.rs:681-696):
+ *   - Every call that takes a `stream` (a cudaStream_t, passed as void*) only
+ *     ENQUEUES work on it and returns; results are valid once the stream has
+ *     reached that point. Nothing synchronises unless it says so.
+ *   - The caller owns every buffer it passes and keeps it alive until the
+ *     stream has consumed it. The library owns what `lily_sampler_create`
+ *     allocates.
+ *   - Return value: 0 = LILY_OK; negative = the arguments were refused on the
+ *     host before anything was enqueued; positive = CUDA / device error. The
+ *     text of the last error of a handle: lily_sampler_last_error().
+ *   - A handle is not thread-safe: one handle per engine thread.
+ *   - Determinism: same logits, history / counts, params and uniforms give
+ *     the same token, whatever the batch around the row and however the row
+ *     is split over thread blocks.
+ *   - There is no CPU fallback: without a CUDA device every call that needs
+ *     one fails with LILY_ERR_CUDA.
+ */
+#ifndef LILY_SAMPLER_H
+#define LILY_SAMPLER_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LILY_ABI_VERSION 1u
+
+/* src/kernels/sample.rs:17 SAMPLE_K_CAP: largest candidate set. */
+#define LILY_K_CAP 1024u
+
+enum lily_status {
+    LILY_OK = 0,
+    LILY_ERR_ARG = -1,        /* null / out-of-range argument */
+    LILY_ERR_PARAMS = -2,     /* SamplingParams::validate refused a row */
+    LILY_ERR_CAPACITY = -3,   /* rows / vocab / list length beyond the handle's */
+    LILY_ERR_FAULT = -4,      /* an injected or latched fault (see inject_fault) */
+    LILY_ERR_VOCAB = -5,      /* handles of different vocabularies */
+    LILY_ERR_CUDA = 1,        /* a CUDA runtime call failed */
+    LILY_ERR_DEVICE_ROW = 2   /* a row reported an error word (see row status) */
+};
+
+/* Per-row status words written to `out_status` (0 = drawn normally). */
+enum lily_row_status {
+    LILY_ROW_OK = 0,
+    LILY_ROW_NAN = 1,        /* a NaN among the adjusted logits */
+    LILY_ROW_NONFINITE = 2,  /* largest adjusted logit not finite (all banned) */
+    LILY_ROW_PARAMS = 3,     /* device-resident params failed validation */
+    LILY_ROW_FORCED = 16     /* informational: the row returned its forced id */
+};
+
+enum lily_dtype { LILY_F32 = 0, LILY_BF16 = 1 };
+
+/*
+ * src/kernels/sample.rs:19-31 SamplingParams, as a 40-byte POD (top_k as
+ * u32, 0 = off; negative API values map to 0 as src/serve/api.rs:802-806).
+ * `seed` is used only when a call is given draw indices instead of uniforms.
+ */
+typedef struct lily_sampling_params {
+    float temperature;
+    uint32_t top_k;
+    float top_p;
+    float min_p;
+    float presence_penalty;
+    float frequency_penalty;
+    float repetition_penalty;
+    uint32_t reserved;
+    uint64_t seed;
+} lily_sampling_params_t;
+
+typedef struct lily_sampler lily_sampler_t;
+
+/* ------------------------------------------------------------ host-only -- */
+
+uint32_t lily_abi_version(void);
+
+/* src/kernels/sample.rs:57-79 SamplingParams::validate. */
+int32_t lily_params_validate(const lily_sampling_params_t *p);
+/* src/kernels/sample.rs:47-49 is_greedy; :51-55 uses_penalties. */
+int32_t lily_params_is_greedy(const lily_sampling_params_t *p);
+int32_t lily_params_uses_penalties(const lily_sampling_params_t *p);
+/* src/kernels/sample.rs:83-94 effective(): what the kernel consumes. */
+void lily_params_effective(const lily_sampling_params_t *p, float *temperature,
+                           uint32_t *top_k);
+/* src/kernels/sample.rs:227-234 draft_params: the request's sampler without
+ * the penalties. */
+void lily_draft_params(const lily_sampling_params_t *p, lily_sampling_params_t *out);
+/* src/kernels/sample.rs:435-441 uniform_for (bit-exact). */
+float lily_uniform_for(uint64_t seed, uint32_t step);
+/* src/kernels/sample.rs:220-222 draft_step: step | 0x4000_0000. */
+uint32_t lily_draft_step(uint32_t step);
+/* src/kernels/metal/sample.metal:649 residual-draw domain: step | 0x8000_0000. */
+uint32_t lily_residual_step(uint32_t step);
+
+/* ---------------------------------------------------------------- handle -- */
+
+/* lily_sampler_create flags */
+#define LILY_FLAG_COUNTS_TABLE 1u /* keep a persistent u32[max_rows, vocab]
+                                     emission histogram (the reference's
+                                     SamplerScratch::counts), one slot per row */
+
+/*
+ * src/kernels/sample.rs:130-143 SamplerScratch::new, for `max_rows` rows at
+ * once. Allocates on `device`: the per-row candidate scratch, the parameter
+ * staging ring, the status words and (with LILY_FLAG_COUNTS_TABLE) the
+ * histogram slots. `max_history` bounds history_len; `max_list` bounds the
+ * bias and ban list lengths.
+ */
+int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
+                            uint32_t max_history, uint32_t max_list, uint32_t flags,
+                            lily_sampler_t **out);
+void lily_sampler_destroy(lily_sampler_t *h);
+/* src/kernels/sample.rs:176-178 SamplerScratch::vocab. */
+uint32_t lily_sampler_vocab(const lily_sampler_t *h);
+const char *lily_sampler_last_error(const lily_sampler_t *h);
+
+/*
+ * src/metal.rs:681-696 fault latch and MetalContext::inject_fault
+ * (src/main.rs:296-301 --debug-inject-metal-fault). Host-side only: after
+ * inject_fault(code != 0) every enqueueing call returns LILY_ERR_FAULT until
+ * clear_fault. `lily_sampler_status` synchronises `stream`, then returns the
+ * latched fault, else the OR-reduced error words of the rows drawn since the
+ * last call to it (LILY_ERR_DEVICE_ROW if any row failed).
+ */
+void lily_sampler_inject_fault(lily_sampler_t *h, int32_t code);
+void lily_sampler_clear_fault(lily_sampler_t *h);
+int32_t lily_sampler_status(lily_sampler_t *h, void *stream);
+
+/*
+ * src/kernels/sample.rs:145-174 reset_counts / uncount / copy_counts_from on
+ * histogram slot `slot` (needs LILY_FLAG_COUNTS_TABLE). Stream-ordered.
+ * copy_counts refuses handles of different vocabularies (LILY_ERR_VOCAB).
+ */
+int32_t lily_sampler_reset_counts(lily_sampler_t *h, void *stream, uint32_t slot);
+int32_t lily_sampler_uncount(lily_sampler_t *h, void *stream, uint32_t slot, uint32_t token);
+int32_t lily_sampler_copy_counts(lily_sampler_t *dst, uint32_t dst_slot,
+                                 const lily_sampler_t *src, uint32_t src_slot, void *stream);
+/* Test / checkpoint access to a slot's histogram (device-to-host or
+ * host-to-device copy of vocab words, stream-ordered then synchronised). */
+int32_t lily_sampler_read_counts(lily_sampler_t *h, void *stream, uint32_t slot, uint32_t *host_out);
+int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream, uint32_t slot, const uint32_t *host_in);
+
+/* ------------------------------------------------------------------ draw -- */
+
+/*
+ * One batch of independent draws: src/kernels/sample.rs:373-387 sample_f32
+ * for each row (its greedy route, the exact lowest-index argmax of
+ * src/kernels/elementwise.rs:297-308, included), and with the `kept_*`
+ * outputs set also :394-408 sample_draft_f32.
+ *
+ * Order of operations on a row's logits, all in fp32 (bf16 widens exactly):
+ *   l = logit + sum of the row's bias entries for that id (list order)
+ *   if penalties are on and count(id) > 0:
+ *       l = l > 0 ? l / repetition : l * repetition
+ *       l -= presence + frequency * count(id)
+ *   banned ids: l = -inf
+ *   l /= temperature                    (IEEE division)
+ * then the top-k by (value descending, id ascending), p = exp(l - l_top),
+ * sequential prefix sums in rank order, the top-p / min-p cut relative to
+ * the top-k mass, and the inverse-CDF draw on uniform * kept mass.
+ *
+ * count(id) is the multiplicity of id in the row's history list, or, with
+ * `count_slots`, the slot's persistent histogram (which the draw then
+ * increments, src/kernels/metal/sample.metal:509-511).
+ *
+ * Device pointers unless marked HOST. Optional pointers may be NULL.
+ */
+typedef struct lily_sample_args {
+    uint32_t struct_size;        /* sizeof(lily_sample_args_t) */
+    uint32_t rows;               /* B, 1..max_rows */
+    const void *logits;          /* [rows, logits_ld] of logits_dtype */
+    uint32_t logits_dtype;       /* enum lily_dtype */
+    uint32_t params_on_device;   /* 0: `params`/`steps` are HOST arrays */
+    uint64_t logits_ld;          /* elements between rows (>= vocab) */
+    const lily_sampling_params_t *params; /* [rows] */
+    const float *uniforms;       /* [rows] in [0,1), or NULL: use steps */
+    const uint32_t *steps;       /* [rows] draw indices for uniform_for(seed, step);
+                                    same side as params; used when uniforms == NULL */
+    const uint32_t *history_ids; /* [rows, history_ld] or NULL */
+    const uint32_t *history_len; /* [rows] */
+    uint64_t history_ld;
+    const uint32_t *bias_ids;    /* [rows, list_ld] or NULL */
+    const float *bias_vals;      /* [rows, list_ld] */
+    const uint32_t *bias_len;    /* [rows] */
+    const uint32_t *ban_ids;     /* [rows, list_ld] or NULL */
+    const uint32_t *ban_len;     /* [rows] */
+    uint64_t list_ld;            /* row pitch of the bias and ban arrays */
+    const int32_t *forced_ids;   /* [rows], < 0 = none: the row returns this id
+                                    without drawing (thinking-budget forcing) */
+    const uint32_t *count_slots; /* HOST [rows] histogram slots, or NULL */
+    uint32_t *out_ids;           /* [rows] */
+    uint32_t *out_status;        /* [rows] enum lily_row_status, or NULL */
+    uint32_t *kept_n;            /* [rows] size of the kept set, or NULL */
+    uint32_t *kept_ids;          /* [rows, kept_ld] kept ids in rank order */
+    float *kept_probs;           /* [rows, kept_ld] probabilities over the kept mass */
+    uint64_t kept_ld;            /* >= LILY_K_CAP when kept_* are set */
+} lily_sample_args_t;
+
+int32_t lily_sample_batch(lily_sampler_t *h, void *stream, const lily_sample_args_t *args);
+
+/*
+ * src/kernels/elementwise.rs:297-308 argmax_f32 for each row: first maximum,
+ * lowest index on ties, NaN never wins.
+ */
+int32_t lily_argmax_batch(lily_sampler_t *h, void *stream, const void *logits,
+                          uint32_t logits_dtype, uint64_t logits_ld, uint32_t rows,
+                          uint32_t *out_ids);
+
+/* ------------------------------------------------------------ speculation -- */
+
+enum lily_spec_mode {
+    LILY_SPEC_REJECTION = 0,   /* speculative sampling with the residual draw */
+    LILY_SPEC_GREEDY_MATCH = 1 /* every row is the argmax; equality accepts */
+};
+
+/*
+ * One verify step of a speculative decode: src/qwen4exp/model.rs:3013-3040
+ * (rows j < m-1: src/kernels/sample.rs:417-432 sample_spec_f32 against
+ * proposal j; last row: sample_f32), followed by the accepted count of
+ * src/kernels/metal/spec.metal:26-29. Rows share the request's penalty
+ * state: with penalties on, row j sees the draws of rows < j of this step.
+ *
+ * The draft distribution of proposal j is either dense, q_dense[j, id], or
+ * the reference's sparse export (src/kernels/sample.rs:186-215 DraftDists):
+ * q_ids / q_probs [m-1, LILY_K_CAP] with q_n[j] entries.
+ */
+typedef struct lily_spec_args {
+    uint32_t struct_size;
+    uint32_t m;                  /* verified rows: drafts + 1 (<= 8) */
+    const void *target_logits;   /* [m, logits_ld] */
+    uint32_t logits_dtype;
+    uint32_t mode;               /* enum lily_spec_mode */
+    uint64_t logits_ld;
+    const lily_sampling_params_t *params; /* HOST, one request */
+    const uint32_t *draft_ids;   /* [m-1] proposals */
+    const float *q_dense;        /* [m-1, q_ld] or NULL */
+    uint64_t q_ld;
+    const uint32_t *q_ids;       /* [m-1, LILY_K_CAP] or NULL */
+    const float *q_probs;        /* [m-1, LILY_K_CAP] */
+    const uint32_t *q_n;         /* [m-1] */
+    const float *u_accept;       /* [m] accept test / plain draw uniforms, or NULL */
+    const float *u_resid;        /* [m-1] residual draw uniforms, or NULL */
+    uint32_t step0;              /* with NULL uniforms: row j draws uniform_for(seed, step0+j)
+                                    and its residual on step | 0x8000_0000 */
+    uint32_t history_len;        /* HOST value */
+    const uint32_t *history_ids; /* [history_len] or NULL */
+    const uint32_t *count_slot;  /* HOST pointer to one slot index, or NULL */
+    uint32_t *out_ids;           /* [m] */
+    uint32_t *out_accepted;      /* [1] */
+    uint32_t *out_status;        /* [m] or NULL */
+} lily_spec_args_t;
+
+int32_t lily_spec_verify(lily_sampler_t *h, void *stream, const lily_spec_args_t *args);
+
+/*
+ * src/kernels/spec.rs:52-91 spec_accept with its control block
+ * (src/kernels/metal/spec.metal:8-38): ctrl[0] = a, ctrl[stride] = a + 1,
+ * then per chain row i the position pos0 + a + 1 + i, its block
+ * (position / ratio) and whether it completes one. `stride` words between
+ * slots (the reference uses 4). ctrl holds (2 + 3*chain) * stride words.
+ */
+int32_t lily_spec_accept(lily_sampler_t *h, void *stream, const uint32_t *draws,
+                         const uint32_t *ids, uint32_t m, uint32_t *ctrl, uint32_t pos0,
+                         uint32_t ratio, uint32_t chain, uint32_t stride);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LILY_SAMPLER_H */
