@@ -1,0 +1,416 @@
+#!/usr/bin/env python
+"""Benchmark of the sampling hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload: the large-batch configuration, B=256 rows of bf16 logits at
+V=151,936 with 32,768-id histories per row (top-k 50, top-p 0.9, min-p 0.05,
+T 0.8, repetition 1.1). A step is one pass of the sampler over one batch.
+With N GPUs every rank draws its own 256-row batch per step (rows are
+independent: no collective), so `value` is N x 256 rows per step time.
+
+`value`   rows/s with inputs resident in HBM (CUDA events around K steps).
+`e2e`     the same through the C ABI with HOST buffers: pinned host logits,
+          histories and uniforms copied in, token ids copied out, per step.
+`roofline` algorithmic bytes (logits + history read once) / kernel time
+          against the measured HBM copy bandwidth.
+`cpu_baseline` the CPU oracle (a port of the reference's CPU sampler) timed
+          on this host's cores on a bounded sample.
+`--impl reference` times only that CPU port, on all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+
+ROWS = 256
+HISTORY = 32_768
+NB = 4  # distinct resident batches rotated through, 445 MB in all (> the 126 MB L2)
+METRIC = "sampled rows/s at B=256,V=151,936"
+UNIT = "rows/s"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def ncu_traffic():
+    """DRAM bytes per launch of the sampling kernel from the committed ncu
+    summary, if one has been recorded."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("sample_rows_kernel_b256_dram_bytes_per_launch")
+    return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during a timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_rows_per_s(batch, threads: int, min_seconds: float, mode: int = 1):
+    """Times the CPU oracle over the rows of `batch` on `threads` host threads
+    (ctypes releases the GIL), repeating the batch until min_seconds passed."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    import oracle
+
+    lf_bits = batch.logits
+    params = [oracle.params(**p) for p in batch.params]
+
+    def one(r):
+        logits = oracle.widen_bf16(lf_bits[r])
+        d = oracle.sample(logits, params[r], float(batch.uniforms[r]),
+                          history=batch.history[r, :batch.history_len[r]], mode=mode)
+        return d.token
+
+    rows = lf_bits.shape[0]
+    done = 0
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        while True:
+            list(pool.map(one, range(rows)))
+            done += rows
+            if time.perf_counter() - t0 >= min_seconds:
+                break
+    dt = time.perf_counter() - t0
+    return done / dt, done, dt
+
+
+def run_reference(args):
+    """The reference arm: the CPU port of the reference's sampler on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import lily_b200.workloads as w
+    import oracle
+
+    oracle.build()
+    cores = os.cpu_count() or 1
+    batch = w.config4_batch(rows=ROWS, history=HISTORY)
+    # One step = one 256-row batch through the CPU sampler.
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        cpu_rows_per_s(batch, cores, 0.0)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = ROWS * len(times) / total
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic (seeded numpy; shapes and distributions of the large-batch configuration)",
+        "config": {"workload": "large-batch B=256 V=151936 bf16 history=32768", "rows": ROWS,
+                   "vocab": w.VOCAB, "history": HISTORY},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{len(times)} steps of one 256-row batch, partial-selection "
+                                   "variant of the CPU sampler (identical outputs to the full sort)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--b4-steps", type=int, default=300)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import lily_b200 as lily
+    import lily_b200.workloads as w
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sampler has no CPU fallback")
+    lily.lib()  # fails loudly if the CUDA library has not been built
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    vocab = w.VOCAB
+    # Seeded host batches (pinned: the end-to-end leg copies from them).
+    host = []
+    for b in range(NB):
+        batch = w.config4_batch(rows=ROWS, history=HISTORY, seed=4004 + 97 * rank, step=b)
+        lg = torch.from_numpy(batch.logits.view(np.int16)).pin_memory()
+        hi = torch.from_numpy(batch.history.view(np.int32)).pin_memory()
+        un = torch.from_numpy(batch.uniforms).pin_memory()
+        host.append((batch, lg, hi, un))
+    params = [lily.SamplingParams(**p) for p in host[0][0].params]
+    hist_len = torch.full((ROWS,), HISTORY, dtype=torch.int32, device=dev)
+    resident = [(lg.to(dev).view(torch.bfloat16), hi.to(dev), un.to(dev)) for _, lg, hi, un in host]
+    raw = np.frombuffer(b"".join(bytes(p) for p in params), dtype=np.uint8).copy()
+    d_params = torch.from_numpy(raw).to(dev)
+    out = torch.zeros(ROWS, dtype=torch.int32, device=dev)
+    scratch = lily.SamplerScratch(vocab, max_rows=ROWS, max_history=HISTORY, device=local)
+    stream = torch.cuda.current_stream()
+
+    def step_resident(i):
+        lg, hi, un = resident[i % NB]
+        scratch.sample_batch(lg, d_params, out, uniforms=un, history_ids=hi, history_len=hist_len,
+                             params_on_device=True, stream=stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput -------------------------------------
+    for i in range(args.warmup):
+        step_resident(i)
+    barrier()
+    clocks = ClockSampler(local)
+    clocks.start()
+    time.sleep(0.3)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record(stream)
+    for i in range(args.steps):
+        step_resident(i)
+        ev[i + 1].record(stream)
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    # Keep the GPU busy a little longer so that nvidia-smi sees it under load.
+    t_end = time.time() + 1.0
+    i = 0
+    while time.time() < t_end:
+        step_resident(i)
+        i += 1
+    torch.cuda.synchronize()
+    clock_info = clocks.stop()
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * ROWS * args.steps / (total_ms * 1e-3)
+    assert scratch.status(stream) == lily.OK
+
+    # ---- end to end through the C ABI with host buffers ------------------
+    d_lg = torch.empty_like(resident[0][0])
+    d_hi = torch.empty_like(resident[0][1])
+    d_un = torch.empty_like(resident[0][2])
+    h_out = torch.zeros(ROWS, dtype=torch.int32).pin_memory()
+
+    def step_e2e(i):
+        _, lg, hi, un = host[i % NB]
+        d_lg.view(torch.int16).copy_(lg, non_blocking=True)
+        d_hi.copy_(hi, non_blocking=True)
+        d_un.copy_(un, non_blocking=True)
+        scratch.sample_batch(d_lg, params, out, uniforms=d_un, history_ids=d_hi,
+                             history_len=hist_len, stream=stream)
+        h_out.copy_(out, non_blocking=True)
+
+    e2e_steps = max(10, min(args.steps, 50))
+    for i in range(3):
+        step_e2e(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(e2e_steps):
+        step_e2e(i)
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * ROWS * e2e_steps / (e2e_ms * 1e-3)
+    h2d = ROWS * vocab * 2 + ROWS * HISTORY * 4 + ROWS * 4 + ROWS * 40
+    d2h = ROWS * 4
+    check = host[(e2e_steps - 1) % NB][0]
+
+    # ---- p50 latency of the 4-row server batch ----------------------------
+    b4 = None
+    if rank == 0 and args.b4_steps > 0:
+        b4 = b4_latency(torch, lily, w, dev, stream, args.b4_steps)
+
+    # ---- roofline ----------------------------------------------------------
+    alg_bytes = ROWS * (vocab * 2 + HISTORY * 4)
+    kernel_ms = statistics.mean(per_launch_ms)
+    peak, peak_kind = peaks()
+    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": ncu_traffic(), "peak_kind": peak_kind,
+                "kernel": "sample_rows_kernel<bf16, vec>", "kernel_ms": kernel_ms,
+                "kernel_ms_p50": statistics.median(per_launch_ms),
+                "algorithmic_bytes_per_launch": alg_bytes}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+
+        oracle.build()
+        cores = os.cpu_count() or 1
+        v, done, dt = cpu_rows_per_s(host[0][0], cores, args.cpu_seconds)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"{done} rows (the 256-row batch repeated for {dt:.1f} s), "
+                         "partial-selection variant of the CPU sampler"}
+        # The last end-to-end step's tokens, checked against the CPU port.
+        want = [oracle.sample(oracle.widen_bf16(check.logits[r]), oracle.params(**check.params[r]),
+                              float(check.uniforms[r]), history=check.history[r]).token
+                for r in range(0, ROWS, 16)]
+        got = h_out.numpy().view(np.uint32)[::16].tolist()
+        assert got == want, "bench: the end-to-end tokens differ from the CPU port"
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic (seeded numpy; shapes and distributions of the large-batch configuration)",
+            "config": {"workload": "large-batch B=256 V=151936 bf16 history=32768 "
+                                   "(top-k 50, top-p 0.9, min-p 0.05, T 0.8, repetition 1.1)",
+                       "rows_per_gpu": ROWS, "global_rows": ROWS * world, "vocab": vocab,
+                       "history": HISTORY, "parallelism": f"rows x{world}, no collective",
+                       "l2": f"{NB} resident batches rotated ({NB * alg_bytes / 1e6:.0f} MB > 126 MB L2)"},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": args.steps, "clocks": clock_info, "latency_b4": b4,
+            "us_per_step": ms_per_step * 1e3,
+        }
+        print(json.dumps(line), flush=True)
+    scratch.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def b4_latency(torch, lily, w, dev, stream, steps):
+    """p50 / p90 microseconds per step of the 4-row server batch (mixed params,
+    8192-id histories, bias, ban and one forced row), inputs resident."""
+    vocab = w.VOCAB
+    nb = 16
+    batches = []
+    for b in range(nb):
+        x = w.config2_step(b)
+        t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a).view(dt)).to(dev)
+        batches.append(dict(
+            logits=t(x.logits, np.int16).view(torch.bfloat16), params=[lily.SamplingParams(**p) for p in x.params],
+            uniforms=t(x.uniforms, np.float32), history_ids=t(x.history, np.int32),
+            history_len=t(x.history_len, np.int32), bias_ids=t(x.bias_ids, np.int32),
+            bias_vals=t(x.bias_vals, np.float32), bias_len=t(x.bias_len, np.int32),
+            ban_ids=t(x.ban_ids, np.int32), ban_len=t(x.ban_len, np.int32),
+            forced_ids=t(x.forced, np.int32)))
+    s = lily.SamplerScratch(vocab, max_rows=4, max_list=64, device=dev.index)
+    out = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def go(i):
+        kw = dict(batches[i % nb])
+        lg, ps = kw.pop("logits"), kw.pop("params")
+        s.sample_batch(lg, ps, out, stream=stream, **kw)
+
+    for i in range(20):
+        go(i)
+    torch.cuda.synchronize()
+    us = []
+    for i in range(steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        go(i)
+        b.record(stream)
+        b.synchronize()
+        us.append(a.elapsed_time(b) * 1e3)
+    # Back-to-back, no host sync between steps: what a pipelined decode loop sees.
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        go(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    s.close()
+    us.sort()
+    return {"p50_us": us[len(us) // 2], "p90_us": us[int(len(us) * 0.9)], "steps": steps,
+            "back_to_back_us": e0.elapsed_time(e1) * 1e3 / steps,
+            "workload": "server batch B=4 V=151936 bf16, host params, events around each call"}
+
+
+if __name__ == "__main__":
+    main()

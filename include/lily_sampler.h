@@ -272,6 +272,16 @@ int32_t lily_spec_accept(lily_sampler_t *h, void *stream, const uint32_t *draws,
                          const uint32_t *ids, uint32_t m, uint32_t *ctrl, uint32_t pos0,
                          uint32_t ratio, uint32_t chain, uint32_t stride);
 
+/* ------------------------------------------------------------------ test -- */
+
+/*
+ * out[i] = the kernels' exp(in[i]) (device pointers). The reference calls the
+ * platform's f32::exp (tests/unit/kernels/sample.rs:37); this library uses
+ * one fixed sequence of binary32 operations instead so that results do not
+ * depend on the platform. Exposed so that a checker can compare it.
+ */
+int32_t lily_debug_exp(void *stream, const float *in, float *out, uint64_t n);
+
 #ifdef __cplusplus
 }
 #endif

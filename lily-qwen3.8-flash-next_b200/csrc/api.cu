@@ -1,0 +1,842 @@
+// Host side of the C ABI declared in include/lily_sampler.h: argument
+// checks, parameter staging, launch geometry. All device work is enqueued on
+// the caller's stream; nothing here falls back to the CPU.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "../../include/lily_sampler.h"
+#include "sample_kernel.cuh"
+
+namespace {
+
+constexpr int RING = 8;
+
+struct StageLayout {
+    size_t params, steps, slots, hist_len, total;
+};
+
+StageLayout stage_layout(uint32_t max_rows) {
+    StageLayout l;
+    size_t off = 0;
+    l.params = off;
+    off += sizeof(lily_sampling_params_t) * max_rows;
+    l.steps = off;
+    off += sizeof(uint32_t) * max_rows;
+    l.slots = off;
+    off += sizeof(uint32_t) * max_rows;
+    l.hist_len = off;
+    off += sizeof(uint32_t) * max_rows;
+    l.total = (off + 255) & ~size_t(255);
+    return l;
+}
+
+}  // namespace
+
+struct lily_sampler {
+    int device = 0;
+    uint32_t vocab = 0, max_rows = 0, max_history = 0, max_list = 0, flags = 0;
+    std::string last_error;
+    int32_t fault = 0;
+    int sm_count = 0;
+    int max_smem = 0;
+    uint2 *part = nullptr;
+    uint32_t *part_n = nullptr;
+    uint32_t *tickets = nullptr;
+    uint32_t *status_word = nullptr;
+    uint32_t *counts_scratch = nullptr;
+    uint32_t *counts_table = nullptr;
+    uint32_t *seen_table = nullptr;
+    uint32_t seen_words = 0;
+    StageLayout layout{};
+    char *h_stage[RING] = {};
+    char *d_stage[RING] = {};
+    cudaEvent_t ev[RING] = {};
+    int ring_pos = 0;
+    uint32_t *h_status = nullptr;
+    uint32_t attr_mask = 0;  // kernel variants whose shared-memory limit is raised
+};
+
+namespace {
+
+int32_t fail(lily_sampler *h, int32_t code, const char *msg) {
+    if (h) {
+        h->last_error = msg;
+    }
+    return code;
+}
+
+int32_t cuda_fail(lily_sampler *h, cudaError_t e, const char *what) {
+    if (h) {
+        h->last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    }
+    return LILY_ERR_CUDA;
+}
+
+#define CU(h, call)                              \
+    do {                                         \
+        cudaError_t e_ = (call);                 \
+        if (e_ != cudaSuccess) {                 \
+            return cuda_fail((h), e_, #call);    \
+        }                                        \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) {
+            prev = -1;
+        }
+        if (prev != dev) {
+            ok = cudaSetDevice(dev) == cudaSuccess;
+        }
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) {
+            cudaSetDevice(prev);
+        }
+    }
+};
+
+bool params_ok(const lily_sampling_params_t &p) {
+    return std::isfinite(p.temperature) && p.temperature >= 0.0f && std::isfinite(p.top_p) &&
+           p.top_p > 0.0f && p.top_p <= 1.0f && std::isfinite(p.min_p) && p.min_p >= 0.0f &&
+           p.min_p <= 1.0f && std::isfinite(p.repetition_penalty) &&
+           p.repetition_penalty > 0.0f && std::isfinite(p.presence_penalty) &&
+           std::isfinite(p.frequency_penalty);
+}
+
+bool is_greedy(const lily_sampling_params_t &p) {
+    return p.temperature <= 0.0f || p.top_k == 1u;
+}
+
+bool uses_penalties(const lily_sampling_params_t &p) {
+    return p.presence_penalty != 0.0f || p.frequency_penalty != 0.0f ||
+           p.repetition_penalty != 1.0f;
+}
+
+uint32_t effective_k(const lily_sampling_params_t &p) {
+    if (is_greedy(p)) {
+        return 1u;
+    }
+    return p.top_k == 0u ? LILY_K_CAP : (p.top_k < LILY_K_CAP ? p.top_k : LILY_K_CAP);
+}
+
+// A staging slot whose previous use has left the stream.
+int32_t next_stage(lily_sampler *h, int *slot) {
+    const int s = h->ring_pos;
+    h->ring_pos = (h->ring_pos + 1) % RING;
+    CU(h, cudaEventSynchronize(h->ev[s]));
+    *slot = s;
+    return LILY_OK;
+}
+
+size_t smem_bytes(uint32_t vocab, uint32_t n_slices) {
+    // The largest slice a row can get is the one of a row cut into
+    // min(n_slices, CAP / KCAP) pieces.
+    const uint32_t want = n_slices < lily::CAP / lily::KCAP ? n_slices : lily::CAP / lily::KCAP;
+    const uint32_t slice_len = (((vocab + want - 1u) / want) + 255u) & ~255u;
+    const size_t words = (slice_len + 31u) / 32u + 8u;
+    return sizeof(lily::SmemFixed) + words * sizeof(uint32_t);
+}
+
+template <typename T, bool VEC>
+int32_t launch_one(lily_sampler *h, cudaStream_t stream, const lily::KArgs &a, uint32_t rows,
+                   size_t smem) {
+    auto kernel = lily::sample_rows_kernel<T, VEC>;
+    const uint32_t bit = 1u << ((sizeof(T) == 4 ? 0 : 2) + (VEC ? 1 : 0));
+    if (!(h->attr_mask & bit)) {
+        CU(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   h->max_smem));
+        h->attr_mask |= bit;
+    }
+    dim3 grid(a.n_slices, rows, 1);
+    kernel<<<grid, lily::NT, smem, stream>>>(a);
+    CU(h, cudaGetLastError());
+    return LILY_OK;
+}
+
+int32_t launch(lily_sampler *h, cudaStream_t stream, const lily::KArgs &a, uint32_t rows,
+               uint32_t dtype) {
+    const size_t smem = smem_bytes(a.vocab, a.n_slices);
+    if (smem > (size_t)h->max_smem) {
+        return fail(h, LILY_ERR_CAPACITY, "vocabulary too large for the shared-memory bitmap");
+    }
+    const size_t esize = dtype == LILY_F32 ? 4 : 2;
+    const bool vec = (reinterpret_cast<uintptr_t>(a.logits) % 16u == 0u) &&
+                     ((a.logits_ld * esize) % 16u == 0u);
+    if (dtype == LILY_F32) {
+        return vec ? launch_one<float, true>(h, stream, a, rows, smem)
+                   : launch_one<float, false>(h, stream, a, rows, smem);
+    }
+    return vec ? launch_one<__nv_bfloat16, true>(h, stream, a, rows, smem)
+               : launch_one<__nv_bfloat16, false>(h, stream, a, rows, smem);
+}
+
+uint32_t choose_slices(const lily_sampler *h, uint32_t rows) {
+    const uint32_t target = 2u * (uint32_t)h->sm_count;
+    uint32_t s = target / rows;
+    if (s < 1u) {
+        s = 1u;
+    }
+    if (s > lily::MAX_SLICES) {
+        s = lily::MAX_SLICES;
+    }
+    // Slices shorter than one round of 4096 logits buy nothing.
+    const uint32_t by_len = (h->vocab + lily::ROUND - 1u) / lily::ROUND;
+    if (s > by_len) {
+        s = by_len;
+    }
+    return s < 1u ? 1u : s;
+}
+
+void base_args(const lily_sampler *h, lily::KArgs *a) {
+    std::memset(a, 0, sizeof(*a));
+    a->vocab = h->vocab;
+    a->counts_table = h->counts_table;
+    a->seen_table = h->seen_table;
+    a->seen_words = h->seen_words;
+    a->counts_scratch = h->counts_scratch;
+    a->part = h->part;
+    a->part_n = h->part_n;
+    a->tickets = h->tickets;
+    a->status_word = h->status_word;
+}
+
+int32_t ensure_counts_scratch(lily_sampler *h) {
+    if (h->counts_scratch == nullptr) {
+        const size_t bytes = (size_t)h->max_rows * h->vocab * sizeof(uint32_t);
+        CU(h, cudaMalloc(&h->counts_scratch, bytes));
+        CU(h, cudaMemset(h->counts_scratch, 0, bytes));
+    }
+    return LILY_OK;
+}
+
+int32_t check_handle(lily_sampler *h) {
+    if (h == nullptr) {
+        return LILY_ERR_ARG;
+    }
+    if (h->fault != 0) {
+        return fail(h, LILY_ERR_FAULT, "a fault is latched on this sampler");
+    }
+    return LILY_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t lily_abi_version(void) { return LILY_ABI_VERSION; }
+
+int32_t lily_params_validate(const lily_sampling_params_t *p) {
+    if (p == nullptr) {
+        return LILY_ERR_ARG;
+    }
+    return params_ok(*p) ? LILY_OK : LILY_ERR_PARAMS;
+}
+
+int32_t lily_params_is_greedy(const lily_sampling_params_t *p) { return p && is_greedy(*p); }
+
+int32_t lily_params_uses_penalties(const lily_sampling_params_t *p) {
+    return p && uses_penalties(*p);
+}
+
+void lily_params_effective(const lily_sampling_params_t *p, float *temperature, uint32_t *top_k) {
+    if (p == nullptr) {
+        return;
+    }
+    if (temperature) {
+        *temperature = is_greedy(*p) ? 1.0f : p->temperature;
+    }
+    if (top_k) {
+        *top_k = effective_k(*p);
+    }
+}
+
+void lily_draft_params(const lily_sampling_params_t *p, lily_sampling_params_t *out) {
+    if (p == nullptr || out == nullptr) {
+        return;
+    }
+    *out = *p;
+    out->presence_penalty = 0.0f;
+    out->frequency_penalty = 0.0f;
+    out->repetition_penalty = 1.0f;
+}
+
+float lily_uniform_for(uint64_t seed, uint32_t step) { return lily::uniform_for(seed, step); }
+
+uint32_t lily_draft_step(uint32_t step) { return step | 0x40000000u; }
+
+uint32_t lily_residual_step(uint32_t step) { return step | 0x80000000u; }
+
+int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
+                            uint32_t max_history, uint32_t max_list, uint32_t flags,
+                            lily_sampler_t **out) {
+    if (out == nullptr || vocab == 0u || max_rows == 0u || max_list > 1024u ||
+        vocab > (1u << 24)) {
+        return LILY_ERR_ARG;
+    }
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        return LILY_ERR_CUDA;
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return LILY_ERR_CUDA;
+    }
+    lily_sampler *h = new (std::nothrow) lily_sampler();
+    if (h == nullptr) {
+        return LILY_ERR_ARG;
+    }
+    h->device = device;
+    h->vocab = vocab;
+    h->max_rows = max_rows;
+    h->max_history = max_history;
+    h->max_list = max_list;
+    h->flags = flags;
+    h->seen_words = (vocab + 31u) / 32u;
+    h->layout = stage_layout(max_rows);
+    auto bail = [&](cudaError_t e, const char *what) {
+        std::fprintf(stderr, "lily_sampler_create: %s: %s\n", what, cudaGetErrorString(e));
+        lily_sampler_destroy(h);
+        return (int32_t)LILY_ERR_CUDA;
+    };
+    cudaError_t e;
+    if ((e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device)) !=
+        cudaSuccess) {
+        return bail(e, "sm count");
+    }
+    if ((e = cudaDeviceGetAttribute(&h->max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                    device)) != cudaSuccess) {
+        return bail(e, "shared memory limit");
+    }
+    if ((e = cudaMalloc(&h->part, (size_t)max_rows * lily::CAP * sizeof(uint2))) != cudaSuccess) {
+        return bail(e, "candidate scratch");
+    }
+    if ((e = cudaMalloc(&h->part_n, (size_t)max_rows * lily::MAX_SLICES * 4)) != cudaSuccess) {
+        return bail(e, "slice counters");
+    }
+    if ((e = cudaMalloc(&h->tickets, (size_t)max_rows * 4)) != cudaSuccess) {
+        return bail(e, "tickets");
+    }
+    if ((e = cudaMemset(h->tickets, 0, (size_t)max_rows * 4)) != cudaSuccess) {
+        return bail(e, "tickets");
+    }
+    if ((e = cudaMalloc(&h->status_word, 4)) != cudaSuccess ||
+        (e = cudaMemset(h->status_word, 0, 4)) != cudaSuccess) {
+        return bail(e, "status word");
+    }
+    if ((e = cudaMallocHost(&h->h_status, 4)) != cudaSuccess) {
+        return bail(e, "status word (host)");
+    }
+    if (flags & LILY_FLAG_COUNTS_TABLE) {
+        const size_t cb = (size_t)max_rows * vocab * 4, sb = (size_t)max_rows * h->seen_words * 4;
+        if ((e = cudaMalloc(&h->counts_table, cb)) != cudaSuccess ||
+            (e = cudaMemset(h->counts_table, 0, cb)) != cudaSuccess ||
+            (e = cudaMalloc(&h->seen_table, sb)) != cudaSuccess ||
+            (e = cudaMemset(h->seen_table, 0, sb)) != cudaSuccess) {
+            return bail(e, "histogram slots");
+        }
+    }
+    for (int i = 0; i < RING; ++i) {
+        if ((e = cudaMallocHost(&h->h_stage[i], h->layout.total)) != cudaSuccess ||
+            (e = cudaMalloc(&h->d_stage[i], h->layout.total)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&h->ev[i], cudaEventDisableTiming)) != cudaSuccess) {
+            return bail(e, "staging ring");
+        }
+    }
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) {
+        return bail(e, "create");
+    }
+    *out = h;
+    return LILY_OK;
+}
+
+void lily_sampler_destroy(lily_sampler_t *h) {
+    if (h == nullptr) {
+        return;
+    }
+    DeviceGuard guard(h->device);
+    cudaDeviceSynchronize();
+    cudaFree(h->part);
+    cudaFree(h->part_n);
+    cudaFree(h->tickets);
+    cudaFree(h->status_word);
+    cudaFree(h->counts_scratch);
+    cudaFree(h->counts_table);
+    cudaFree(h->seen_table);
+    if (h->h_status) {
+        cudaFreeHost(h->h_status);
+    }
+    for (int i = 0; i < RING; ++i) {
+        if (h->h_stage[i]) {
+            cudaFreeHost(h->h_stage[i]);
+        }
+        cudaFree(h->d_stage[i]);
+        if (h->ev[i]) {
+            cudaEventDestroy(h->ev[i]);
+        }
+    }
+    delete h;
+}
+
+uint32_t lily_sampler_vocab(const lily_sampler_t *h) { return h ? h->vocab : 0u; }
+
+const char *lily_sampler_last_error(const lily_sampler_t *h) {
+    return h ? h->last_error.c_str() : "null sampler";
+}
+
+void lily_sampler_inject_fault(lily_sampler_t *h, int32_t code) {
+    if (h) {
+        h->fault = code;
+    }
+}
+
+void lily_sampler_clear_fault(lily_sampler_t *h) {
+    if (h) {
+        h->fault = 0;
+    }
+}
+
+int32_t lily_sampler_status(lily_sampler_t *h, void *stream_) {
+    if (h == nullptr) {
+        return LILY_ERR_ARG;
+    }
+    if (h->fault != 0) {
+        return fail(h, LILY_ERR_FAULT, "a fault is latched on this sampler");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    CU(h, cudaMemcpyAsync(h->h_status, h->status_word, 4, cudaMemcpyDeviceToHost, stream));
+    CU(h, cudaMemsetAsync(h->status_word, 0, 4, stream));
+    CU(h, cudaStreamSynchronize(stream));
+    if (*h->h_status != 0u) {
+        char buf[96];
+        std::snprintf(buf, sizeof buf, "rows reported error bits 0x%x", *h->h_status);
+        return fail(h, LILY_ERR_DEVICE_ROW, buf);
+    }
+    return LILY_OK;
+}
+
+// ------------------------------------------------------------- histogram --
+
+int32_t lily_sampler_reset_counts(lily_sampler_t *h, void *stream_, uint32_t slot) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (h->counts_table == nullptr || slot >= h->max_rows) {
+        return fail(h, LILY_ERR_ARG, "no such histogram slot");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    CU(h, cudaMemsetAsync(h->counts_table + (size_t)slot * h->vocab, 0, (size_t)h->vocab * 4,
+                          stream));
+    CU(h, cudaMemsetAsync(h->seen_table + (size_t)slot * h->seen_words, 0,
+                          (size_t)h->seen_words * 4, stream));
+    return LILY_OK;
+}
+
+int32_t lily_sampler_uncount(lily_sampler_t *h, void *stream_, uint32_t slot, uint32_t token) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (h->counts_table == nullptr || slot >= h->max_rows) {
+        return fail(h, LILY_ERR_ARG, "no such histogram slot");
+    }
+    if (token >= h->vocab) {
+        return LILY_OK;  // src/kernels/sample.rs:148-151: out of range is ignored
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    lily::uncount_kernel<<<1, 1, 0, stream>>>(h->counts_table + (size_t)slot * h->vocab,
+                                              h->seen_table + (size_t)slot * h->seen_words,
+                                              h->vocab, token);
+    CU(h, cudaGetLastError());
+    return LILY_OK;
+}
+
+int32_t lily_sampler_copy_counts(lily_sampler_t *dst, uint32_t dst_slot, const lily_sampler_t *src,
+                                 uint32_t src_slot, void *stream_) {
+    int32_t st = check_handle(dst);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (src == nullptr || dst->counts_table == nullptr || src->counts_table == nullptr ||
+        dst_slot >= dst->max_rows || src_slot >= src->max_rows) {
+        return fail(dst, LILY_ERR_ARG, "no such histogram slot");
+    }
+    if (src->vocab != dst->vocab) {
+        return fail(dst, LILY_ERR_VOCAB, "sampler scratches for different vocabularies");
+    }
+    DeviceGuard guard(dst->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    CU(dst, cudaMemcpyAsync(dst->counts_table + (size_t)dst_slot * dst->vocab,
+                            src->counts_table + (size_t)src_slot * src->vocab,
+                            (size_t)dst->vocab * 4, cudaMemcpyDefault, stream));
+    CU(dst, cudaMemcpyAsync(dst->seen_table + (size_t)dst_slot * dst->seen_words,
+                            src->seen_table + (size_t)src_slot * src->seen_words,
+                            (size_t)dst->seen_words * 4, cudaMemcpyDefault, stream));
+    return LILY_OK;
+}
+
+int32_t lily_sampler_read_counts(lily_sampler_t *h, void *stream_, uint32_t slot,
+                                 uint32_t *host_out) {
+    if (h == nullptr || host_out == nullptr || h->counts_table == nullptr ||
+        slot >= h->max_rows) {
+        return fail(h, LILY_ERR_ARG, "no such histogram slot");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    CU(h, cudaMemcpyAsync(host_out, h->counts_table + (size_t)slot * h->vocab,
+                          (size_t)h->vocab * 4, cudaMemcpyDeviceToHost, stream));
+    CU(h, cudaStreamSynchronize(stream));
+    return LILY_OK;
+}
+
+int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream_, uint32_t slot,
+                                  const uint32_t *host_in) {
+    if (h == nullptr || host_in == nullptr || h->counts_table == nullptr ||
+        slot >= h->max_rows) {
+        return fail(h, LILY_ERR_ARG, "no such histogram slot");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    uint32_t *counts = h->counts_table + (size_t)slot * h->vocab;
+    CU(h, cudaMemcpyAsync(counts, host_in, (size_t)h->vocab * 4, cudaMemcpyHostToDevice, stream));
+    const uint32_t threads = 256, blocks = (h->seen_words + threads - 1u) / threads;
+    lily::rebuild_seen_kernel<<<blocks, threads, 0, stream>>>(
+        counts, h->seen_table + (size_t)slot * h->seen_words, h->vocab);
+    CU(h, cudaGetLastError());
+    CU(h, cudaStreamSynchronize(stream));
+    return LILY_OK;
+}
+
+// ------------------------------------------------------------------ draw --
+
+int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_args_t *args) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (args == nullptr || args->struct_size != sizeof(lily_sample_args_t)) {
+        return fail(h, LILY_ERR_ARG, "args is null or of another ABI version");
+    }
+    const lily_sample_args_t &g = *args;
+    if (g.rows == 0u || g.rows > h->max_rows) {
+        return fail(h, LILY_ERR_CAPACITY, "rows outside 1..max_rows");
+    }
+    if (g.logits == nullptr || g.out_ids == nullptr || g.params == nullptr ||
+        g.logits_ld < h->vocab || g.logits_dtype > LILY_BF16) {
+        return fail(h, LILY_ERR_ARG, "logits must be F32 or BF16 [rows, ld >= vocab]; out and params set");
+    }
+    if (g.uniforms == nullptr && g.steps == nullptr) {
+        return fail(h, LILY_ERR_ARG, "either uniforms or steps must be given");
+    }
+    if ((g.history_ids != nullptr) != (g.history_len != nullptr) ||
+        (g.bias_ids != nullptr) != (g.bias_len != nullptr) ||
+        (g.bias_ids != nullptr) != (g.bias_vals != nullptr) ||
+        (g.ban_ids != nullptr) != (g.ban_len != nullptr)) {
+        return fail(h, LILY_ERR_ARG, "a list needs both its ids and its lengths");
+    }
+    if (g.kept_n != nullptr &&
+        (g.kept_ids == nullptr || g.kept_probs == nullptr || g.kept_ld < LILY_K_CAP)) {
+        return fail(h, LILY_ERR_ARG, "kept_n needs kept_ids, kept_probs and kept_ld >= 1024");
+    }
+    if (g.count_slots != nullptr && h->counts_table == nullptr) {
+        return fail(h, LILY_ERR_ARG, "count_slots needs LILY_FLAG_COUNTS_TABLE");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    lily::KArgs a;
+    base_args(h, &a);
+    bool need_scratch = false;
+    const lily_sampling_params_t *d_params = g.params;
+    const uint32_t *d_steps = g.steps;
+    const uint32_t *d_slots = nullptr;
+    int slot = -1;
+    if (!g.params_on_device || g.count_slots != nullptr) {
+        st = next_stage(h, &slot);
+        if (st != LILY_OK) {
+            return st;
+        }
+    }
+    if (!g.params_on_device) {
+        for (uint32_t r = 0; r < g.rows; ++r) {
+            if (!params_ok(g.params[r])) {
+                char buf[64];
+                std::snprintf(buf, sizeof buf, "row %u: invalid sampling parameters", r);
+                return fail(h, LILY_ERR_PARAMS, buf);
+            }
+            need_scratch = need_scratch || (uses_penalties(g.params[r]) &&
+                                            g.params[r].frequency_penalty != 0.0f);
+        }
+        char *hs = h->h_stage[slot];
+        std::memcpy(hs + h->layout.params, g.params, sizeof(lily_sampling_params_t) * g.rows);
+        d_params = reinterpret_cast<const lily_sampling_params_t *>(h->d_stage[slot] +
+                                                                    h->layout.params);
+        if (g.steps != nullptr) {
+            std::memcpy(hs + h->layout.steps, g.steps, sizeof(uint32_t) * g.rows);
+            d_steps = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.steps);
+        }
+    } else {
+        need_scratch = true;
+    }
+    if (g.count_slots != nullptr) {
+        for (uint32_t r = 0; r < g.rows; ++r) {
+            if (g.count_slots[r] >= h->max_rows) {
+                return fail(h, LILY_ERR_ARG, "no such histogram slot");
+            }
+        }
+        std::memcpy(h->h_stage[slot] + h->layout.slots, g.count_slots, sizeof(uint32_t) * g.rows);
+        d_slots = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.slots);
+        need_scratch = false;
+    }
+    if (need_scratch && g.history_ids != nullptr) {
+        st = ensure_counts_scratch(h);
+        if (st != LILY_OK) {
+            return st;
+        }
+        a.counts_scratch = h->counts_scratch;
+    }
+    if (slot >= 0) {
+        CU(h, cudaMemcpyAsync(h->d_stage[slot], h->h_stage[slot], h->layout.total,
+                              cudaMemcpyHostToDevice, stream));
+    }
+    a.logits = g.logits;
+    a.logits_ld = g.logits_ld;
+    a.rows = g.rows;
+    a.params = d_params;
+    a.uniforms = g.uniforms;
+    a.steps = d_steps;
+    a.history_ids = g.history_ids;
+    a.history_len = g.history_len;
+    a.history_ld = g.history_ld;
+    a.bias_ids = g.bias_ids;
+    a.bias_vals = g.bias_vals;
+    a.bias_len = g.bias_len;
+    a.ban_ids = g.ban_ids;
+    a.ban_len = g.ban_len;
+    a.list_ld = g.list_ld;
+    a.forced_ids = g.forced_ids;
+    a.count_slots = d_slots;
+    a.out_ids = g.out_ids;
+    a.out_status = g.out_status;
+    a.kept_n = g.kept_n;
+    a.kept_ids = g.kept_ids;
+    a.kept_probs = g.kept_probs;
+    a.kept_ld = g.kept_ld;
+    a.n_slices = choose_slices(h, g.rows);
+    st = launch(h, stream, a, g.rows, g.logits_dtype);
+    if (slot >= 0) {
+        CU(h, cudaEventRecord(h->ev[slot], stream));
+    }
+    return st;
+}
+
+int32_t lily_argmax_batch(lily_sampler_t *h, void *stream_, const void *logits,
+                          uint32_t logits_dtype, uint64_t logits_ld, uint32_t rows,
+                          uint32_t *out_ids) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (rows == 0u || rows > h->max_rows) {
+        return fail(h, LILY_ERR_CAPACITY, "rows outside 1..max_rows");
+    }
+    if (logits == nullptr || out_ids == nullptr || logits_ld < h->vocab ||
+        logits_dtype > LILY_BF16) {
+        return fail(h, LILY_ERR_ARG, "logits must be F32 or BF16 [rows, ld >= vocab]");
+    }
+    DeviceGuard guard(h->device);
+    lily::KArgs a;
+    base_args(h, &a);
+    a.logits = logits;
+    a.logits_ld = logits_ld;
+    a.rows = rows;
+    a.force_greedy = 1;
+    a.out_ids = out_ids;
+    a.n_slices = choose_slices(h, rows);
+    return launch(h, static_cast<cudaStream_t>(stream_), a, rows, logits_dtype);
+}
+
+// ----------------------------------------------------------- speculation --
+
+int32_t lily_spec_verify(lily_sampler_t *h, void *stream_, const lily_spec_args_t *args) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (args == nullptr || args->struct_size != sizeof(lily_spec_args_t)) {
+        return fail(h, LILY_ERR_ARG, "args is null or of another ABI version");
+    }
+    const lily_spec_args_t &g = *args;
+    if (g.m == 0u || g.m > 8u || g.m > h->max_rows) {
+        return fail(h, LILY_ERR_CAPACITY, "m outside 1..min(8, max_rows)");
+    }
+    if (g.target_logits == nullptr || g.params == nullptr || g.out_ids == nullptr ||
+        g.out_accepted == nullptr || g.logits_ld < h->vocab || g.logits_dtype > LILY_BF16 ||
+        g.mode > LILY_SPEC_GREEDY_MATCH) {
+        return fail(h, LILY_ERR_ARG, "target logits, params and outputs must be set");
+    }
+    if (g.m > 1u && g.draft_ids == nullptr) {
+        return fail(h, LILY_ERR_ARG, "draft_ids missing");
+    }
+    if (!params_ok(*g.params)) {
+        return fail(h, LILY_ERR_PARAMS, "invalid sampling parameters");
+    }
+    lily_sampling_params_t p = *g.params;
+    if (g.mode == LILY_SPEC_GREEDY_MATCH) {
+        p.temperature = 0.0f;
+    }
+    const bool pen = uses_penalties(p);
+    const bool argmax_rows = is_greedy(p) && !pen;
+    const bool spec_rows = g.mode == LILY_SPEC_REJECTION && !argmax_rows && g.m > 1u;
+    if (spec_rows) {
+        const bool dense = g.q_dense != nullptr;
+        const bool sparse = g.q_ids != nullptr && g.q_probs != nullptr && g.q_n != nullptr;
+        if (dense == sparse) {
+            return fail(h, LILY_ERR_ARG, "give the draft distribution dense or sparse, not both");
+        }
+        if (dense && g.q_ld < h->vocab) {
+            return fail(h, LILY_ERR_ARG, "q_ld < vocab");
+        }
+    }
+    if (g.history_len > 0u && g.history_ids == nullptr) {
+        return fail(h, LILY_ERR_ARG, "history_len without history_ids");
+    }
+    if (g.count_slot != nullptr && (h->counts_table == nullptr || *g.count_slot >= h->max_rows)) {
+        return fail(h, LILY_ERR_ARG, "no such histogram slot");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int slot = -1;
+    st = next_stage(h, &slot);
+    if (st != LILY_OK) {
+        return st;
+    }
+    char *hs = h->h_stage[slot];
+    auto *sp = reinterpret_cast<lily_sampling_params_t *>(hs + h->layout.params);
+    auto *ss = reinterpret_cast<uint32_t *>(hs + h->layout.steps);
+    auto *sl = reinterpret_cast<uint32_t *>(hs + h->layout.slots);
+    auto *sh = reinterpret_cast<uint32_t *>(hs + h->layout.hist_len);
+    for (uint32_t j = 0; j < g.m; ++j) {
+        sp[j] = p;
+        ss[j] = g.step0 + j;
+        sl[j] = g.count_slot ? *g.count_slot : 0u;
+        sh[j] = g.history_len;
+    }
+    CU(h, cudaMemcpyAsync(h->d_stage[slot], hs, h->layout.total, cudaMemcpyHostToDevice, stream));
+    char *ds = h->d_stage[slot];
+
+    lily::KArgs a;
+    base_args(h, &a);
+    const bool list_counts = pen && p.frequency_penalty != 0.0f && g.count_slot == nullptr;
+    if (list_counts) {
+        st = ensure_counts_scratch(h);
+        if (st != LILY_OK) {
+            return st;
+        }
+        a.counts_scratch = h->counts_scratch;
+    }
+    a.logits = g.target_logits;
+    a.logits_ld = g.logits_ld;
+    a.rows = g.m;
+    a.params = reinterpret_cast<const lily_sampling_params_t *>(ds + h->layout.params);
+    a.uniforms = g.u_accept;
+    a.steps = reinterpret_cast<const uint32_t *>(ds + h->layout.steps);
+    a.history_ids = g.history_ids;
+    a.history_len = g.history_ids ? reinterpret_cast<const uint32_t *>(ds + h->layout.hist_len)
+                                  : nullptr;
+    a.history_ld = 0;  // every row of the step reads the same list
+    a.count_slots = g.count_slot ? reinterpret_cast<const uint32_t *>(ds + h->layout.slots)
+                                 : nullptr;
+    a.out_ids = g.out_ids;
+    a.out_status = g.out_status;
+    if (spec_rows) {
+        a.spec.draft_ids = g.draft_ids;
+        a.spec.q_dense = g.q_dense;
+        a.spec.q_ld = g.q_ld;
+        a.spec.q_ids = g.q_ids;
+        a.spec.q_probs = g.q_probs;
+        a.spec.q_n = g.q_n;
+        a.spec.u_resid = g.u_resid;
+        a.spec.n_spec = g.m - 1u;
+    }
+    if (!pen) {
+        // Without penalties the rows do not depend on one another.
+        a.n_slices = choose_slices(h, g.m);
+        st = launch(h, stream, a, g.m, g.logits_dtype);
+    } else {
+        // Row j's penalties see the draws of rows < j (the reference's rows
+        // share one histogram, src/qwen4exp/model.rs:3008-3012): one launch
+        // per row, in stream order.
+        a.n_slices = choose_slices(h, 1u);
+        for (uint32_t j = 0; j < g.m && st == LILY_OK; ++j) {
+            a.row0 = j;
+            if (g.count_slot == nullptr) {
+                a.extra_ids = g.out_ids;
+                a.extra_len = j;
+            }
+            st = launch(h, stream, a, 1u, g.logits_dtype);
+        }
+    }
+    if (st == LILY_OK) {
+        if (g.m > 1u) {
+            lily::spec_accept_kernel<<<1, 1, 0, stream>>>(g.out_ids, g.draft_ids, 0u, g.m,
+                                                          g.out_accepted, 0u, 1u, 0u, 0u);
+        } else {
+            CU(h, cudaMemsetAsync(g.out_accepted, 0, 4, stream));
+        }
+        CU(h, cudaGetLastError());
+    }
+    CU(h, cudaEventRecord(h->ev[slot], stream));
+    return st;
+}
+
+int32_t lily_spec_accept(lily_sampler_t *h, void *stream_, const uint32_t *draws,
+                         const uint32_t *ids, uint32_t m, uint32_t *ctrl, uint32_t pos0,
+                         uint32_t ratio, uint32_t chain, uint32_t stride) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (draws == nullptr || ids == nullptr || ctrl == nullptr || m == 0u) {
+        return fail(h, LILY_ERR_ARG, "draws and ids must both hold the verified rows");
+    }
+    if (ratio == 0u) {
+        return fail(h, LILY_ERR_ARG, "indexer block ratio must be nonzero");
+    }
+    if (stride == 0u) {
+        return fail(h, LILY_ERR_ARG, "stride must be nonzero");
+    }
+    DeviceGuard guard(h->device);
+    lily::spec_accept_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_)>>>(
+        draws, ids, 1u, m, ctrl, pos0, ratio, chain, stride);
+    CU(h, cudaGetLastError());
+    return LILY_OK;
+}
+
+int32_t lily_debug_exp(void *stream_, const float *in, float *out, uint64_t n) {
+    if (in == nullptr || out == nullptr) {
+        return LILY_ERR_ARG;
+    }
+    if (n == 0u) {
+        return LILY_OK;
+    }
+    const uint32_t threads = 256;
+    const uint64_t blocks = (n + threads - 1u) / threads;
+    lily::exp_kernel<<<(uint32_t)(blocks > 65535u * 16u ? 65535u * 16u : blocks), threads, 0,
+                       static_cast<cudaStream_t>(stream_)>>>(in, out, n);
+    return cudaGetLastError() == cudaSuccess ? LILY_OK : LILY_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,1105 @@
+// The sampling kernel: one launch draws every row of a batch.
+//
+// Grid (n_slices, rows), 512 threads. A thread block owns one slice of one
+// row's vocabulary and makes ONE pass over it:
+//
+//   A. history ids -> a "seen" bitmap in shared memory (and, when the
+//      frequency penalty needs multiplicities, a count table in global
+//      scratch that the block clears again before it exits);
+//   B. the few ids with a logit bias or a ban are adjusted one by one and
+//      put into the candidate buffer up front;
+//   C. the slice streams through registers in rounds of 4096 logits,
+//      16-byte loads, several rounds in flight. A logit is looked at only
+//      if it beats a threshold that is exact in the raw (unscaled) domain:
+//      the largest float c whose scaled value still does not beat the
+//      k-th best candidate so far. Survivors are penalised, scaled and
+//      pushed as (monotone key, id) pairs into a shared-memory buffer; when
+//      the buffer could overflow in the next round, a radix select keeps
+//      the best k and raises the threshold;
+//   D. the block's best k go to global scratch; the last block of the row
+//      to arrive (an atomic ticket, nobody waits) merges the slices,
+//      sorts the k survivors by (value descending, id ascending) and runs
+//      the softmax prefix / top-p / min-p cut / draw exactly in the order
+//      the reference's CPU sampler does (tests/unit/kernels/sample.rs:8-54).
+//
+// With one slice per row (large batches) step D happens in the same block.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lily_sampler.h"
+#include "lily_math.cuh"
+
+namespace lily {
+
+constexpr int NT = 512;                 // threads per block
+constexpr uint32_t CAP = 8192;          // candidate buffer entries
+constexpr uint32_t GROUP = 8;           // logits per thread per round
+constexpr uint32_t ROUND = NT * GROUP;  // logits per block per round
+constexpr uint32_t KCAP = LILY_K_CAP;
+constexpr uint32_t SP_SMEM = 256;       // bias + ban entries staged in shared memory
+constexpr uint32_t MAX_SLICES = 128;
+
+// Row status bits OR-ed into the handle's status word.
+constexpr uint32_t ROW_INTERNAL = 8;  // candidate buffer overflow: a bug, never expected
+
+struct SpecArgs {
+    const uint32_t *draft_ids;  // [n_spec]
+    const float *q_dense;       // [n_spec, q_ld] or null
+    uint64_t q_ld;
+    const uint32_t *q_ids;      // [n_spec, KCAP] or null
+    const float *q_probs;
+    const uint32_t *q_n;
+    const float *u_resid;       // [n_spec] or null (then from seed/step)
+    uint32_t n_spec;            // rows [row0, row0 + ...) below this index draw speculatively
+};
+
+struct KArgs {
+    const void *logits;
+    uint64_t logits_ld;
+    uint32_t vocab;
+    uint32_t rows;
+    const lily_sampling_params_t *params;  // device [rows] (null with force_greedy)
+    const float *uniforms;
+    const uint32_t *steps;
+    const uint32_t *history_ids;
+    const uint32_t *history_len;
+    uint64_t history_ld;
+    const uint32_t *extra_ids;  // ids appended to every row's history (earlier draws of a step)
+    uint32_t extra_len;
+    uint32_t force_greedy;      // ignore params: exact argmax rows
+    const uint32_t *bias_ids;
+    const float *bias_vals;
+    const uint32_t *bias_len;
+    const uint32_t *ban_ids;
+    const uint32_t *ban_len;
+    uint64_t list_ld;
+    const int32_t *forced_ids;
+    const uint32_t *count_slots;   // device [rows] or null
+    uint32_t *counts_table;        // [slots, vocab]
+    uint32_t *seen_table;          // [slots, seen_words]
+    uint32_t seen_words;           // words per slot bitmap = ceil(vocab / 32)
+    uint32_t row0;                 // first row of this launch (grid.y rows follow it)
+    uint32_t *counts_scratch;      // [max_rows, vocab], all zero between launches
+    uint32_t *out_ids;
+    uint32_t *out_status;
+    uint32_t *kept_n;
+    uint32_t *kept_ids;
+    float *kept_probs;
+    uint64_t kept_ld;
+    uint32_t n_slices;             // grid.x: the most slices a row may be cut into
+    uint2 *part;                   // [max_rows, CAP] (key, id): slice s at s * k
+    uint32_t *part_n;              // [max_rows, MAX_SLICES]
+    uint32_t *tickets;             // [max_rows], zero between launches
+    uint32_t *status_word;
+    SpecArgs spec;
+};
+
+struct SmemFixed {
+    uint32_t key[CAP];
+    uint32_t id[CAP];
+    uint32_t tkey[KCAP];  // select's staging; later the candidates' p
+    uint32_t tid[KCAP];   // select's staging; later the prefix sums
+    uint32_t hist[256];
+    uint32_t sp_ids[SP_SMEM];
+    float sp_vals[SP_SMEM];
+    uint32_t n;
+    uint32_t cnt;
+    uint32_t sel_digit;
+    uint32_t sel_before;
+    uint32_t sel_count;
+    uint32_t tau_key;
+    float c_raw;
+    uint32_t have_tau;
+    uint32_t err;
+    uint32_t is_last;
+    uint32_t n_keep;
+    uint32_t chosen;
+    float p_d;
+    float q_d;
+    uint32_t bloom[32];
+};
+
+struct RowCtx {
+    float T, rep, presence, frequency, top_p, min_p;
+    uint32_t k;
+    bool use_pen, need_counts, argmax_mode, monotone, has_special;
+    uint32_t lo, hi;
+    const uint32_t *seen;    // shared-memory bitmap of [lo, hi)
+    const uint32_t *counts;  // global count table of this row (null unless need_counts)
+    const uint32_t *bias_ids;
+    const float *bias_vals;
+    uint32_t bias_len;
+    const uint32_t *ban_ids;
+    uint32_t ban_len;
+    bool sp_in_smem;
+};
+
+__device__ __forceinline__ float neg_inf() { return __uint_as_float(0xFF800000u); }
+
+// Warp-aggregated append to the candidate buffer.
+__device__ __forceinline__ void push(SmemFixed *sm, uint32_t key, uint32_t id) {
+    const unsigned act = __activemask();
+    const int lane = threadIdx.x & 31;
+    const int leader = __ffs(act) - 1;
+    uint32_t base = 0;
+    if (lane == leader) {
+        base = atomicAdd(&sm->n, (uint32_t)__popc(act));
+    }
+    base = __shfl_sync(act, base, leader);
+    const uint32_t slot = base + __popc(act & ((1u << lane) - 1u));
+    if (slot < CAP) {
+        sm->key[slot] = key;
+        sm->id[slot] = id;
+    } else {
+        sm->err = ROW_INTERNAL;
+    }
+}
+
+// The key of a logit that neither history nor bias nor ban touches.
+__device__ __forceinline__ uint32_t plain_key(float l, float T, bool argmax_mode) {
+    float q = __fdiv_rn(l, T);
+    if (argmax_mode) {
+        // The exact-argmax route compares floats: NaN never wins and the two
+        // zeros tie (src/kernels/metal/elementwise.metal:145-150).
+        q = q != q ? neg_inf() : __fadd_rn(q, 0.0f);
+    }
+    return key_of(q);
+}
+
+// Whether `id` is on the row's bias or ban list.
+__device__ __forceinline__ bool is_special(const SmemFixed *sm, const RowCtx &c, uint32_t id) {
+    if (!((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u)) {
+        return false;
+    }
+    const uint32_t n = c.bias_len + c.ban_len;
+    for (uint32_t j = 0; j < n; ++j) {
+        uint32_t e;
+        if (c.sp_in_smem) {
+            e = sm->sp_ids[j];
+        } else {
+            e = j < c.bias_len ? c.bias_ids[j] : c.ban_ids[j - c.bias_len];
+        }
+        if (e == id) {
+            return true;
+        }
+    }
+    return false;
+}
+
+// Full adjustment of one logit and its push. `special`: the id is on the
+// bias / ban list (called from the up-front pass only).
+__device__ __forceinline__ void consider(SmemFixed *sm, const RowCtx &c, uint32_t id, float l,
+                                         bool special, bool have_tau, uint32_t tau_key) {
+    float x = l;
+    bool banned = false;
+    if (special) {
+        for (uint32_t j = 0; j < c.bias_len; ++j) {
+            const uint32_t e = c.sp_in_smem ? sm->sp_ids[j] : c.bias_ids[j];
+            if (e == id) {
+                x = __fadd_rn(x, c.sp_in_smem ? sm->sp_vals[j] : c.bias_vals[j]);
+            }
+        }
+        for (uint32_t j = 0; j < c.ban_len; ++j) {
+            const uint32_t e = c.sp_in_smem ? sm->sp_ids[c.bias_len + j] : c.ban_ids[j];
+            banned = banned || e == id;
+        }
+    } else if (c.has_special && is_special(sm, c, id)) {
+        return;  // handled up front
+    }
+    if (c.use_pen) {
+        const uint32_t off = id - c.lo;
+        if ((c.seen[off >> 5] >> (off & 31u)) & 1u) {
+            float cnt = 1.0f;
+            if (c.need_counts) {
+                cnt = (float)__ldcg(c.counts + id);
+            }
+            x = x > 0.0f ? __fdiv_rn(x, c.rep) : __fmul_rn(x, c.rep);
+            x = __fsub_rn(x, __fadd_rn(c.presence, __fmul_rn(c.frequency, cnt)));
+        }
+    }
+    if (banned) {
+        x = neg_inf();
+    }
+    float q = __fdiv_rn(x, c.T);
+    if (c.argmax_mode) {
+        q = q != q ? neg_inf() : __fadd_rn(q, 0.0f);
+    } else if (q != q) {
+        sm->err = LILY_ROW_NAN;
+        return;
+    }
+    const uint32_t key = key_of(q);
+    if (!have_tau || key > tau_key) {
+        push(sm, key, id);
+    }
+}
+
+// Warp 0 finds the histogram bin in which the running count (from the top
+// bin down when `descending`, else from bin 0 up) reaches `remaining`.
+__device__ __forceinline__ void find_digit(SmemFixed *sm, uint32_t remaining, bool descending) {
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        uint32_t c[8];
+        uint32_t sum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int bin = lane * 8 + j;
+            bin = descending ? 255 - bin : bin;
+            c[j] = sm->hist[bin];
+            sum += c[j];
+        }
+        uint32_t incl = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        const uint32_t excl = incl - sum;
+        if (excl < remaining && remaining <= incl) {
+            uint32_t cum = excl;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (cum + c[j] >= remaining) {
+                    int bin = lane * 8 + j;
+                    bin = descending ? 255 - bin : bin;
+                    sm->sel_digit = (uint32_t)bin;
+                    sm->sel_before = cum;
+                    sm->sel_count = c[j];
+                    break;
+                }
+                cum += c[j];
+            }
+        }
+    }
+}
+
+// Keeps the best k of the n buffered candidates (n > k), by key descending
+// then id ascending, in slots [0, k) in any order; records the k-th key.
+__device__ void select_topk(SmemFixed *sm, uint32_t n, uint32_t k) {
+    const uint32_t tid = threadIdx.x;
+    uint32_t prefix = 0, mask = 0, remaining = k, count_eq = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) {
+            sm->hist[tid] = 0;
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < n; i += NT) {
+            const uint32_t key = sm->key[i];
+            if ((key & mask) == prefix) {
+                atomicAdd(&sm->hist[(key >> shift) & 255u], 1u);
+            }
+        }
+        __syncthreads();
+        find_digit(sm, remaining, true);
+        __syncthreads();
+        prefix |= sm->sel_digit << shift;
+        mask |= 255u << shift;
+        remaining -= sm->sel_before;
+        count_eq = sm->sel_count;
+    }
+    const uint32_t kstar = prefix;
+    uint32_t istar = 0xFFFFFFFFu;
+    if (count_eq > remaining) {
+        // More candidates share the k-th key than fit: the lowest ids win.
+        uint32_t ip = 0, im = 0, rem = remaining;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (tid < 256) {
+                sm->hist[tid] = 0;
+            }
+            __syncthreads();
+            for (uint32_t i = tid; i < n; i += NT) {
+                const uint32_t id = sm->id[i];
+                if (sm->key[i] == kstar && (id & im) == ip) {
+                    atomicAdd(&sm->hist[(id >> shift) & 255u], 1u);
+                }
+            }
+            __syncthreads();
+            find_digit(sm, rem, false);
+            __syncthreads();
+            ip |= sm->sel_digit << shift;
+            im |= 255u << shift;
+            rem -= sm->sel_before;
+        }
+        istar = ip;
+    }
+    if (tid == 0) {
+        sm->cnt = 0;
+    }
+    __syncthreads();
+    for (uint32_t i0 = 0; i0 < n; i0 += NT) {
+        const uint32_t i = i0 + tid;
+        if (i < n) {
+            const uint32_t key = sm->key[i];
+            const uint32_t id = sm->id[i];
+            if (key > kstar || (key == kstar && id <= istar)) {
+                const unsigned act = __activemask();
+                const int lane = tid & 31;
+                const int leader = __ffs(act) - 1;
+                uint32_t base = 0;
+                if (lane == leader) {
+                    base = atomicAdd(&sm->cnt, (uint32_t)__popc(act));
+                }
+                base = __shfl_sync(act, base, leader);
+                const uint32_t slot = base + __popc(act & ((1u << lane) - 1u));
+                if (slot < KCAP) {
+                    sm->tkey[slot] = key;
+                    sm->tid[slot] = id;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < k; i += NT) {
+        sm->key[i] = sm->tkey[i];
+        sm->id[i] = sm->tid[i];
+    }
+    if (tid == 0) {
+        if (sm->cnt != k) {
+            sm->err = ROW_INTERNAL;
+        }
+        sm->n = k;
+        sm->tau_key = kstar;
+    }
+    __syncthreads();
+}
+
+// The largest raw logit c whose plain key does not beat kstar: an untouched
+// logit l beats the k-th candidate exactly when l > c. Thread 0 only.
+__device__ float raw_threshold(uint32_t kstar, float T, bool argmax_mode) {
+    const float tq = float_of_key(kstar);
+    if (tq != tq) {
+        return tq;
+    }
+    if (tq == neg_inf() || tq == -neg_inf()) {
+        return tq;
+    }
+    uint32_t ck = key_of(__fmul_rn(tq, T));
+    int it = 0;
+    while (plain_key(float_of_key(ck), T, argmax_mode) > kstar && it < 64) {
+        --ck;
+        ++it;
+    }
+    while (plain_key(float_of_key(ck + 1u), T, argmax_mode) <= kstar && it < 64) {
+        ++ck;
+        ++it;
+    }
+    if (it >= 64) {
+        return neg_inf();  // conservative: every finite logit is looked at
+    }
+    float c = float_of_key(ck);
+    if (c == 0.0f) {
+        // The float compare cannot tell the zeros apart; let both through.
+        c = __uint_as_float(0x80000001u);
+    }
+    return c;
+}
+
+// Bitonic sort of slots [0, n) by (key descending, id ascending).
+__device__ void sort_candidates(SmemFixed *sm, uint32_t n) {
+    const uint32_t tid = threadIdx.x;
+    uint32_t P = 1;
+    while (P < n) {
+        P <<= 1;
+    }
+    for (uint32_t i = n + tid; i < P; i += NT) {
+        sm->key[i] = 0u;
+        sm->id[i] = 0xFFFFFFFFu;
+    }
+    __syncthreads();
+    for (uint32_t size = 2; size <= P; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            for (uint32_t t = tid; t < (P >> 1); t += NT) {
+                const uint32_t i = ((t / stride) * stride << 1) + (t % stride);
+                const uint32_t j = i + stride;
+                const uint32_t ka = sm->key[i], kb = sm->key[j];
+                const uint32_t ia = sm->id[i], ib = sm->id[j];
+                const bool a_first = ka > kb || (ka == kb && ia < ib);
+                const bool forward = (i & size) == 0;
+                if (forward != a_first) {
+                    sm->key[i] = kb;
+                    sm->key[j] = ka;
+                    sm->id[i] = ib;
+                    sm->id[j] = ia;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// First slot of [0, n) whose prefix sum exceeds target, else the last slot
+// (tests/unit/kernels/sample.rs:48-52). Result in sm->chosen.
+__device__ void pick(SmemFixed *sm, const float *cum, uint32_t n, float target) {
+    const uint32_t tid = threadIdx.x;
+    if (tid == 0) {
+        sm->chosen = n - 1u;
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < n; i += NT) {
+        if (target < cum[i]) {
+            atomicMin(&sm->chosen, i);
+        }
+    }
+    __syncthreads();
+}
+
+// Steps 6-8 on the sorted candidates [0, n): softmax weights, sequential
+// prefix, cut, draw (plain or speculative), outputs.
+__device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_t row,
+                         uint32_t n, const lily_sampling_params_t &P) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t out_row = row;
+    float *p = reinterpret_cast<float *>(sm->tkey);
+    float *cum = reinterpret_cast<float *>(sm->tid);
+    const float top = float_of_key(sm->key[0]);
+    uint32_t err = sm->err;
+    if (!c.argmax_mode && err == 0 && (top == neg_inf() || top == -neg_inf())) {
+        err = LILY_ROW_NONFINITE;
+    }
+    if (err != 0) {
+        if (tid == 0) {
+            a.out_ids[out_row] = 0xFFFFFFFFu;
+            if (a.out_status) {
+                a.out_status[out_row] = err;
+            }
+            if (a.kept_n) {
+                a.kept_n[out_row] = 0;
+            }
+            atomicOr(a.status_word, 1u << (err & 31u));
+        }
+        return;
+    }
+    if (c.argmax_mode) {
+        if (tid == 0) {
+            a.out_ids[out_row] = sm->id[0];
+            if (a.out_status) {
+                a.out_status[out_row] = LILY_ROW_OK;
+            }
+            if (a.kept_n) {
+                a.kept_n[out_row] = 1;
+                a.kept_ids[(uint64_t)out_row * a.kept_ld] = sm->id[0];
+                a.kept_probs[(uint64_t)out_row * a.kept_ld] = 1.0f;
+            }
+        }
+        return;
+    }
+    for (uint32_t i = tid; i < n; i += NT) {
+        p[i] = exp_f32(__fsub_rn(float_of_key(sm->key[i]), top));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float s = 0.0f;
+        for (uint32_t i = 0; i < n; ++i) {
+            s = __fadd_rn(s, p[i]);
+            cum[i] = s;
+        }
+        sm->n_keep = n;
+    }
+    __syncthreads();
+    const float limit = __fmul_rn(c.top_p, cum[n - 1u]);
+    for (uint32_t i = tid + 1u; i < n; i += NT) {
+        if (!(cum[i - 1u] < limit && p[i] >= c.min_p)) {
+            atomicMin(&sm->n_keep, i);
+        }
+    }
+    __syncthreads();
+    const uint32_t n_keep = sm->n_keep;
+    const float mass = cum[n_keep - 1u];
+
+    float u;
+    uint32_t step = 0;
+    if (a.uniforms) {
+        u = a.uniforms[row];
+    } else {
+        step = a.steps ? a.steps[row] : 0u;
+        u = uniform_for(P.seed, step);
+    }
+    if (a.kept_n) {
+        for (uint32_t i = tid; i < n_keep; i += NT) {
+            a.kept_ids[(uint64_t)out_row * a.kept_ld + i] = sm->id[i];
+            a.kept_probs[(uint64_t)out_row * a.kept_ld + i] = __fdiv_rn(p[i], mass);
+        }
+        if (tid == 0) {
+            a.kept_n[out_row] = n_keep;
+        }
+    }
+
+    uint32_t chosen_id;
+    if (row < a.spec.n_spec) {
+        // Speculative draw against proposal `row` (tests/unit/kernels/
+        // sample.rs:264-283; src/kernels/metal/sample.metal:597-658).
+        const uint32_t d = a.spec.draft_ids[row];
+        if (tid == 0) {
+            sm->p_d = 0.0f;
+            float qd = 0.0f;
+            if (a.spec.q_dense) {
+                qd = d < a.vocab ? a.spec.q_dense[(uint64_t)row * a.spec.q_ld + d] : 0.0f;
+            }
+            sm->q_d = qd;
+        }
+        __syncthreads();
+        const uint32_t qn = a.spec.q_dense ? 0u : min(a.spec.q_n[row], KCAP);
+        const uint32_t *qi = a.spec.q_ids + (uint64_t)row * KCAP;
+        const float *qp = a.spec.q_probs + (uint64_t)row * KCAP;
+        for (uint32_t i = tid; i < n_keep; i += NT) {
+            if (sm->id[i] == d) {
+                sm->p_d = __fdiv_rn(p[i], mass);
+            }
+        }
+        for (uint32_t j = tid; j < qn; j += NT) {
+            if (qi[j] == d) {
+                sm->q_d = qp[j];
+            }
+        }
+        __syncthreads();
+        if (__fmul_rn(u, sm->q_d) < sm->p_d) {
+            chosen_id = d;
+        } else {
+            // Residual max(0, p - q) over the kept set, rank order.
+            float *r = reinterpret_cast<float *>(sm->key + KCAP);
+            float *rcum = reinterpret_cast<float *>(sm->id + KCAP);
+            for (uint32_t i = tid; i < n_keep; i += NT) {
+                const uint32_t id = sm->id[i];
+                float q = 0.0f;
+                if (a.spec.q_dense) {
+                    q = a.spec.q_dense[(uint64_t)row * a.spec.q_ld + id];
+                } else {
+                    for (uint32_t j = 0; j < qn; ++j) {
+                        if (qi[j] == id) {
+                            q = qp[j];
+                            break;
+                        }
+                    }
+                }
+                const float x = __fsub_rn(__fdiv_rn(p[i], mass), q);
+                r[i] = x > 0.0f ? x : 0.0f;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                float s = 0.0f;
+                for (uint32_t i = 0; i < n_keep; ++i) {
+                    s = __fadd_rn(s, r[i]);
+                    rcum[i] = s;
+                }
+            }
+            __syncthreads();
+            const float r_total = rcum[n_keep - 1u];
+            float u2;
+            if (a.spec.u_resid) {
+                u2 = a.spec.u_resid[row];
+            } else {
+                u2 = uniform_for(P.seed, step | 0x80000000u);
+            }
+            if (r_total > 0.0f) {
+                pick(sm, rcum, n_keep, __fmul_rn(u2, r_total));
+            } else {
+                pick(sm, cum, n_keep, __fmul_rn(u2, mass));
+            }
+            chosen_id = sm->id[sm->chosen];
+        }
+    } else {
+        pick(sm, cum, n_keep, __fmul_rn(u, mass));
+        chosen_id = sm->id[sm->chosen];
+    }
+    if (tid == 0) {
+        a.out_ids[out_row] = chosen_id;
+        if (a.out_status) {
+            a.out_status[out_row] = LILY_ROW_OK;
+        }
+        if (c.use_pen && a.count_slots) {
+            // src/kernels/metal/sample.metal:509-511: the draw is counted.
+            const uint32_t slot = a.count_slots[row];
+            if (chosen_id < a.vocab) {
+                atomicAdd(a.counts_table + (uint64_t)slot * a.vocab + chosen_id, 1u);
+                atomicOr(a.seen_table + (uint64_t)slot * a.seen_words + (chosen_id >> 5),
+                         1u << (chosen_id & 31u));
+            }
+        }
+    }
+}
+
+template <typename T>
+struct Frag;
+
+template <>
+struct Frag<float> {
+    uint4 v[2];
+};
+
+template <>
+struct Frag<__nv_bfloat16> {
+    uint4 v[1];
+};
+
+template <typename T>
+__device__ __forceinline__ float frag_get(const Frag<T> &f, int e);
+
+template <>
+__device__ __forceinline__ float frag_get<float>(const Frag<float> &f, int e) {
+    const uint4 &q = f.v[e >> 2];
+    const uint32_t w = (e & 3) == 0 ? q.x : (e & 3) == 1 ? q.y : (e & 3) == 2 ? q.z : q.w;
+    return __uint_as_float(w);
+}
+
+template <>
+__device__ __forceinline__ float frag_get<__nv_bfloat16>(const Frag<__nv_bfloat16> &f, int e) {
+    const uint4 &q = f.v[0];
+    const uint32_t w = (e >> 1) == 0 ? q.x : (e >> 1) == 1 ? q.y : (e >> 1) == 2 ? q.z : q.w;
+    return (e & 1) ? bf16_hi(w) : bf16_lo(w);
+}
+
+// The NaN-propagating maximum of the fragment's eight logits.
+__device__ __forceinline__ float frag_max(const Frag<float> &f) {
+    const float a = max_nan_f32(__uint_as_float(f.v[0].x), __uint_as_float(f.v[0].y));
+    const float b = max_nan_f32(__uint_as_float(f.v[0].z), __uint_as_float(f.v[0].w));
+    const float c = max_nan_f32(__uint_as_float(f.v[1].x), __uint_as_float(f.v[1].y));
+    const float d = max_nan_f32(__uint_as_float(f.v[1].z), __uint_as_float(f.v[1].w));
+    return max_nan_f32(max_nan_f32(a, b), max_nan_f32(c, d));
+}
+
+__device__ __forceinline__ float frag_max(const Frag<__nv_bfloat16> &f) {
+    const uint32_t a = max_nan_bf16x2(f.v[0].x, f.v[0].y);
+    const uint32_t b = max_nan_bf16x2(f.v[0].z, f.v[0].w);
+    const uint32_t m = max_nan_bf16x2(a, b);
+    return max_nan_f32(bf16_lo(m), bf16_hi(m));
+}
+
+__device__ __forceinline__ float widen(float x) { return x; }
+__device__ __forceinline__ float widen(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+// Loads the eight logits [base, base + 8) of a row; slots at or past `hi`
+// read as zero and are never looked at.
+template <typename T, bool VEC>
+__device__ __forceinline__ void load_frag(Frag<T> &f, const T *row, uint32_t base, uint32_t hi) {
+    constexpr int NV = sizeof(Frag<T>) / 16;
+    if (VEC && base + GROUP <= hi) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(row + base);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            f.v[i] = __ldcs(src + i);
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        f.v[i] = make_uint4(0, 0, 0, 0);
+    }
+    if (base >= hi) {
+        return;
+    }
+    uint32_t *words = reinterpret_cast<uint32_t *>(&f);
+    if (sizeof(T) == 4) {
+#pragma unroll
+        for (int e = 0; e < (int)GROUP; ++e) {
+            if (base + e < hi) {
+                words[e] = __float_as_uint(widen(row[base + e]));
+            }
+        }
+    } else {
+        const uint16_t *r16 = reinterpret_cast<const uint16_t *>(row);
+#pragma unroll
+        for (int e = 0; e < (int)GROUP; ++e) {
+            if (base + e < hi) {
+                const uint32_t b = r16[base + e];
+                words[e >> 1] |= (e & 1) ? (b << 16) : b;
+            }
+        }
+    }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constant__ KArgs a) {
+    extern __shared__ uint4 smem_raw[];
+    SmemFixed *sm = reinterpret_cast<SmemFixed *>(smem_raw);
+    uint32_t *seen = reinterpret_cast<uint32_t *>(sm + 1);
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t row = a.row0 + blockIdx.y;  // every per-row array is indexed by this
+    const uint32_t slice = blockIdx.x;
+    const uint32_t out_row = row;
+
+    // ---- forced rows and parameters (uniform per block, before any barrier)
+    if (a.forced_ids) {
+        const int32_t forced = a.forced_ids[row];
+        if (forced >= 0) {
+            if (slice == 0 && tid == 0) {
+                a.out_ids[out_row] = (uint32_t)forced;
+                if (a.out_status) {
+                    a.out_status[out_row] = LILY_ROW_FORCED;
+                }
+                if (a.kept_n) {
+                    a.kept_n[out_row] = 0;
+                }
+            }
+            return;
+        }
+    }
+    lily_sampling_params_t P;
+    if (a.force_greedy) {
+        P.temperature = 0.0f;
+        P.top_k = 1;
+        P.top_p = 1.0f;
+        P.min_p = 0.0f;
+        P.presence_penalty = 0.0f;
+        P.frequency_penalty = 0.0f;
+        P.repetition_penalty = 1.0f;
+        P.seed = 0;
+    } else {
+        P = a.params[row];
+    }
+    {
+        // src/kernels/sample.rs:57-79, for parameters the host never saw.
+        const bool fin = isfinite(P.temperature) && isfinite(P.top_p) && isfinite(P.min_p) &&
+                         isfinite(P.repetition_penalty) && isfinite(P.presence_penalty) &&
+                         isfinite(P.frequency_penalty);
+        const bool ok = fin && P.temperature >= 0.0f && P.top_p > 0.0f && P.top_p <= 1.0f &&
+                        P.min_p >= 0.0f && P.min_p <= 1.0f && P.repetition_penalty > 0.0f;
+        if (!ok) {
+            if (slice == 0 && tid == 0) {
+                a.out_ids[out_row] = 0xFFFFFFFFu;
+                if (a.out_status) {
+                    a.out_status[out_row] = LILY_ROW_PARAMS;
+                }
+                if (a.kept_n) {
+                    a.kept_n[out_row] = 0;
+                }
+                atomicOr(a.status_word, 1u << LILY_ROW_PARAMS);
+            }
+            return;
+        }
+    }
+
+    RowCtx c;
+    const bool greedy = P.temperature <= 0.0f || P.top_k == 1u;
+    c.use_pen = P.presence_penalty != 0.0f || P.frequency_penalty != 0.0f ||
+                P.repetition_penalty != 1.0f;
+    c.T = greedy ? 1.0f : P.temperature;
+    c.k = greedy ? 1u : (P.top_k == 0u ? KCAP : min(P.top_k, KCAP));
+    c.rep = P.repetition_penalty;
+    c.presence = P.presence_penalty;
+    c.frequency = P.frequency_penalty;
+    c.top_p = P.top_p;
+    c.min_p = P.min_p;
+    c.bias_len = (a.bias_ids && a.bias_len) ? a.bias_len[row] : 0u;
+    c.ban_len = (a.ban_ids && a.ban_len) ? a.ban_len[row] : 0u;
+    c.bias_ids = a.bias_ids ? a.bias_ids + (uint64_t)row * a.list_ld : nullptr;
+    c.bias_vals = a.bias_vals ? a.bias_vals + (uint64_t)row * a.list_ld : nullptr;
+    c.ban_ids = a.ban_ids ? a.ban_ids + (uint64_t)row * a.list_ld : nullptr;
+    c.has_special = (c.bias_len + c.ban_len) > 0u;
+    c.sp_in_smem = (c.bias_len + c.ban_len) <= SP_SMEM;
+    c.argmax_mode = greedy && !c.use_pen && !c.has_special;
+    // Penalties that can only lower a logit let the raw threshold reject
+    // seen ids without adjusting them.
+    c.monotone = P.repetition_penalty >= 1.0f &&
+                 !(__float_as_uint(P.presence_penalty) >> 31) &&
+                 !(__float_as_uint(P.frequency_penalty) >> 31);
+    c.need_counts = c.use_pen && P.frequency_penalty != 0.0f;
+    // A row is cut into at most CAP / k slices so that the merge of the
+    // slices' best k fits the candidate buffer; blocks past that leave.
+    const uint32_t want = min(a.n_slices, CAP / c.k);
+    const uint32_t slice_len = (((a.vocab + want - 1u) / want) + 255u) & ~255u;
+    const uint32_t n_slices = (a.vocab + slice_len - 1u) / slice_len;
+    if (slice >= n_slices) {
+        return;
+    }
+    c.lo = slice * slice_len;
+    c.hi = min(a.vocab, c.lo + slice_len);
+    c.seen = seen;
+    const bool table_mode = a.count_slots != nullptr;
+    const uint32_t slot = table_mode ? a.count_slots[row] : 0u;
+    uint32_t *counts_rw = nullptr;
+    if (c.need_counts) {
+        counts_rw = table_mode ? a.counts_table + (uint64_t)slot * a.vocab
+                               : a.counts_scratch + (uint64_t)row * a.vocab;
+    }
+    c.counts = counts_rw;
+    const uint32_t hist_len = (c.use_pen && !table_mode && a.history_ids && a.history_len)
+                                  ? a.history_len[row]
+                                  : 0u;
+    const uint32_t *hist = a.history_ids ? a.history_ids + (uint64_t)row * a.history_ld : nullptr;
+    const uint32_t extra_len = (c.use_pen && !table_mode) ? a.extra_len : 0u;
+    const T *row_ptr = reinterpret_cast<const T *>(a.logits) + (uint64_t)row * a.logits_ld;
+
+    // ---- A. bitmaps
+    const uint32_t slice_words = (c.hi - c.lo + 31u) >> 5;
+    if (tid == 0) {
+        sm->n = 0;
+        sm->err = 0;
+        sm->have_tau = 0;
+        sm->tau_key = 0;
+        sm->c_raw = __uint_as_float(0x7FC00000u);
+    }
+    if (tid < 32) {
+        sm->bloom[tid] = 0;
+    }
+    if (c.use_pen) {
+        if (table_mode) {
+            const uint32_t *src = a.seen_table + (uint64_t)slot * a.seen_words + (c.lo >> 5);
+            for (uint32_t w = tid; w < slice_words; w += NT) {
+                seen[w] = src[w];
+            }
+        } else {
+            for (uint32_t w = tid; w < slice_words; w += NT) {
+                seen[w] = 0;
+            }
+        }
+    }
+    __syncthreads();
+    if (hist_len + extra_len > 0u) {
+        for (uint32_t i = tid; i < hist_len + extra_len; i += NT) {
+            const uint32_t id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
+            if (id >= c.lo && id < c.hi) {
+                const uint32_t off = id - c.lo;
+                atomicOr(&seen[off >> 5], 1u << (off & 31u));
+                if (c.need_counts) {
+                    atomicAdd(counts_rw + id, 1u);
+                }
+            }
+        }
+    }
+    if (c.has_special) {
+        const uint32_t n_sp = c.bias_len + c.ban_len;
+        for (uint32_t j = tid; j < n_sp; j += NT) {
+            const uint32_t id = j < c.bias_len ? c.bias_ids[j] : c.ban_ids[j - c.bias_len];
+            atomicOr(&sm->bloom[(id >> 5) & 31u], 1u << (id & 31u));
+            if (c.sp_in_smem) {
+                sm->sp_ids[j] = id;
+                sm->sp_vals[j] = j < c.bias_len ? c.bias_vals[j] : 0.0f;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- B. ids on the bias / ban lists, each once
+    if (c.has_special) {
+        const uint32_t n_sp = c.bias_len + c.ban_len;
+        for (uint32_t j = tid; j < n_sp; j += NT) {
+            const uint32_t id = j < c.bias_len ? c.bias_ids[j] : c.ban_ids[j - c.bias_len];
+            if (id < c.lo || id >= c.hi) {
+                continue;
+            }
+            bool first = true;
+            for (uint32_t e = 0; e < j && first; ++e) {
+                const uint32_t other = c.sp_in_smem
+                                           ? sm->sp_ids[e]
+                                           : (e < c.bias_len ? c.bias_ids[e] : c.ban_ids[e - c.bias_len]);
+                first = other != id;
+            }
+            if (first) {
+                consider(sm, c, id, widen(row_ptr[id]), true, false, 0u);
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- C. one streaming pass over the slice
+    constexpr int PF = sizeof(T) == 4 ? 3 : 4;
+    const uint32_t span = c.hi - c.lo;
+    const uint32_t nrounds = (span + ROUND - 1u) / ROUND;
+    float c_raw = __uint_as_float(0x7FC00000u);  // NaN: nothing is rejected yet
+    uint32_t tau_key = 0;
+    bool have_tau = false;
+    const bool group_check = c.use_pen && !c.monotone;
+    Frag<T> ring[PF];
+#pragma unroll
+    for (int d = 0; d < PF; ++d) {
+        load_frag<T, VEC>(ring[d], row_ptr, c.lo + (uint32_t)d * ROUND + tid * GROUP, c.hi);
+    }
+    for (uint32_t r0 = 0; r0 < nrounds; r0 += PF) {
+#pragma unroll
+        for (int d = 0; d < PF; ++d) {
+            const uint32_t r = r0 + d;
+            if (r < nrounds) {
+                const Frag<T> cur = ring[d];
+                load_frag<T, VEC>(ring[d], row_ptr, c.lo + (r + PF) * ROUND + tid * GROUP, c.hi);
+                const uint32_t base = c.lo + r * ROUND + tid * GROUP;
+                if (base < c.hi) {
+                    const uint32_t nvalid = min(GROUP, c.hi - base);
+                    bool all = nvalid < GROUP;
+                    if (group_check && !all) {
+                        const uint32_t off = base - c.lo;
+                        all = ((seen[off >> 5] >> (off & 31u)) & 0xFFu) != 0u;
+                    }
+                    if (all || !(frag_max(cur) <= c_raw)) {
+#pragma unroll
+                        for (int e = 0; e < (int)GROUP; ++e) {
+                            const float l = frag_get<T>(cur, e);
+                            if ((uint32_t)e < nvalid && (all || !(l <= c_raw))) {
+                                consider(sm, c, base + e, l, false, have_tau, tau_key);
+                            }
+                        }
+                    }
+                }
+                const uint32_t pending = *reinterpret_cast<volatile uint32_t *>(&sm->n);
+                if (__syncthreads_or(pending > CAP - ROUND)) {
+                    select_topk(sm, min(sm->n, CAP), c.k);
+                    if (tid == 0) {
+                        sm->c_raw = raw_threshold(sm->tau_key, c.T, c.argmax_mode);
+                        sm->have_tau = 1;
+                    }
+                    __syncthreads();
+                    c_raw = sm->c_raw;
+                    tau_key = sm->tau_key;
+                    have_tau = true;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // The count table goes back to all zero (history-list mode only).
+    if (c.need_counts && !table_mode) {
+        for (uint32_t i = tid; i < hist_len + extra_len; i += NT) {
+            const uint32_t id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
+            if (id >= c.lo && id < c.hi) {
+                atomicSub(counts_rw + id, 1u);
+            }
+        }
+    }
+
+    uint32_t n = min(sm->n, CAP);
+    __syncthreads();
+    if (n > c.k) {
+        select_topk(sm, n, c.k);
+        n = c.k;
+    }
+
+    // ---- D. merge the slices
+    if (n_slices > 1u) {
+        uint2 *mine = a.part + (uint64_t)row * CAP + slice * c.k;
+        for (uint32_t i = tid; i < n; i += NT) {
+            mine[i] = make_uint2(sm->key[i], sm->id[i]);
+        }
+        if (tid == 0) {
+            a.part_n[row * MAX_SLICES + slice] = n | (sm->err << 24);
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t ticket = atomicAdd(a.tickets + row, 1u);
+            sm->is_last = ticket == n_slices - 1u;
+        }
+        __syncthreads();
+        if (!sm->is_last) {
+            return;
+        }
+        __threadfence();
+        uint32_t total = 0;
+        uint32_t err = 0;
+        for (uint32_t s = 0; s < n_slices; ++s) {
+            const uint32_t word = __ldcg(a.part_n + row * MAX_SLICES + s);
+            const uint32_t cnt = word & 0xFFFFFFu;
+            err |= word >> 24;
+            const uint2 *src = a.part + (uint64_t)row * CAP + s * c.k;
+            for (uint32_t i = tid; i < cnt; i += NT) {
+                if (total + i < CAP) {
+                    const uint2 e = __ldcg(src + i);
+                    sm->key[total + i] = e.x;
+                    sm->id[total + i] = e.y;
+                }
+            }
+            total += cnt;
+        }
+        if (tid == 0) {
+            a.tickets[row] = 0;
+            sm->n = min(total, CAP);
+            if (err) {
+                sm->err = err & (err - 1u) ? LILY_ROW_NAN : err;
+            }
+            if (total > CAP) {
+                sm->err = ROW_INTERNAL;
+            }
+        }
+        __syncthreads();
+        n = sm->n;
+        if (n > c.k) {
+            select_topk(sm, n, c.k);
+            n = c.k;
+        }
+    }
+    if (n == 0u) {
+        // Nothing but NaNs reached the buffer (or a bug): an error row.
+        if (tid == 0) {
+            const uint32_t err = sm->err ? sm->err : ROW_INTERNAL;
+            a.out_ids[out_row] = 0xFFFFFFFFu;
+            if (a.out_status) {
+                a.out_status[out_row] = err;
+            }
+            if (a.kept_n) {
+                a.kept_n[out_row] = 0;
+            }
+            atomicOr(a.status_word, 1u << (err & 31u));
+        }
+        return;
+    }
+    sort_candidates(sm, n);
+    finalize(sm, a, c, row, n, P);
+}
+
+// src/kernels/metal/spec.metal:14-38, one thread.
+__global__ void spec_accept_kernel(const uint32_t *draws, const uint32_t *ids, uint32_t id_offset,
+                                   uint32_t m, uint32_t *ctrl, uint32_t pos0, uint32_t ratio,
+                                   uint32_t chain, uint32_t stride) {
+    if (blockIdx.x != 0 || threadIdx.x != 0) {
+        return;
+    }
+    // ids[j + id_offset] is the token row j's draw must equal: the verified
+    // tokens start with the pending token (offset 1), a bare proposal list
+    // does not (offset 0).
+    uint32_t acc = 0;
+    while (acc + 1u < m && draws[acc] == ids[acc + id_offset]) {
+        ++acc;
+    }
+    ctrl[0] = acc;
+    if (stride == 0u) {
+        return;
+    }
+    ctrl[stride] = acc + 1u;
+    for (uint32_t i = 0; i < chain; ++i) {
+        const uint32_t p = pos0 + acc + 1u + i;
+        ctrl[(2u + 3u * i) * stride] = p;
+        ctrl[(3u + 3u * i) * stride] = p / ratio;
+        ctrl[(4u + 3u * i) * stride] = ((p + 1u) % ratio == 0u) ? 1u : 0u;
+    }
+}
+
+// Histogram-slot maintenance (src/kernels/sample.rs:145-174).
+__global__ void uncount_kernel(uint32_t *counts, uint32_t *seen, uint32_t vocab, uint32_t token) {
+    if (blockIdx.x != 0 || threadIdx.x != 0 || token >= vocab) {
+        return;
+    }
+    const uint32_t cur = counts[token];
+    if (cur > 0u) {
+        counts[token] = cur - 1u;
+        if (cur == 1u) {
+            seen[token >> 5] &= ~(1u << (token & 31u));
+        }
+    }
+}
+
+__global__ void rebuild_seen_kernel(const uint32_t *counts, uint32_t *seen, uint32_t vocab) {
+    const uint32_t w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w * 32u >= vocab) {
+        return;
+    }
+    uint32_t bits = 0;
+    for (uint32_t b = 0; b < 32u; ++b) {
+        const uint32_t id = w * 32u + b;
+        if (id < vocab && counts[id] > 0u) {
+            bits |= 1u << b;
+        }
+    }
+    seen[w] = bits;
+}
+
+__global__ void exp_kernel(const float *in, float *out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        out[i] = exp_f32(in[i]);
+    }
+}
+
+}  // namespace lily

@@ -379,6 +379,19 @@ int lo_sample(const float *logits, uint32_t vocab, const lo_params_t *p,
     if (lo_validate(p) != LO_OK) {
         return LO_ERR_PARAMS;
     }
+    if (lo_is_greedy(p) && !lo_uses_penalties(p) && n_bias == 0u && n_ban == 0u) {
+        /* src/kernels/sample.rs:382-385: not a sampled draw, the exact argmax. */
+        *out_id = lo_argmax(logits, vocab);
+        kept_ids[0] = *out_id;
+        kept_w[0] = 1.0f;
+        kept_cum[0] = 1.0f;
+        kept_prob[0] = 1.0f;
+        *n_keep = 1u;
+        if (near_tie != NULL) {
+            *near_tie = 0u;
+        }
+        return LO_OK;
+    }
     float *adjusted = (float *)malloc((size_t)vocab * sizeof(float));
     if (adjusted == NULL) {
         return LO_ERR_ARG;
