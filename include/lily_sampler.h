@@ -188,12 +188,13 @@ typedef struct lily_sample_args {
     const uint32_t *history_ids; /* [rows, history_ld] or NULL */
     const uint32_t *history_len; /* [rows] */
     uint64_t history_ld;
-    const uint32_t *bias_ids;    /* [rows, list_ld] or NULL */
-    const float *bias_vals;      /* [rows, list_ld] */
+    const uint32_t *bias_ids;    /* [rows, bias_ld] or NULL */
+    const float *bias_vals;      /* [rows, bias_ld] */
     const uint32_t *bias_len;    /* [rows] */
-    const uint32_t *ban_ids;     /* [rows, list_ld] or NULL */
+    uint64_t bias_ld;
+    const uint32_t *ban_ids;     /* [rows, ban_ld] or NULL */
     const uint32_t *ban_len;     /* [rows] */
-    uint64_t list_ld;            /* row pitch of the bias and ban arrays */
+    uint64_t ban_ld;
     const int32_t *forced_ids;   /* [rows], < 0 = none: the row returns this id
                                     without drawing (thinking-budget forcing) */
     const uint32_t *count_slots; /* HOST [rows] histogram slots, or NULL */

@@ -87,8 +87,8 @@ class SampleArgs(C.Structure):
         ("logits_ld", C.c_uint64),
         ("params", _vp), ("uniforms", _f32p), ("steps", _u32p),
         ("history_ids", _u32p), ("history_len", _u32p), ("history_ld", C.c_uint64),
-        ("bias_ids", _u32p), ("bias_vals", _f32p), ("bias_len", _u32p),
-        ("ban_ids", _u32p), ("ban_len", _u32p), ("list_ld", C.c_uint64),
+        ("bias_ids", _u32p), ("bias_vals", _f32p), ("bias_len", _u32p), ("bias_ld", C.c_uint64),
+        ("ban_ids", _u32p), ("ban_len", _u32p), ("ban_ld", C.c_uint64),
         ("forced_ids", _i32p), ("count_slots", _u32p),
         ("out_ids", _u32p), ("out_status", _u32p),
         ("kept_n", _u32p), ("kept_ids", _u32p), ("kept_probs", _f32p), ("kept_ld", C.c_uint64),
@@ -206,6 +206,13 @@ def _ptr(t):
     return t.data_ptr()
 
 
+def _ld(t) -> int:
+    """Row pitch in elements of a [rows, n] (or [n]) tensor."""
+    if t.dim() == 2 and t.shape[0] > 1:
+        return t.stride(0)
+    return t.shape[-1]
+
+
 def _dtype_code(t) -> int:
     import torch
 
@@ -313,7 +320,7 @@ class SamplerScratch:
         a.rows = rows
         a.logits = _ptr(logits)
         a.logits_dtype = _dtype_code(logits)
-        a.logits_ld = logits.stride(0) if logits.dim() == 2 else logits.shape[0]
+        a.logits_ld = _ld(logits)
         keep = []
         if params_on_device:
             a.params_on_device = 1
@@ -331,17 +338,13 @@ class SamplerScratch:
         if history_ids is not None:
             a.history_ids = _ptr(history_ids)
             a.history_len = _ptr(history_len)
-            a.history_ld = history_ids.stride(0) if history_ids.dim() == 2 else history_ids.shape[0]
-        list_ld = None
+            a.history_ld = _ld(history_ids)
         if bias_ids is not None:
             a.bias_ids, a.bias_vals, a.bias_len = _ptr(bias_ids), _ptr(bias_vals), _ptr(bias_len)
-            list_ld = bias_ids.stride(0) if bias_ids.dim() == 2 else bias_ids.shape[0]
+            a.bias_ld = _ld(bias_ids)
         if ban_ids is not None:
             a.ban_ids, a.ban_len = _ptr(ban_ids), _ptr(ban_len)
-            ld = ban_ids.stride(0) if ban_ids.dim() == 2 else ban_ids.shape[0]
-            assert list_ld is None or list_ld == ld, "bias and ban lists share one row pitch"
-            list_ld = ld
-        a.list_ld = list_ld or 0
+            a.ban_ld = _ld(ban_ids)
         a.forced_ids = _ptr(forced_ids)
         if count_slots is not None:
             carr = (C.c_uint32 * rows)(*[int(s) for s in count_slots])
@@ -351,13 +354,13 @@ class SamplerScratch:
         a.out_status = _ptr(out_status)
         if kept_n is not None:
             a.kept_n, a.kept_ids, a.kept_probs = _ptr(kept_n), _ptr(kept_ids), _ptr(kept_probs)
-            a.kept_ld = kept_ids.stride(0) if kept_ids.dim() == 2 else kept_ids.shape[0]
+            a.kept_ld = _ld(kept_ids)
         self._check(lib().lily_sample_batch(self._h, _stream_ptr(stream), C.byref(a)))
 
     def argmax_batch(self, logits, out_ids, stream=None):
         """src/kernels/elementwise.rs:297-308 argmax_f32 for each row."""
         rows = logits.shape[0] if logits.dim() == 2 else 1
-        ld = logits.stride(0) if logits.dim() == 2 else logits.shape[0]
+        ld = _ld(logits)
         self._check(lib().lily_argmax_batch(self._h, _stream_ptr(stream), _ptr(logits),
                                             _dtype_code(logits), ld, rows, _ptr(out_ids)))
 
@@ -371,12 +374,12 @@ class SamplerScratch:
         a.target_logits = _ptr(target_logits)
         a.logits_dtype = _dtype_code(target_logits)
         a.mode = mode
-        a.logits_ld = target_logits.stride(0)
+        a.logits_ld = _ld(target_logits)
         a.params = C.cast(C.pointer(params), C.c_void_p)
         a.draft_ids = _ptr(draft_ids)
         if q_dense is not None:
             a.q_dense = _ptr(q_dense)
-            a.q_ld = q_dense.stride(0)
+            a.q_ld = _ld(q_dense)
         a.q_ids, a.q_probs, a.q_n = _ptr(q_ids), _ptr(q_probs), _ptr(q_n)
         a.u_accept, a.u_resid = _ptr(u_accept), _ptr(u_resid)
         a.step0 = step0

@@ -623,9 +623,10 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
     a.bias_ids = g.bias_ids;
     a.bias_vals = g.bias_vals;
     a.bias_len = g.bias_len;
+    a.bias_ld = g.bias_ld;
     a.ban_ids = g.ban_ids;
     a.ban_len = g.ban_len;
-    a.list_ld = g.list_ld;
+    a.ban_ld = g.ban_ld;
     a.forced_ids = g.forced_ids;
     a.count_slots = d_slots;
     a.out_ids = g.out_ids;

@@ -72,9 +72,10 @@ struct KArgs {
     const uint32_t *bias_ids;
     const float *bias_vals;
     const uint32_t *bias_len;
+    uint64_t bias_ld;
     const uint32_t *ban_ids;
     const uint32_t *ban_len;
-    uint64_t list_ld;
+    uint64_t ban_ld;
     const int32_t *forced_ids;
     const uint32_t *count_slots;   // device [rows] or null
     uint32_t *counts_table;        // [slots, vocab]
@@ -785,9 +786,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     c.min_p = P.min_p;
     c.bias_len = (a.bias_ids && a.bias_len) ? a.bias_len[row] : 0u;
     c.ban_len = (a.ban_ids && a.ban_len) ? a.ban_len[row] : 0u;
-    c.bias_ids = a.bias_ids ? a.bias_ids + (uint64_t)row * a.list_ld : nullptr;
-    c.bias_vals = a.bias_vals ? a.bias_vals + (uint64_t)row * a.list_ld : nullptr;
-    c.ban_ids = a.ban_ids ? a.ban_ids + (uint64_t)row * a.list_ld : nullptr;
+    c.bias_ids = a.bias_ids ? a.bias_ids + (uint64_t)row * a.bias_ld : nullptr;
+    c.bias_vals = a.bias_vals ? a.bias_vals + (uint64_t)row * a.bias_ld : nullptr;
+    c.ban_ids = a.ban_ids ? a.ban_ids + (uint64_t)row * a.ban_ld : nullptr;
     c.has_special = (c.bias_len + c.ban_len) > 0u;
     c.sp_in_smem = (c.bias_len + c.ban_len) <= SP_SMEM;
     c.argmax_mode = greedy && !c.use_pen && !c.has_special;
