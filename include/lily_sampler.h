@@ -108,6 +108,12 @@ uint32_t lily_residual_step(uint32_t step);
                                      emission histogram (the reference's
                                      SamplerScratch::counts), one slot per row */
 
+#define LILY_FLAG_PHASE_CLOCKS 2u /* record per-block phase time stamps (the
+                                     counterpart of LILY_KERNEL_PROFILE,
+                                     src/metal.rs:140-198); off by default */
+#define LILY_MAX_SLICES 128u      /* most thread blocks a row is split over */
+#define LILY_PHASES 16u           /* stamps per block, see lily_sampler_read_phase_clocks */
+
 /*
  * src/kernels/sample.rs:130-143 SamplerScratch::new, for `max_rows` rows at
  * once. Allocates on `device`: the per-row candidate scratch, the parameter
@@ -148,6 +154,15 @@ int32_t lily_sampler_copy_counts(lily_sampler_t *dst, uint32_t dst_slot,
  * host-to-device copy of vocab words, stream-ordered then synchronised). */
 int32_t lily_sampler_read_counts(lily_sampler_t *h, void *stream, uint32_t slot, uint32_t *host_out);
 int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream, uint32_t slot, const uint32_t *host_in);
+
+/*
+ * With LILY_FLAG_PHASE_CLOCKS: copies the SM clock stamps of the last launch
+ * to host_out[max_rows][LILY_MAX_SLICES][LILY_PHASES] (int64 each, 0 where a
+ * block did not pass) and clears them; synchronises `stream`. Stamps, in
+ * order: start, history bitmap built, bias/ban ids done, vocabulary streamed,
+ * block's best k selected, slices merged, candidates sorted, draw done.
+ */
+int32_t lily_sampler_read_phase_clocks(lily_sampler_t *h, void *stream, int64_t *host_out);
 
 /* ------------------------------------------------------------------ draw -- */
 

@@ -23,6 +23,8 @@ K_CAP = 1024
 F32, BF16 = 0, 1
 SPEC_REJECTION, SPEC_GREEDY_MATCH = 0, 1
 FLAG_COUNTS_TABLE = 1
+FLAG_PHASE_CLOCKS = 2
+MAX_SLICES, PHASES = 128, 16
 
 OK = 0
 ERR_ARG, ERR_PARAMS, ERR_CAPACITY, ERR_FAULT, ERR_VOCAB = -1, -2, -3, -4, -5
@@ -162,6 +164,7 @@ def lib():
                                        C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32,
                                        C.c_uint32, C.c_uint32]
         L.lily_debug_exp.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]
+        L.lily_sampler_read_phase_clocks.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = L
     return _lib
 
@@ -236,7 +239,8 @@ class SamplerScratch:
     for up to `max_rows` rows per call."""
 
     def __init__(self, vocab: int, max_rows: int = 1, max_history: int = 1 << 16,
-                 max_list: int = 256, counts_table: bool = False, device: int | None = None):
+                 max_list: int = 256, counts_table: bool = False, device: int | None = None,
+                 phase_clocks: bool = False):
         import torch
 
         if device is None:
@@ -245,7 +249,8 @@ class SamplerScratch:
         self.device = device
         self.max_rows = max_rows
         st = lib().lily_sampler_create(device, vocab, max_rows, max_history, max_list,
-                                       FLAG_COUNTS_TABLE if counts_table else 0,
+                                       (FLAG_COUNTS_TABLE if counts_table else 0)
+                                       | (FLAG_PHASE_CLOCKS if phase_clocks else 0),
                                        C.byref(self._h))
         if st != OK:
             raise LilyError(st, "lily_sampler_create failed (is a CUDA device present?)")
@@ -305,6 +310,16 @@ class SamplerScratch:
         assert counts.size == self.vocab()
         self._check(lib().lily_sampler_write_counts(self._h, _stream_ptr(stream), slot,
                                                     counts.ctypes.data))
+
+    def read_phase_clocks(self, stream=None):
+        """SM clock stamps [max_rows, MAX_SLICES, PHASES] of the last launch
+        (needs phase_clocks=True); see lily_sampler_read_phase_clocks."""
+        import numpy as np
+
+        out = np.zeros((self.max_rows, MAX_SLICES, PHASES), dtype=np.int64)
+        self._check(lib().lily_sampler_read_phase_clocks(self._h, _stream_ptr(stream),
+                                                         out.ctypes.data))
+        return out
 
     # -- draws
     def sample_batch(self, logits, params, out_ids, *, uniforms=None, steps=None,

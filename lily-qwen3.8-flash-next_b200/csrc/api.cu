@@ -59,6 +59,7 @@ struct lily_sampler {
     int ring_pos = 0;
     uint32_t *h_status = nullptr;
     uint32_t attr_mask = 0;  // kernel variants whose shared-memory limit is raised
+    long long *phase_clocks = nullptr;
 };
 
 namespace {
@@ -206,6 +207,7 @@ void base_args(const lily_sampler *h, lily::KArgs *a) {
     a->part_n = h->part_n;
     a->tickets = h->tickets;
     a->status_word = h->status_word;
+    a->phase_clocks = h->phase_clocks;
 }
 
 int32_t ensure_counts_scratch(lily_sampler *h) {
@@ -344,6 +346,13 @@ int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
             return bail(e, "histogram slots");
         }
     }
+    if (flags & LILY_FLAG_PHASE_CLOCKS) {
+        const size_t pb = (size_t)max_rows * LILY_MAX_SLICES * LILY_PHASES * sizeof(long long);
+        if ((e = cudaMalloc(&h->phase_clocks, pb)) != cudaSuccess ||
+            (e = cudaMemset(h->phase_clocks, 0, pb)) != cudaSuccess) {
+            return bail(e, "phase clocks");
+        }
+    }
     for (int i = 0; i < RING; ++i) {
         if ((e = cudaMallocHost(&h->h_stage[i], h->layout.total)) != cudaSuccess ||
             (e = cudaMalloc(&h->d_stage[i], h->layout.total)) != cudaSuccess ||
@@ -371,6 +380,7 @@ void lily_sampler_destroy(lily_sampler_t *h) {
     cudaFree(h->counts_scratch);
     cudaFree(h->counts_table);
     cudaFree(h->seen_table);
+    cudaFree(h->phase_clocks);
     if (h->h_status) {
         cudaFreeHost(h->h_status);
     }
@@ -515,6 +525,19 @@ int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream_, uint32_t slo
     lily::rebuild_seen_kernel<<<blocks, threads, 0, stream>>>(
         counts, h->seen_table + (size_t)slot * h->seen_words, h->vocab);
     CU(h, cudaGetLastError());
+    CU(h, cudaStreamSynchronize(stream));
+    return LILY_OK;
+}
+
+int32_t lily_sampler_read_phase_clocks(lily_sampler_t *h, void *stream_, int64_t *host_out) {
+    if (h == nullptr || host_out == nullptr || h->phase_clocks == nullptr) {
+        return fail(h, LILY_ERR_ARG, "the sampler was not created with LILY_FLAG_PHASE_CLOCKS");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const size_t pb = (size_t)h->max_rows * LILY_MAX_SLICES * LILY_PHASES * sizeof(long long);
+    CU(h, cudaMemcpyAsync(host_out, h->phase_clocks, pb, cudaMemcpyDeviceToHost, stream));
+    CU(h, cudaMemsetAsync(h->phase_clocks, 0, pb, stream));
     CU(h, cudaStreamSynchronize(stream));
     return LILY_OK;
 }

@@ -39,7 +39,7 @@ constexpr uint32_t GROUP = 8;           // logits per thread per round
 constexpr uint32_t ROUND = NT * GROUP;  // logits per block per round
 constexpr uint32_t KCAP = LILY_K_CAP;
 constexpr uint32_t SP_SMEM = 256;       // bias + ban entries staged in shared memory
-constexpr uint32_t MAX_SLICES = 128;
+constexpr uint32_t MAX_SLICES = LILY_MAX_SLICES;
 
 // Row status bits OR-ed into the handle's status word.
 constexpr uint32_t ROW_INTERNAL = 8;  // candidate buffer overflow: a bug, never expected
@@ -94,32 +94,8 @@ struct KArgs {
     uint32_t *part_n;              // [max_rows, MAX_SLICES]
     uint32_t *tickets;             // [max_rows], zero between launches
     uint32_t *status_word;
+    long long *phase_clocks;       // optional [max_rows, MAX_SLICES, 8] SM clock stamps per phase
     SpecArgs spec;
-};
-
-struct SmemFixed {
-    uint32_t key[CAP];
-    uint32_t id[CAP];
-    uint32_t tkey[KCAP];  // select's staging; later the candidates' p
-    uint32_t tid[KCAP];   // select's staging; later the prefix sums
-    uint32_t hist[256];
-    uint32_t sp_ids[SP_SMEM];
-    float sp_vals[SP_SMEM];
-    uint32_t n;
-    uint32_t cnt;
-    uint32_t sel_digit;
-    uint32_t sel_before;
-    uint32_t sel_count;
-    uint32_t tau_key;
-    float c_raw;
-    uint32_t have_tau;
-    uint32_t err;
-    uint32_t is_last;
-    uint32_t n_keep;
-    uint32_t chosen;
-    float p_d;
-    float q_d;
-    uint32_t bloom[32];
 };
 
 struct RowCtx {
@@ -135,6 +111,35 @@ struct RowCtx {
     const uint32_t *ban_ids;
     uint32_t ban_len;
     bool sp_in_smem;
+};
+
+struct SmemFixed {
+    uint32_t key[CAP];
+    uint32_t id[CAP];
+    uint32_t tkey[KCAP];  // select's staging; later the candidates' p
+    uint32_t tid[KCAP];   // select's staging; later the prefix sums
+    uint32_t warp_sums[NT / 32];
+    uint32_t sel_min;
+    uint32_t sel_max;
+    uint32_t sp_ids[SP_SMEM];
+    float sp_vals[SP_SMEM];
+    uint32_t n;      // buffered candidates
+    uint32_t n_adj;  // the first n_adj hold adjusted keys, the rest raw logit bits
+    uint32_t cnt;
+    uint32_t sel_digit;
+    uint32_t sel_before;
+    uint32_t sel_count;
+    uint32_t tau_key;
+    float c_raw;
+    uint32_t have_tau;
+    uint32_t err;
+    uint32_t is_last;
+    uint32_t n_keep;
+    uint32_t chosen;
+    float p_d;
+    float q_d;
+    uint32_t bloom[32];
+    RowCtx ctx;  // the row's parameters, for the out-of-line slow path
 };
 
 __device__ __forceinline__ float neg_inf() { return __uint_as_float(0xFF800000u); }
@@ -189,10 +194,12 @@ __device__ __forceinline__ bool is_special(const SmemFixed *sm, const RowCtx &c,
     return false;
 }
 
-// Full adjustment of one logit and its push. `special`: the id is on the
-// bias / ban list (called from the up-front pass only).
-__device__ __forceinline__ void consider(SmemFixed *sm, const RowCtx &c, uint32_t id, float l,
-                                         bool special, bool have_tau, uint32_t tau_key) {
+// The adjusted key of logit `l` of id `id`: bias (list order), penalties,
+// ban, division by the temperature, monotone key. `special`: the id is on
+// the bias / ban list (the up-front pass only; the stream skips those ids).
+// A NaN marks the row as failed.
+__device__ __noinline__ uint32_t adjusted_key(SmemFixed *sm, uint32_t id, float l, bool special) {
+    const RowCtx &c = sm->ctx;
     float x = l;
     bool banned = false;
     if (special) {
@@ -206,8 +213,6 @@ __device__ __forceinline__ void consider(SmemFixed *sm, const RowCtx &c, uint32_
             const uint32_t e = c.sp_in_smem ? sm->sp_ids[c.bias_len + j] : c.ban_ids[j];
             banned = banned || e == id;
         }
-    } else if (c.has_special && is_special(sm, c, id)) {
-        return;  // handled up front
     }
     if (c.use_pen) {
         const uint32_t off = id - c.lo;
@@ -228,108 +233,185 @@ __device__ __forceinline__ void consider(SmemFixed *sm, const RowCtx &c, uint32_
         q = q != q ? neg_inf() : __fadd_rn(q, 0.0f);
     } else if (q != q) {
         sm->err = LILY_ROW_NAN;
-        return;
+        return 0u;
     }
-    const uint32_t key = key_of(q);
-    if (!have_tau || key > tau_key) {
-        push(sm, key, id);
-    }
+    return key_of(q);
 }
 
-// Warp 0 finds the histogram bin in which the running count (from the top
-// bin down when `descending`, else from bin 0 up) reaches `remaining`.
-__device__ __forceinline__ void find_digit(SmemFixed *sm, uint32_t remaining, bool descending) {
-    if (threadIdx.x < 32) {
-        const int lane = threadIdx.x;
-        uint32_t c[8];
-        uint32_t sum = 0;
+// The stream pushes raw logits; before a selection looks at the buffer, the
+// entries pushed since the last one, [n_adj, n), become adjusted keys, all
+// threads at once.
+__device__ __noinline__ void adjust_pending(SmemFixed *sm) {
+    const uint32_t n = min(sm->n, CAP);
+    const uint32_t from = sm->n_adj;
+    for (uint32_t i = from + threadIdx.x; i < n; i += NT) {
+        sm->key[i] = adjusted_key(sm, sm->id[i], __uint_as_float(sm->key[i]), false);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        sm->n_adj = n;
+    }
+    __syncthreads();
+}
+
+constexpr uint32_t SEL_BITS = 11;
+constexpr uint32_t SEL_BINS = 1u << SEL_BITS;  // the select's histogram aliases tkey + tid
+
+// All threads: finds the bin of hist[0, nbins) in which the running count,
+// taken from the top bin down when `descending` and from bin 0 up otherwise,
+// reaches `remaining`. Results in sm->sel_digit / sel_before / sel_count.
+__device__ __forceinline__ void find_bin(SmemFixed *sm, const uint32_t *hist, uint32_t nbins,
+                                         uint32_t remaining, bool descending) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    uint32_t c[4];
+    uint32_t sum = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int bin = lane * 8 + j;
-            bin = descending ? 255 - bin : bin;
-            c[j] = sm->hist[bin];
-            sum += c[j];
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t pos = tid * 4u + j;
+        uint32_t v = 0;
+        if (pos < nbins) {
+            v = hist[descending ? nbins - 1u - pos : pos];
         }
-        uint32_t incl = sum;
+        c[j] = v;
+        sum += v;
+    }
+    uint32_t incl = sum;
 #pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
-            if (lane >= off) {
-                incl += t;
-            }
-        }
-        const uint32_t excl = incl - sum;
-        if (excl < remaining && remaining <= incl) {
-            uint32_t cum = excl;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (cum + c[j] >= remaining) {
-                    int bin = lane * 8 + j;
-                    bin = descending ? 255 - bin : bin;
-                    sm->sel_digit = (uint32_t)bin;
-                    sm->sel_before = cum;
-                    sm->sel_count = c[j];
-                    break;
-                }
-                cum += c[j];
-            }
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+        if (lane >= (uint32_t)off) {
+            incl += t;
         }
     }
+    if (lane == 31u) {
+        sm->warp_sums[warp] = incl;
+    }
+    __syncthreads();
+    uint32_t before = 0;
+    for (uint32_t w = 0; w < warp; ++w) {
+        before += sm->warp_sums[w];
+    }
+    const uint32_t excl = before + incl - sum;
+    if (excl < remaining && remaining <= excl + sum) {
+        uint32_t cum = excl;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (cum + c[j] >= remaining) {
+                const uint32_t pos = tid * 4u + j;
+                sm->sel_digit = descending ? nbins - 1u - pos : pos;
+                sm->sel_before = cum;
+                sm->sel_count = c[j];
+                break;
+            }
+            cum += c[j];
+        }
+    }
+    __syncthreads();
+}
+
+// Range-adaptive radix select over the buffered candidates [0, n).
+//   BY_ID = false: the `remaining`-th largest key.
+//   BY_ID = true:  the `remaining`-th smallest id among entries whose key is kstar.
+// Every pass buckets the live value range [lo, hi] into at most 2048 bins
+// (so that candidates, whose float keys share their high bits, still spread
+// over the histogram), keeps the bin that holds the wanted rank and narrows
+// the range to it; three passes at most. Returns the value; *remaining_out
+// is the rank wanted inside that value's ties, *count_eq_out how many
+// entries hold the value.
+template <bool BY_ID>
+__device__ __noinline__ uint32_t adaptive_select(SmemFixed *sm, uint32_t n, uint32_t remaining, uint32_t kstar,
+                                    uint32_t *remaining_out, uint32_t *count_eq_out) {
+    const uint32_t tid = threadIdx.x;
+    uint32_t *hist = sm->tkey;  // SEL_BINS words: tkey and tid are adjacent
+    if (tid == 0) {
+        sm->sel_min = 0xFFFFFFFFu;
+        sm->sel_max = 0u;
+    }
+    __syncthreads();
+    uint32_t mn = 0xFFFFFFFFu, mx = 0u;
+    for (uint32_t i = tid; i < n; i += NT) {
+        if (!BY_ID || sm->key[i] == kstar) {
+            const uint32_t v = BY_ID ? sm->id[i] : sm->key[i];
+            mn = min(mn, v);
+            mx = max(mx, v);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        mn = min(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, off));
+        mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    }
+    if ((tid & 31u) == 0u) {
+        atomicMin(&sm->sel_min, mn);
+        atomicMax(&sm->sel_max, mx);
+    }
+    __syncthreads();
+    uint32_t lo = sm->sel_min, hi = sm->sel_max;
+    uint32_t count_eq = 0;
+    for (int pass = 0; pass < 4; ++pass) {
+        const uint32_t range = hi - lo;
+        const uint32_t bits = 32u - (uint32_t)__clz((int)range);  // 0 when range == 0
+        const uint32_t shift = bits > SEL_BITS ? bits - SEL_BITS : 0u;
+        const uint32_t nbins = (range >> shift) + 1u;
+        for (uint32_t b = tid; b < nbins; b += NT) {
+            hist[b] = 0;
+        }
+        __syncthreads();
+        for (uint32_t i0 = 0; i0 < n; i0 += NT) {
+            const uint32_t i = i0 + tid;
+            bool ok = i < n;
+            uint32_t bin = 0;
+            if (ok) {
+                ok = !BY_ID || sm->key[i] == kstar;
+                const uint32_t v = BY_ID ? sm->id[i] : sm->key[i];
+                ok = ok && v >= lo && v <= hi;
+                bin = (v - lo) >> shift;
+            }
+            // Candidates crowd into few bins: one atomic per distinct bin of the warp.
+            const unsigned live = __ballot_sync(0xFFFFFFFFu, ok);
+            if (ok) {
+                const unsigned peers = __match_any_sync(live, bin);
+                if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
+                    atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+                }
+            }
+        }
+        __syncthreads();
+        find_bin(sm, hist, nbins, remaining, !BY_ID);
+        remaining -= sm->sel_before;
+        count_eq = sm->sel_count;
+        const uint32_t new_lo = lo + (sm->sel_digit << shift);
+        const uint32_t width = shift == 0u ? 0u : (1u << shift) - 1u;
+        hi = min(hi, new_lo + width);
+        lo = new_lo;
+        __syncthreads();
+        if (shift == 0u) {
+            break;
+        }
+    }
+    *remaining_out = remaining;
+    *count_eq_out = count_eq;
+    return lo;
 }
 
 // Keeps the best k of the n buffered candidates (n > k), by key descending
 // then id ascending, in slots [0, k) in any order; records the k-th key.
-__device__ void select_topk(SmemFixed *sm, uint32_t n, uint32_t k) {
+__device__ __noinline__ void select_topk(SmemFixed *sm, uint32_t n, uint32_t k) {
     const uint32_t tid = threadIdx.x;
-    uint32_t prefix = 0, mask = 0, remaining = k, count_eq = 0;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        if (tid < 256) {
-            sm->hist[tid] = 0;
-        }
-        __syncthreads();
-        for (uint32_t i = tid; i < n; i += NT) {
-            const uint32_t key = sm->key[i];
-            if ((key & mask) == prefix) {
-                atomicAdd(&sm->hist[(key >> shift) & 255u], 1u);
-            }
-        }
-        __syncthreads();
-        find_digit(sm, remaining, true);
-        __syncthreads();
-        prefix |= sm->sel_digit << shift;
-        mask |= 255u << shift;
-        remaining -= sm->sel_before;
-        count_eq = sm->sel_count;
-    }
-    const uint32_t kstar = prefix;
+    uint32_t remaining = 0, count_eq = 0;
+    const uint32_t kstar = adaptive_select<false>(sm, n, k, 0u, &remaining, &count_eq);
     uint32_t istar = 0xFFFFFFFFu;
     if (count_eq > remaining) {
         // More candidates share the k-th key than fit: the lowest ids win.
-        uint32_t ip = 0, im = 0, rem = remaining;
-        for (int shift = 24; shift >= 0; shift -= 8) {
-            if (tid < 256) {
-                sm->hist[tid] = 0;
-            }
-            __syncthreads();
-            for (uint32_t i = tid; i < n; i += NT) {
-                const uint32_t id = sm->id[i];
-                if (sm->key[i] == kstar && (id & im) == ip) {
-                    atomicAdd(&sm->hist[(id >> shift) & 255u], 1u);
-                }
-            }
-            __syncthreads();
-            find_digit(sm, rem, false);
-            __syncthreads();
-            ip |= sm->sel_digit << shift;
-            im |= 255u << shift;
-            rem -= sm->sel_before;
-        }
-        istar = ip;
+        uint32_t r2 = 0, c2 = 0;
+        istar = adaptive_select<true>(sm, n, remaining, kstar, &r2, &c2);
     }
     if (tid == 0) {
         sm->cnt = 0;
     }
     __syncthreads();
+    // The survivors go to the front of the id array's upper half first (the
+    // histogram's storage doubles as staging and is free again by now).
     for (uint32_t i0 = 0; i0 < n; i0 += NT) {
         const uint32_t i = i0 + tid;
         if (i < n) {
@@ -362,6 +444,7 @@ __device__ void select_topk(SmemFixed *sm, uint32_t n, uint32_t k) {
             sm->err = ROW_INTERNAL;
         }
         sm->n = k;
+        sm->n_adj = k;
         sm->tau_key = kstar;
     }
     __syncthreads();
@@ -369,7 +452,7 @@ __device__ void select_topk(SmemFixed *sm, uint32_t n, uint32_t k) {
 
 // The largest raw logit c whose plain key does not beat kstar: an untouched
 // logit l beats the k-th candidate exactly when l > c. Thread 0 only.
-__device__ float raw_threshold(uint32_t kstar, float T, bool argmax_mode) {
+__device__ __noinline__ float raw_threshold(uint32_t kstar, float T, bool argmax_mode) {
     const float tq = float_of_key(kstar);
     if (tq != tq) {
         return tq;
@@ -398,21 +481,40 @@ __device__ float raw_threshold(uint32_t kstar, float T, bool argmax_mode) {
     return c;
 }
 
+// The steps after the selection run on k candidates. For k <= 64 (the
+// common case) one warp does them with warp barriers only; larger k uses the
+// whole block. `Team` abstracts the two.
+template <bool SMALL>
+struct Team {
+    static __device__ __forceinline__ uint32_t size() { return SMALL ? 32u : (uint32_t)NT; }
+    static __device__ __forceinline__ uint32_t rank() {
+        return SMALL ? (threadIdx.x & 31u) : threadIdx.x;
+    }
+    static __device__ __forceinline__ void sync() {
+        if (SMALL) {
+            __syncwarp();
+        } else {
+            __syncthreads();
+        }
+    }
+};
+
 // Bitonic sort of slots [0, n) by (key descending, id ascending).
-__device__ void sort_candidates(SmemFixed *sm, uint32_t n) {
-    const uint32_t tid = threadIdx.x;
+template <bool SMALL>
+__device__ __noinline__ void sort_candidates(SmemFixed *sm, uint32_t n) {
+    const uint32_t me = Team<SMALL>::rank(), team = Team<SMALL>::size();
     uint32_t P = 1;
     while (P < n) {
         P <<= 1;
     }
-    for (uint32_t i = n + tid; i < P; i += NT) {
+    for (uint32_t i = n + me; i < P; i += team) {
         sm->key[i] = 0u;
         sm->id[i] = 0xFFFFFFFFu;
     }
-    __syncthreads();
+    Team<SMALL>::sync();
     for (uint32_t size = 2; size <= P; size <<= 1) {
         for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-            for (uint32_t t = tid; t < (P >> 1); t += NT) {
+            for (uint32_t t = me; t < (P >> 1); t += team) {
                 const uint32_t i = ((t / stride) * stride << 1) + (t % stride);
                 const uint32_t j = i + stride;
                 const uint32_t ka = sm->key[i], kb = sm->key[j];
@@ -426,32 +528,35 @@ __device__ void sort_candidates(SmemFixed *sm, uint32_t n) {
                     sm->id[j] = ia;
                 }
             }
-            __syncthreads();
+            Team<SMALL>::sync();
         }
     }
 }
 
 // First slot of [0, n) whose prefix sum exceeds target, else the last slot
 // (tests/unit/kernels/sample.rs:48-52). Result in sm->chosen.
-__device__ void pick(SmemFixed *sm, const float *cum, uint32_t n, float target) {
-    const uint32_t tid = threadIdx.x;
-    if (tid == 0) {
+template <bool SMALL>
+__device__ __forceinline__ void pick(SmemFixed *sm, const float *cum, uint32_t n, float target) {
+    const uint32_t me = Team<SMALL>::rank(), team = Team<SMALL>::size();
+    if (me == 0) {
         sm->chosen = n - 1u;
     }
-    __syncthreads();
-    for (uint32_t i = tid; i < n; i += NT) {
+    Team<SMALL>::sync();
+    for (uint32_t i = me; i < n; i += team) {
         if (target < cum[i]) {
             atomicMin(&sm->chosen, i);
         }
     }
-    __syncthreads();
+    Team<SMALL>::sync();
 }
 
 // Steps 6-8 on the sorted candidates [0, n): softmax weights, sequential
 // prefix, cut, draw (plain or speculative), outputs.
-__device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_t row,
-                         uint32_t n, const lily_sampling_params_t &P) {
-    const uint32_t tid = threadIdx.x;
+template <bool SMALL>
+__device__ __noinline__ void finalize(SmemFixed *sm, const KArgs &a, uint32_t row, uint32_t n,
+                                      uint64_t seed) {
+    const RowCtx &c = sm->ctx;
+    const uint32_t me = Team<SMALL>::rank(), team = Team<SMALL>::size();
     const uint32_t out_row = row;
     float *p = reinterpret_cast<float *>(sm->tkey);
     float *cum = reinterpret_cast<float *>(sm->tid);
@@ -461,7 +566,7 @@ __device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_
         err = LILY_ROW_NONFINITE;
     }
     if (err != 0) {
-        if (tid == 0) {
+        if (me == 0) {
             a.out_ids[out_row] = 0xFFFFFFFFu;
             if (a.out_status) {
                 a.out_status[out_row] = err;
@@ -474,7 +579,7 @@ __device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_
         return;
     }
     if (c.argmax_mode) {
-        if (tid == 0) {
+        if (me == 0) {
             a.out_ids[out_row] = sm->id[0];
             if (a.out_status) {
                 a.out_status[out_row] = LILY_ROW_OK;
@@ -487,11 +592,20 @@ __device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_
         }
         return;
     }
-    for (uint32_t i = tid; i < n; i += NT) {
+    // The uniform is fetched early: its latency hides behind the prefix sums.
+    float u;
+    uint32_t step = 0;
+    if (a.uniforms) {
+        u = a.uniforms[row];
+    } else {
+        step = a.steps ? a.steps[row] : 0u;
+        u = uniform_for(seed, step);
+    }
+    for (uint32_t i = me; i < n; i += team) {
         p[i] = exp_f32(__fsub_rn(float_of_key(sm->key[i]), top));
     }
-    __syncthreads();
-    if (tid == 0) {
+    Team<SMALL>::sync();
+    if (me == 0) {
         float s = 0.0f;
         for (uint32_t i = 0; i < n; ++i) {
             s = __fadd_rn(s, p[i]);
@@ -499,31 +613,23 @@ __device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_
         }
         sm->n_keep = n;
     }
-    __syncthreads();
+    Team<SMALL>::sync();
     const float limit = __fmul_rn(c.top_p, cum[n - 1u]);
-    for (uint32_t i = tid + 1u; i < n; i += NT) {
+    for (uint32_t i = me + 1u; i < n; i += team) {
         if (!(cum[i - 1u] < limit && p[i] >= c.min_p)) {
             atomicMin(&sm->n_keep, i);
         }
     }
-    __syncthreads();
+    Team<SMALL>::sync();
     const uint32_t n_keep = sm->n_keep;
     const float mass = cum[n_keep - 1u];
 
-    float u;
-    uint32_t step = 0;
-    if (a.uniforms) {
-        u = a.uniforms[row];
-    } else {
-        step = a.steps ? a.steps[row] : 0u;
-        u = uniform_for(P.seed, step);
-    }
     if (a.kept_n) {
-        for (uint32_t i = tid; i < n_keep; i += NT) {
+        for (uint32_t i = me; i < n_keep; i += team) {
             a.kept_ids[(uint64_t)out_row * a.kept_ld + i] = sm->id[i];
             a.kept_probs[(uint64_t)out_row * a.kept_ld + i] = __fdiv_rn(p[i], mass);
         }
-        if (tid == 0) {
+        if (me == 0) {
             a.kept_n[out_row] = n_keep;
         }
     }
@@ -533,7 +639,7 @@ __device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_
         // Speculative draw against proposal `row` (tests/unit/kernels/
         // sample.rs:264-283; src/kernels/metal/sample.metal:597-658).
         const uint32_t d = a.spec.draft_ids[row];
-        if (tid == 0) {
+        if (me == 0) {
             sm->p_d = 0.0f;
             float qd = 0.0f;
             if (a.spec.q_dense) {
@@ -541,28 +647,28 @@ __device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_
             }
             sm->q_d = qd;
         }
-        __syncthreads();
+        Team<SMALL>::sync();
         const uint32_t qn = a.spec.q_dense ? 0u : min(a.spec.q_n[row], KCAP);
         const uint32_t *qi = a.spec.q_ids + (uint64_t)row * KCAP;
         const float *qp = a.spec.q_probs + (uint64_t)row * KCAP;
-        for (uint32_t i = tid; i < n_keep; i += NT) {
+        for (uint32_t i = me; i < n_keep; i += team) {
             if (sm->id[i] == d) {
                 sm->p_d = __fdiv_rn(p[i], mass);
             }
         }
-        for (uint32_t j = tid; j < qn; j += NT) {
+        for (uint32_t j = me; j < qn; j += team) {
             if (qi[j] == d) {
                 sm->q_d = qp[j];
             }
         }
-        __syncthreads();
+        Team<SMALL>::sync();
         if (__fmul_rn(u, sm->q_d) < sm->p_d) {
             chosen_id = d;
         } else {
             // Residual max(0, p - q) over the kept set, rank order.
             float *r = reinterpret_cast<float *>(sm->key + KCAP);
             float *rcum = reinterpret_cast<float *>(sm->id + KCAP);
-            for (uint32_t i = tid; i < n_keep; i += NT) {
+            for (uint32_t i = me; i < n_keep; i += team) {
                 const uint32_t id = sm->id[i];
                 float q = 0.0f;
                 if (a.spec.q_dense) {
@@ -578,34 +684,34 @@ __device__ void finalize(SmemFixed *sm, const KArgs &a, const RowCtx &c, uint32_
                 const float x = __fsub_rn(__fdiv_rn(p[i], mass), q);
                 r[i] = x > 0.0f ? x : 0.0f;
             }
-            __syncthreads();
-            if (tid == 0) {
+            Team<SMALL>::sync();
+            if (me == 0) {
                 float s = 0.0f;
                 for (uint32_t i = 0; i < n_keep; ++i) {
                     s = __fadd_rn(s, r[i]);
                     rcum[i] = s;
                 }
             }
-            __syncthreads();
+            Team<SMALL>::sync();
             const float r_total = rcum[n_keep - 1u];
             float u2;
             if (a.spec.u_resid) {
                 u2 = a.spec.u_resid[row];
             } else {
-                u2 = uniform_for(P.seed, step | 0x80000000u);
+                u2 = uniform_for(seed, step | 0x80000000u);
             }
             if (r_total > 0.0f) {
-                pick(sm, rcum, n_keep, __fmul_rn(u2, r_total));
+                pick<SMALL>(sm, rcum, n_keep, __fmul_rn(u2, r_total));
             } else {
-                pick(sm, cum, n_keep, __fmul_rn(u2, mass));
+                pick<SMALL>(sm, cum, n_keep, __fmul_rn(u2, mass));
             }
             chosen_id = sm->id[sm->chosen];
         }
     } else {
-        pick(sm, cum, n_keep, __fmul_rn(u, mass));
+        pick<SMALL>(sm, cum, n_keep, __fmul_rn(u, mass));
         chosen_id = sm->id[sm->chosen];
     }
-    if (tid == 0) {
+    if (me == 0) {
         a.out_ids[out_row] = chosen_id;
         if (a.out_status) {
             a.out_status[out_row] = LILY_ROW_OK;
@@ -710,6 +816,36 @@ __device__ __forceinline__ void load_frag(Frag<T> &f, const T *row, uint32_t bas
         }
     }
 }
+
+// The slow path of one thread's eight logits: those that pass the raw
+// threshold (or all of them) go into the buffer as raw bits; ids on the bias
+// / ban list were handled up front and are skipped. One copy, out of line,
+// so that the streaming loop stays small.
+template <typename T>
+__device__ __noinline__ void push_group(SmemFixed *sm, Frag<T> cur, uint32_t base,
+                                        uint32_t nvalid, bool all, float c_raw) {
+    const RowCtx &c = sm->ctx;
+#pragma unroll
+    for (int e = 0; e < (int)GROUP; ++e) {
+        const float l = frag_get<T>(cur, e);
+        if ((uint32_t)e < nvalid && (all || !(l <= c_raw))) {
+            if (!(c.has_special && is_special(sm, c, base + e))) {
+                push(sm, __float_as_uint(l), base + e);
+            }
+        }
+    }
+}
+
+// Phase stamps for the optional per-block timing trace.
+enum { PH_START = 0, PH_BITMAPS, PH_LISTS, PH_STREAM, PH_LOCAL_SELECT, PH_MERGE, PH_SORT, PH_END,
+       PH_ROUND0, PH_SELECT0, PH_THRESH0, PH_R1, PH_R4, PH_R8, PH_R16, PH_R32 };
+
+#define LILY_STAMP(phase)                                                               \
+    do {                                                                                \
+        if (a.phase_clocks != nullptr && threadIdx.x == 0) {                            \
+            a.phase_clocks[((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES + (phase)] = clock64(); \
+        }                                                                               \
+    } while (0)
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constant__ KArgs a) {
@@ -824,10 +960,21 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     const uint32_t extra_len = (c.use_pen && !table_mode) ? a.extra_len : 0u;
     const T *row_ptr = reinterpret_cast<const T *>(a.logits) + (uint64_t)row * a.logits_ld;
 
+    // The first rounds of logits start their way from HBM now, so that the
+    // history pass below overlaps with them.
+    constexpr int PF = sizeof(T) == 4 ? 3 : 4;
+    Frag<T> ring[PF];
+#pragma unroll
+    for (int d = 0; d < PF; ++d) {
+        load_frag<T, VEC>(ring[d], row_ptr, c.lo + (uint32_t)d * ROUND + tid * GROUP, c.hi);
+    }
+
     // ---- A. bitmaps
     const uint32_t slice_words = (c.hi - c.lo + 31u) >> 5;
     if (tid == 0) {
+        sm->ctx = c;
         sm->n = 0;
+        sm->n_adj = 0;
         sm->err = 0;
         sm->have_tau = 0;
         sm->tau_key = 0;
@@ -849,14 +996,42 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         }
     }
     __syncthreads();
+    LILY_STAMP(PH_START);
     if (hist_len + extra_len > 0u) {
-        for (uint32_t i = tid; i < hist_len + extra_len; i += NT) {
-            const uint32_t id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
-            if (id >= c.lo && id < c.hi) {
-                const uint32_t off = id - c.lo;
-                atomicOr(&seen[off >> 5], 1u << (off & 31u));
+        const uint32_t total = hist_len + extra_len;
+        constexpr int HB = 8;  // ids in flight per thread
+        for (uint32_t i0 = 0; i0 < total; i0 += NT * HB) {
+            uint32_t ids[HB];
+#pragma unroll
+            for (int j = 0; j < HB; ++j) {
+                const uint32_t i = i0 + (uint32_t)j * NT + tid;
+                ids[j] = 0xFFFFFFFFu;
+                if (i < total) {
+                    ids[j] = i < hist_len ? __ldg(hist + i) : a.extra_ids[i - hist_len];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < HB; ++j) {
+                const uint32_t id = ids[j];
+                const bool mine = id >= c.lo && id < c.hi;
+                if (mine) {
+                    // Real histories repeat a few ids very often: skip the
+                    // atomic when the bit is already up.
+                    const uint32_t off = id - c.lo;
+                    const uint32_t bit = 1u << (off & 31u);
+                    if (!(*reinterpret_cast<volatile uint32_t *>(&seen[off >> 5]) & bit)) {
+                        atomicOr(&seen[off >> 5], bit);
+                    }
+                }
                 if (c.need_counts) {
-                    atomicAdd(counts_rw + id, 1u);
+                    // One global atomic per distinct id of the warp.
+                    const unsigned live = __ballot_sync(0xFFFFFFFFu, mine);
+                    if (mine) {
+                        const unsigned peers = __match_any_sync(live, id);
+                        if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
+                            atomicAdd(counts_rw + id, (uint32_t)__popc(peers));
+                        }
+                    }
                 }
             }
         }
@@ -873,6 +1048,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         }
     }
     __syncthreads();
+    LILY_STAMP(PH_BITMAPS);
 
     // ---- B. ids on the bias / ban lists, each once
     if (c.has_special) {
@@ -890,25 +1066,25 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 first = other != id;
             }
             if (first) {
-                consider(sm, c, id, widen(row_ptr[id]), true, false, 0u);
+                const uint32_t key = adjusted_key(sm, id, widen(row_ptr[id]), true);
+                push(sm, key, id);
             }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            sm->n_adj = min(sm->n, CAP);
         }
         __syncthreads();
     }
 
+    LILY_STAMP(PH_LISTS);
     // ---- C. one streaming pass over the slice
-    constexpr int PF = sizeof(T) == 4 ? 3 : 4;
     const uint32_t span = c.hi - c.lo;
     const uint32_t nrounds = (span + ROUND - 1u) / ROUND;
     float c_raw = __uint_as_float(0x7FC00000u);  // NaN: nothing is rejected yet
     uint32_t tau_key = 0;
     bool have_tau = false;
     const bool group_check = c.use_pen && !c.monotone;
-    Frag<T> ring[PF];
-#pragma unroll
-    for (int d = 0; d < PF; ++d) {
-        load_frag<T, VEC>(ring[d], row_ptr, c.lo + (uint32_t)d * ROUND + tid * GROUP, c.hi);
-    }
     for (uint32_t r0 = 0; r0 < nrounds; r0 += PF) {
 #pragma unroll
         for (int d = 0; d < PF; ++d) {
@@ -925,38 +1101,56 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                         all = ((seen[off >> 5] >> (off & 31u)) & 0xFFu) != 0u;
                     }
                     if (all || !(frag_max(cur) <= c_raw)) {
-#pragma unroll
-                        for (int e = 0; e < (int)GROUP; ++e) {
-                            const float l = frag_get<T>(cur, e);
-                            if ((uint32_t)e < nvalid && (all || !(l <= c_raw))) {
-                                consider(sm, c, base + e, l, false, have_tau, tau_key);
-                            }
-                        }
+                        push_group<T>(sm, cur, base, nvalid, all, c_raw);
                     }
                 }
+                // Select when the next round could overflow the buffer, and
+                // once early, as soon as a first threshold can be had.
+                if (r == 0) LILY_STAMP(PH_ROUND0);
                 const uint32_t pending = *reinterpret_cast<volatile uint32_t *>(&sm->n);
-                if (__syncthreads_or(pending > CAP - ROUND)) {
+                const bool first = !have_tau && pending >= 2u * c.k && pending >= 1024u;
+                if (__syncthreads_or(pending > CAP - ROUND || first)) {
+                    adjust_pending(sm);
                     select_topk(sm, min(sm->n, CAP), c.k);
+                    if (r == 0) LILY_STAMP(PH_SELECT0);
                     if (tid == 0) {
                         sm->c_raw = raw_threshold(sm->tau_key, c.T, c.argmax_mode);
                         sm->have_tau = 1;
                     }
                     __syncthreads();
+                    if (r == 0) LILY_STAMP(PH_THRESH0);
                     c_raw = sm->c_raw;
                     tau_key = sm->tau_key;
                     have_tau = true;
                 }
+                if (r == 1) LILY_STAMP(PH_R1);
+                if (r == 4) LILY_STAMP(PH_R4);
+                if (r == 8) LILY_STAMP(PH_R8);
+                if (r == 16) LILY_STAMP(PH_R16);
+                if (r == 32) LILY_STAMP(PH_R32);
             }
         }
     }
     __syncthreads();
 
+    LILY_STAMP(PH_STREAM);
+    adjust_pending(sm);  // reads the count table: before it is cleared
     // The count table goes back to all zero (history-list mode only).
     if (c.need_counts && !table_mode) {
-        for (uint32_t i = tid; i < hist_len + extra_len; i += NT) {
-            const uint32_t id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
-            if (id >= c.lo && id < c.hi) {
-                atomicSub(counts_rw + id, 1u);
+        const uint32_t total = hist_len + extra_len;
+        for (uint32_t i0 = 0; i0 < total; i0 += NT) {
+            const uint32_t i = i0 + tid;
+            uint32_t id = 0xFFFFFFFFu;
+            if (i < total) {
+                id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
+            }
+            const bool mine = id >= c.lo && id < c.hi;
+            const unsigned live = __ballot_sync(0xFFFFFFFFu, mine);
+            if (mine) {
+                const unsigned peers = __match_any_sync(live, id);
+                if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
+                    atomicSub(counts_rw + id, (uint32_t)__popc(peers));
+                }
             }
         }
     }
@@ -967,6 +1161,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         select_topk(sm, n, c.k);
         n = c.k;
     }
+    LILY_STAMP(PH_LOCAL_SELECT);
 
     // ---- D. merge the slices
     if (n_slices > 1u) {
@@ -988,31 +1183,47 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             return;
         }
         __threadfence();
-        uint32_t total = 0;
-        uint32_t err = 0;
-        for (uint32_t s = 0; s < n_slices; ++s) {
-            const uint32_t word = __ldcg(a.part_n + row * MAX_SLICES + s);
-            const uint32_t cnt = word & 0xFFFFFFu;
-            err |= word >> 24;
-            const uint2 *src = a.part + (uint64_t)row * CAP + s * c.k;
-            for (uint32_t i = tid; i < cnt; i += NT) {
-                if (total + i < CAP) {
-                    const uint2 e = __ldcg(src + i);
-                    sm->key[total + i] = e.x;
-                    sm->id[total + i] = e.y;
-                }
+        // Every slice's count at once, a prefix over them, then one parallel
+        // gather of all entries.
+        uint32_t *offs = sm->tkey;  // n_slices + 1 offsets
+        if (tid < n_slices) {
+            const uint32_t word = __ldcg(a.part_n + row * MAX_SLICES + tid);
+            offs[tid + 1u] = word & 0xFFFFFFu;
+            if (word >> 24) {
+                sm->err = word >> 24;
             }
-            total += cnt;
         }
+        __syncthreads();
         if (tid == 0) {
-            a.tickets[row] = 0;
-            sm->n = min(total, CAP);
-            if (err) {
-                sm->err = err & (err - 1u) ? LILY_ROW_NAN : err;
+            uint32_t run = 0;
+            offs[0] = 0;
+            for (uint32_t s = 0; s < n_slices; ++s) {
+                run += offs[s + 1u];
+                offs[s + 1u] = run;
             }
-            if (total > CAP) {
+            a.tickets[row] = 0;
+            sm->n = min(run, CAP);
+            sm->n_adj = min(run, CAP);
+            if (run > CAP) {
                 sm->err = ROW_INTERNAL;
             }
+        }
+        __syncthreads();
+        const uint32_t total = sm->n;
+        for (uint32_t i = tid; i < total; i += NT) {
+            // The slice of entry i: the last offset not above i.
+            uint32_t lo_s = 0, hi_s = n_slices;
+            while (hi_s - lo_s > 1u) {
+                const uint32_t mid = (lo_s + hi_s) >> 1;
+                if (offs[mid] <= i) {
+                    lo_s = mid;
+                } else {
+                    hi_s = mid;
+                }
+            }
+            const uint2 e = __ldcg(a.part + (uint64_t)row * CAP + lo_s * c.k + (i - offs[lo_s]));
+            sm->key[i] = e.x;
+            sm->id[i] = e.y;
         }
         __syncthreads();
         n = sm->n;
@@ -1036,8 +1247,21 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         }
         return;
     }
-    sort_candidates(sm, n);
-    finalize(sm, a, c, row, n, P);
+    LILY_STAMP(PH_MERGE);
+    if (n <= 64u) {
+        // One warp finishes the row; the others are done.
+        if (tid < 32u) {
+            sort_candidates<true>(sm, n);
+            LILY_STAMP(PH_SORT);
+            finalize<true>(sm, a, row, n, P.seed);
+            LILY_STAMP(PH_END);
+        }
+    } else {
+        sort_candidates<false>(sm, n);
+        LILY_STAMP(PH_SORT);
+        finalize<false>(sm, a, row, n, P.seed);
+        LILY_STAMP(PH_END);
+    }
 }
 
 // src/kernels/metal/spec.metal:14-38, one thread.
