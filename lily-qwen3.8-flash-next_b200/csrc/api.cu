@@ -143,7 +143,7 @@ size_t smem_bytes(uint32_t vocab, uint32_t n_slices) {
     const uint32_t want = n_slices < lily::CAP / lily::KCAP ? n_slices : lily::CAP / lily::KCAP;
     const uint32_t slice_len = (((vocab + want - 1u) / want) + 255u) & ~255u;
     const size_t words = (slice_len + 31u) / 32u + 8u;
-    return sizeof(lily::SmemFixed) + words * sizeof(uint32_t);
+    return sizeof(lily::SmemFixed) + lily::RING_BYTES + words * sizeof(uint32_t);
 }
 
 template <typename T, bool VEC>
@@ -279,7 +279,7 @@ uint32_t lily_residual_step(uint32_t step) { return step | 0x80000000u; }
 int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
                             uint32_t max_history, uint32_t max_list, uint32_t flags,
                             lily_sampler_t **out) {
-    if (out == nullptr || vocab == 0u || max_rows == 0u || max_list > 1024u ||
+    if (out == nullptr || vocab == 0u || max_rows == 0u || max_list > 512u ||
         vocab > (1u << 24)) {
         return LILY_ERR_ARG;
     }

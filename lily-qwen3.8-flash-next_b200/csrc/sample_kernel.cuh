@@ -8,21 +8,24 @@
 //      scratch that the block clears again before it exits);
 //   B. the few ids with a logit bias or a ban are adjusted one by one and
 //      put into the candidate buffer up front;
-//   C. the slice streams through registers in rounds of 4096 logits,
-//      16-byte loads, several rounds in flight. A logit is looked at only
-//      if it beats a threshold that is exact in the raw (unscaled) domain:
-//      the largest float c whose scaled value still does not beat the
-//      k-th best candidate so far. Survivors are penalised, scaled and
-//      pushed as (monotone key, id) pairs into a shared-memory buffer; when
-//      the buffer could overflow in the next round, a radix select keeps
-//      the best k and raises the threshold;
-//   D. the block's best k go to global scratch; the last block of the row
-//      to arrive (an atomic ticket, nobody waits) merges the slices,
-//      sorts the k survivors by (value descending, id ascending) and runs
-//      the softmax prefix / top-p / min-p cut / draw exactly in the order
-//      the reference's CPU sampler does (tests/unit/kernels/sample.rs:8-54).
+//   C. the slice streams through a shared-memory ring filled by cp.async
+//      (16 bytes per thread per round of 4096 logits, several rounds in
+//      flight). A logit is looked at only if it beats a threshold that is
+//      exact in the raw (unscaled) domain: the largest float c whose scaled
+//      value does not beat a key that at least k untouched logits seen so
+//      far reach. The first threshold comes from a fine histogram of the
+//      first round; it is tightened from a small histogram of the keys
+//      pushed since. Survivors go into the candidate buffer as raw bits;
+//   D. the buffered candidates are adjusted all at once (bias and bans were
+//      done in B; here the penalties, the division by the temperature and
+//      the monotone key), the best k are selected exactly by (key
+//      descending, id ascending), and go to global scratch; the last block
+//      of the row to arrive (an atomic ticket, nobody waits) merges the
+//      slices, sorts the k survivors and runs the softmax prefix / top-p /
+//      min-p cut / draw exactly in the order the reference's CPU sampler
+//      does (tests/unit/kernels/sample.rs:8-54).
 //
-// With one slice per row (large batches) step D happens in the same block.
+// With one slice per row (large batches) step D ends in the same block.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -34,12 +37,17 @@
 namespace lily {
 
 constexpr int NT = 512;                 // threads per block
-constexpr uint32_t CAP = 8192;          // candidate buffer entries
 constexpr uint32_t GROUP = 8;           // logits per thread per round
 constexpr uint32_t ROUND = NT * GROUP;  // logits per block per round
 constexpr uint32_t KCAP = LILY_K_CAP;
+constexpr uint32_t CAP = ROUND + KCAP;  // candidate buffer entries
+constexpr uint32_t RING_BYTES = 32768;  // cp.async ring: 4 rounds of bf16, 2 of f32
 constexpr uint32_t SP_SMEM = 256;       // bias + ban entries staged in shared memory
 constexpr uint32_t MAX_SLICES = LILY_MAX_SLICES;
+constexpr uint32_t H0_SHIFT = 19;       // first-round histogram: key >> 19, 8192 bins
+constexpr uint32_t H0_BINS = 1u << (32 - H0_SHIFT);
+constexpr uint32_t TH_BINS = 1024;      // tightening histogram: key >> 16 above a base
+constexpr uint32_t RANKSORT_MAX = 384;  // candidate counts up to this are rank-sorted
 
 // Row status bits OR-ed into the handle's status word.
 constexpr uint32_t ROW_INTERNAL = 8;  // candidate buffer overflow: a bug, never expected
@@ -52,7 +60,7 @@ struct SpecArgs {
     const float *q_probs;
     const uint32_t *q_n;
     const float *u_resid;       // [n_spec] or null (then from seed/step)
-    uint32_t n_spec;            // rows [row0, row0 + ...) below this index draw speculatively
+    uint32_t n_spec;            // rows below this index draw speculatively
 };
 
 struct KArgs {
@@ -94,7 +102,7 @@ struct KArgs {
     uint32_t *part_n;              // [max_rows, MAX_SLICES]
     uint32_t *tickets;             // [max_rows], zero between launches
     uint32_t *status_word;
-    long long *phase_clocks;       // optional [max_rows, MAX_SLICES, 8] SM clock stamps per phase
+    long long *phase_clocks;       // optional [max_rows, MAX_SLICES, LILY_PHASES] SM clock stamps
     SpecArgs spec;
 };
 
@@ -113,14 +121,13 @@ struct RowCtx {
     bool sp_in_smem;
 };
 
-struct SmemFixed {
-    uint32_t key[CAP];
-    uint32_t id[CAP];
-    uint32_t tkey[KCAP];  // select's staging; later the candidates' p
-    uint32_t tid[KCAP];   // select's staging; later the prefix sums
+struct alignas(16) SmemFixed {
+    uint32_t key[CAP];    // candidates: adjusted keys below n_adj, raw logit bits above;
+    uint32_t id[CAP];     //   during the first round key+id hold the 8192-bin histogram
+    uint32_t tkey[KCAP];  // select's histogram / staging; later the candidates' p
+    uint32_t tid[KCAP];   // select's histogram / staging; later the prefix sums
+    uint32_t thist[TH_BINS];
     uint32_t warp_sums[NT / 32];
-    uint32_t sel_min;
-    uint32_t sel_max;
     uint32_t sp_ids[SP_SMEM];
     float sp_vals[SP_SMEM];
     uint32_t n;      // buffered candidates
@@ -129,9 +136,14 @@ struct SmemFixed {
     uint32_t sel_digit;
     uint32_t sel_before;
     uint32_t sel_count;
-    uint32_t tau_key;
-    float c_raw;
-    uint32_t have_tau;
+    uint32_t sel_min;
+    uint32_t sel_max;
+    uint32_t tau_key;   // exact k-th key of the last selection
+    uint32_t kstar;     // a logit is looked at iff its plain key is above this
+    float c_raw;        // ... iff it is above this (NaN: no threshold yet)
+    uint32_t th_base;   // key >> 16 of the tightening histogram's bin 0
+    uint32_t th_new;    // pushes counted since the threshold was last tightened
+    uint32_t overflow;  // a push found the buffer full
     uint32_t err;
     uint32_t is_last;
     uint32_t n_keep;
@@ -139,13 +151,18 @@ struct SmemFixed {
     float p_d;
     float q_d;
     uint32_t bloom[32];
-    RowCtx ctx;  // the row's parameters, for the out-of-line slow path
+    RowCtx ctx;  // the row's parameters, for the out-of-line helpers
 };
+
+static_assert(sizeof(uint32_t) * 2 * CAP >= sizeof(uint32_t) * H0_BINS,
+              "the first-round histogram aliases the candidate buffer");
 
 __device__ __forceinline__ float neg_inf() { return __uint_as_float(0xFF800000u); }
 
-// Warp-aggregated append to the candidate buffer.
-__device__ __forceinline__ void push(SmemFixed *sm, uint32_t key, uint32_t id) {
+// Warp-aggregated append to the candidate buffer. A full buffer refuses the
+// entry and raises the overflow flag; the caller remembers the element and
+// offers it again after the next selection has made room.
+__device__ __forceinline__ bool push(SmemFixed *sm, uint32_t key, uint32_t id) {
     const unsigned act = __activemask();
     const int lane = threadIdx.x & 31;
     const int leader = __ffs(act) - 1;
@@ -158,9 +175,10 @@ __device__ __forceinline__ void push(SmemFixed *sm, uint32_t key, uint32_t id) {
     if (slot < CAP) {
         sm->key[slot] = key;
         sm->id[slot] = id;
-    } else {
-        sm->err = ROW_INTERNAL;
+        return true;
     }
+    sm->overflow = 1;
+    return false;
 }
 
 // The key of a logit that neither history nor bias nor ban touches.
@@ -172,6 +190,11 @@ __device__ __forceinline__ uint32_t plain_key(float l, float T, bool argmax_mode
         q = q != q ? neg_inf() : __fadd_rn(q, 0.0f);
     }
     return key_of(q);
+}
+
+__device__ __forceinline__ bool seen_bit(const RowCtx &c, uint32_t id) {
+    const uint32_t off = id - c.lo;
+    return (c.seen[off >> 5] >> (off & 31u)) & 1u;
 }
 
 // Whether `id` is on the row's bias or ban list.
@@ -214,16 +237,13 @@ __device__ __noinline__ uint32_t adjusted_key(SmemFixed *sm, uint32_t id, float 
             banned = banned || e == id;
         }
     }
-    if (c.use_pen) {
-        const uint32_t off = id - c.lo;
-        if ((c.seen[off >> 5] >> (off & 31u)) & 1u) {
-            float cnt = 1.0f;
-            if (c.need_counts) {
-                cnt = (float)__ldcg(c.counts + id);
-            }
-            x = x > 0.0f ? __fdiv_rn(x, c.rep) : __fmul_rn(x, c.rep);
-            x = __fsub_rn(x, __fadd_rn(c.presence, __fmul_rn(c.frequency, cnt)));
+    if (c.use_pen && seen_bit(c, id)) {
+        float cnt = 1.0f;
+        if (c.need_counts) {
+            cnt = (float)__ldcg(c.counts + id);
         }
+        x = x > 0.0f ? __fdiv_rn(x, c.rep) : __fmul_rn(x, c.rep);
+        x = __fsub_rn(x, __fadd_rn(c.presence, __fmul_rn(c.frequency, cnt)));
     }
     if (banned) {
         x = neg_inf();
@@ -257,17 +277,18 @@ __device__ __noinline__ void adjust_pending(SmemFixed *sm) {
 constexpr uint32_t SEL_BITS = 11;
 constexpr uint32_t SEL_BINS = 1u << SEL_BITS;  // the select's histogram aliases tkey + tid
 
-// All threads: finds the bin of hist[0, nbins) in which the running count,
+// All threads: finds the bin of hist[0, nbins), nbins <= BPT * 512, in which the running count,
 // taken from the top bin down when `descending` and from bin 0 up otherwise,
 // reaches `remaining`. Results in sm->sel_digit / sel_before / sel_count.
+template <int BPT>
 __device__ __forceinline__ void find_bin(SmemFixed *sm, const uint32_t *hist, uint32_t nbins,
                                          uint32_t remaining, bool descending) {
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    uint32_t c[4];
+    uint32_t c[BPT];
     uint32_t sum = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t pos = tid * 4u + j;
+    for (int j = 0; j < BPT; ++j) {
+        const uint32_t pos = tid * (uint32_t)BPT + j;
         uint32_t v = 0;
         if (pos < nbins) {
             v = hist[descending ? nbins - 1u - pos : pos];
@@ -295,9 +316,9 @@ __device__ __forceinline__ void find_bin(SmemFixed *sm, const uint32_t *hist, ui
     if (excl < remaining && remaining <= excl + sum) {
         uint32_t cum = excl;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < BPT; ++j) {
             if (cum + c[j] >= remaining) {
-                const uint32_t pos = tid * 4u + j;
+                const uint32_t pos = tid * (uint32_t)BPT + j;
                 sm->sel_digit = descending ? nbins - 1u - pos : pos;
                 sm->sel_before = cum;
                 sm->sel_count = c[j];
@@ -377,7 +398,7 @@ __device__ __noinline__ uint32_t adaptive_select(SmemFixed *sm, uint32_t n, uint
             }
         }
         __syncthreads();
-        find_bin(sm, hist, nbins, remaining, !BY_ID);
+        find_bin<SEL_BINS / NT>(sm, hist, nbins, remaining, !BY_ID);
         remaining -= sm->sel_before;
         count_eq = sm->sel_count;
         const uint32_t new_lo = lo + (sm->sel_digit << shift);
@@ -728,6 +749,100 @@ __device__ __noinline__ void finalize(SmemFixed *sm, const KArgs &a, uint32_t ro
     }
 }
 
+
+// Sets the threshold to `kstar` (thread 0): logits whose plain key is at or
+// below it are not looked at any more.
+__device__ __forceinline__ void set_threshold(SmemFixed *sm, uint32_t kstar) {
+    const RowCtx &c = sm->ctx;
+    if (kstar > sm->kstar) {
+        sm->kstar = kstar;
+        sm->c_raw = raw_threshold(kstar, c.T, c.argmax_mode);
+    }
+}
+
+// One warp tightens the threshold from the histogram of the keys pushed so
+// far: the highest bin edge that at least k counted (untouched) logits reach.
+__device__ __noinline__ void tighten(SmemFixed *sm) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t k = sm->ctx.k;
+    // Lane l owns bins [32 l, 32 l + 32), scanned from the top bin down.
+    uint32_t sum = 0;
+    for (uint32_t j = 0; j < TH_BINS / 32u; ++j) {
+        sum += sm->thist[TH_BINS - 1u - (lane * (TH_BINS / 32u) + j)];
+    }
+    uint32_t incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+        if (lane >= (uint32_t)off) {
+            incl += t;
+        }
+    }
+    const uint32_t excl = incl - sum;
+    if (excl < k && k <= incl) {
+        uint32_t cum = excl;
+        for (uint32_t j = 0; j < TH_BINS / 32u; ++j) {
+            const uint32_t bin = TH_BINS - 1u - (lane * (TH_BINS / 32u) + j);
+            cum += sm->thist[bin];
+            if (cum >= k) {
+                // At least k counted logits have a key of (base + bin) << 16
+                // or more: nothing below that can be among the best k.
+                const uint32_t edge = (sm->th_base + bin) << 16;
+                if (edge > 0u) {
+                    set_threshold(sm, edge - 1u);
+                }
+                break;
+            }
+        }
+    }
+    if (lane == 0) {
+        sm->th_new = 0;
+    }
+}
+
+// Exact best-k of n <= RANKSORT_MAX buffered candidates by counting, for
+// each, how many others come before it: the best k land sorted in [0, k).
+__device__ __noinline__ void rank_sort(SmemFixed *sm, uint32_t n, uint32_t k) {
+    const uint32_t tid = threadIdx.x;
+    uint32_t rank = 0xFFFFFFFFu, mk = 0, mi = 0;
+    if (tid < n) {
+        mk = sm->key[tid];
+        mi = sm->id[tid];
+        rank = 0;
+        for (uint32_t j = 0; j < n; ++j) {
+            const uint32_t kj = sm->key[j], ij = sm->id[j];
+            rank += (kj > mk || (kj == mk && ij < mi)) ? 1u : 0u;
+        }
+    }
+    __syncthreads();
+    if (rank < k) {
+        sm->key[rank] = mk;
+        sm->id[rank] = mi;
+    }
+    if (tid == 0) {
+        sm->n = min(n, k);
+        sm->n_adj = min(n, k);
+    }
+    __syncthreads();
+}
+
+// cp.async: 16 bytes global -> shared, `bytes` of them read, the rest zero.
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gsrc, uint32_t bytes) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gsrc),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
 template <typename T>
 struct Frag;
 
@@ -777,25 +892,15 @@ __device__ __forceinline__ float frag_max(const Frag<__nv_bfloat16> &f) {
 __device__ __forceinline__ float widen(float x) { return x; }
 __device__ __forceinline__ float widen(__nv_bfloat16 x) { return __bfloat162float(x); }
 
-// Loads the eight logits [base, base + 8) of a row; slots at or past `hi`
-// read as zero and are never looked at.
-template <typename T, bool VEC>
-__device__ __forceinline__ void load_frag(Frag<T> &f, const T *row, uint32_t base, uint32_t hi) {
+// Scalar fallback for rows that are not 16-byte aligned: the eight logits
+// [base, base + 8), slots at or past `hi` zero.
+template <typename T>
+__device__ __forceinline__ void load_frag_scalar(Frag<T> &f, const T *row, uint32_t base,
+                                                 uint32_t hi) {
     constexpr int NV = sizeof(Frag<T>) / 16;
-    if (VEC && base + GROUP <= hi) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(row + base);
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            f.v[i] = __ldcs(src + i);
-        }
-        return;
-    }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         f.v[i] = make_uint4(0, 0, 0, 0);
-    }
-    if (base >= hi) {
-        return;
     }
     uint32_t *words = reinterpret_cast<uint32_t *>(&f);
     if (sizeof(T) == 4) {
@@ -817,41 +922,83 @@ __device__ __forceinline__ void load_frag(Frag<T> &f, const T *row, uint32_t bas
     }
 }
 
-// The slow path of one thread's eight logits: those that pass the raw
-// threshold (or all of them) go into the buffer as raw bits; ids on the bias
-// / ban list were handled up front and are skipped. One copy, out of line,
-// so that the streaming loop stays small.
+// One thread's eight logits of a round: those in `mask` that beat the raw
+// threshold (or, when penalties may raise a logit, are in the history) go
+// into the buffer as raw bits; ids on the bias / ban list were handled up
+// front and are skipped. Untouched logits also count in the tightening
+// histogram. Returns the mask of elements the full buffer refused.
 template <typename T>
-__device__ __noinline__ void push_group(SmemFixed *sm, Frag<T> cur, uint32_t base,
-                                        uint32_t nvalid, bool all, float c_raw) {
-    const RowCtx &c = sm->ctx;
+__device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c,
+                                                 const Frag<T> &cur, uint32_t base, uint32_t mask,
+                                                 float c_raw, bool always_seen) {
+    uint32_t failed = 0;
 #pragma unroll
     for (int e = 0; e < (int)GROUP; ++e) {
-        const float l = frag_get<T>(cur, e);
-        if ((uint32_t)e < nvalid && (all || !(l <= c_raw))) {
-            if (!(c.has_special && is_special(sm, c, base + e))) {
-                push(sm, __float_as_uint(l), base + e);
+        if ((mask >> e) & 1u) {
+            const float l = frag_get<T>(cur, e);
+            const uint32_t id = base + e;
+            const bool pass = !(l <= c_raw);
+            bool seen_here = false;
+            if (c.use_pen && (pass || always_seen)) {
+                seen_here = seen_bit(c, id);
+            }
+            if (pass || (always_seen && seen_here)) {
+                if (!(c.has_special && is_special(sm, c, id))) {
+                    if (push(sm, __float_as_uint(l), id)) {
+                        if (!seen_here) {
+                            const uint32_t k16 = plain_key(l, c.T, c.argmax_mode) >> 16;
+                            const uint32_t b16 = sm->th_base;
+                            if (k16 >= b16) {
+                                atomicAdd(&sm->thist[min(k16 - b16, TH_BINS - 1u)], 1u);
+                                sm->th_new = 1;
+                            }
+                        }
+                    } else {
+                        failed |= 1u << e;
+                    }
+                }
             }
         }
     }
+    return failed;
+}
+
+// Block-wide: adjusts what the stream pushed, keeps the exact best k and
+// raises the threshold to the k-th key.
+__device__ __noinline__ void compact(SmemFixed *sm) {
+    adjust_pending(sm);
+    const uint32_t n = min(sm->n, CAP);
+    const uint32_t k = sm->ctx.k;
+    if (n > k) {
+        select_topk(sm, n, k);
+        if (threadIdx.x == 0) {
+            set_threshold(sm, sm->tau_key);
+        }
+    }
+    if (threadIdx.x == 0) {
+        sm->overflow = 0;
+    }
+    __syncthreads();
 }
 
 // Phase stamps for the optional per-block timing trace.
 enum { PH_START = 0, PH_BITMAPS, PH_LISTS, PH_STREAM, PH_LOCAL_SELECT, PH_MERGE, PH_SORT, PH_END,
        PH_ROUND0, PH_SELECT0, PH_THRESH0, PH_R1, PH_R4, PH_R8, PH_R16, PH_R32 };
 
-#define LILY_STAMP(phase)                                                               \
-    do {                                                                                \
-        if (a.phase_clocks != nullptr && threadIdx.x == 0) {                            \
-            a.phase_clocks[((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES + (phase)] = clock64(); \
-        }                                                                               \
+#define LILY_STAMP(phase)                                                                  \
+    do {                                                                                   \
+        if (a.phase_clocks != nullptr && threadIdx.x == 0) {                               \
+            a.phase_clocks[((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES + (phase)] = \
+                clock64();                                                                 \
+        }                                                                                  \
     } while (0)
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constant__ KArgs a) {
     extern __shared__ uint4 smem_raw[];
     SmemFixed *sm = reinterpret_cast<SmemFixed *>(smem_raw);
-    uint32_t *seen = reinterpret_cast<uint32_t *>(sm + 1);
+    uint4 *ring = reinterpret_cast<uint4 *>(sm + 1);
+    uint32_t *seen = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(ring) + RING_BYTES);
 
     const uint32_t tid = threadIdx.x;
     const uint32_t row = a.row0 + blockIdx.y;  // every per-row array is indexed by this
@@ -960,13 +1107,30 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     const uint32_t extra_len = (c.use_pen && !table_mode) ? a.extra_len : 0u;
     const T *row_ptr = reinterpret_cast<const T *>(a.logits) + (uint64_t)row * a.logits_ld;
 
-    // The first rounds of logits start their way from HBM now, so that the
-    // history pass below overlaps with them.
-    constexpr int PF = sizeof(T) == 4 ? 3 : 4;
-    Frag<T> ring[PF];
+    // The ring: STAGES rounds of this block's logits in flight, each thread
+    // copying (and later reading back) its own 16-byte pieces.
+    constexpr int NV = sizeof(Frag<T>) / 16;                       // 16-byte pieces per thread-round
+    constexpr int STAGES = RING_BYTES / (NT * 16 * NV);            // 4 for bf16, 2 for f32
+    const uint32_t span = c.hi - c.lo;
+    const uint32_t nrounds = (span + ROUND - 1u) / ROUND;
+    auto issue = [&](uint32_t r) {
+        if (VEC && r < nrounds) {
+            const uint32_t base = c.lo + r * ROUND + tid * GROUP;
+            const uint32_t left = base < c.hi ? (c.hi - base) * (uint32_t)sizeof(T) : 0u;
 #pragma unroll
-    for (int d = 0; d < PF; ++d) {
-        load_frag<T, VEC>(ring[d], row_ptr, c.lo + (uint32_t)d * ROUND + tid * GROUP, c.hi);
+            for (int i = 0; i < NV; ++i) {
+                const uint32_t off = 16u * i;
+                const uint32_t bytes = left > off ? min(16u, left - off) : 0u;
+                const char *src = bytes ? reinterpret_cast<const char *>(row_ptr + base) + off
+                                        : reinterpret_cast<const char *>(row_ptr);
+                cp_async_16(&ring[((r % STAGES) * NT + tid) * NV + i], src, bytes);
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        issue((uint32_t)s);
     }
 
     // ---- A. bitmaps
@@ -976,12 +1140,18 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         sm->n = 0;
         sm->n_adj = 0;
         sm->err = 0;
-        sm->have_tau = 0;
         sm->tau_key = 0;
+        sm->kstar = 0;
         sm->c_raw = __uint_as_float(0x7FC00000u);
+        sm->th_base = 0;
+        sm->th_new = 0;
+        sm->overflow = 0;
     }
     if (tid < 32) {
         sm->bloom[tid] = 0;
+    }
+    for (uint32_t b = tid; b < TH_BINS; b += NT) {
+        sm->thist[b] = 0;
     }
     if (c.use_pen) {
         if (table_mode) {
@@ -999,7 +1169,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     LILY_STAMP(PH_START);
     if (hist_len + extra_len > 0u) {
         const uint32_t total = hist_len + extra_len;
-        constexpr int HB = 8;  // ids in flight per thread
+        constexpr int HB = 16;  // ids in flight per thread
         for (uint32_t i0 = 0; i0 < total; i0 += NT * HB) {
             uint32_t ids[HB];
 #pragma unroll
@@ -1050,7 +1220,69 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     __syncthreads();
     LILY_STAMP(PH_BITMAPS);
 
-    // ---- B. ids on the bias / ban lists, each once
+    // ---- C0. the first round: a threshold from a fine histogram
+    // The candidate buffer is still empty: its storage holds an 8192-bin
+    // histogram of the keys of the round's untouched logits. The bin in which
+    // the count from the top reaches k gives the first threshold; only the
+    // logits at or above it enter the buffer.
+    issue((uint32_t)(STAGES - 1));
+    uint32_t *hist0 = sm->key;
+    for (uint32_t b = tid; b < H0_BINS; b += NT) {
+        hist0[b] = 0;
+    }
+    __syncthreads();
+    Frag<T> first;
+    const uint32_t base0 = c.lo + tid * GROUP;
+    const uint32_t nvalid0 = base0 < c.hi ? min(GROUP, c.hi - base0) : 0u;
+    if (VEC) {
+        cp_async_wait<STAGES - 1>();
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            first.v[i] = ring[(0 * NT + tid) * NV + i];
+        }
+    } else {
+        load_frag_scalar<T>(first, row_ptr, base0, c.hi);
+    }
+    uint32_t keys0[GROUP];
+#pragma unroll
+    for (int e = 0; e < (int)GROUP; ++e) {
+        keys0[e] = 0;
+        if ((uint32_t)e < nvalid0) {
+            const uint32_t id = base0 + e;
+            keys0[e] = plain_key(frag_get<T>(first, e), c.T, c.argmax_mode);
+            // Possibly on the bias / ban list counts as touched (no list scan here).
+            const bool touched = (c.use_pen && seen_bit(c, id)) ||
+                                 (c.has_special &&
+                                  ((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u));
+            if (!touched) {
+                atomicAdd(&hist0[keys0[e] >> H0_SHIFT], 1u);
+            }
+        }
+    }
+    __syncthreads();
+    find_bin<H0_BINS / NT>(sm, hist0, H0_BINS, c.k, true);  // sets sel_digit when k untouched logits exist
+    uint32_t kstar0 = 0;
+    {
+        // The total is below k when find_bin found no bin: then no threshold.
+        uint32_t total = 0;
+        for (uint32_t w = 0; w < NT / 32; ++w) {
+            total += sm->warp_sums[w];
+        }
+        if (total >= c.k) {
+            const uint32_t edge = sm->sel_digit << H0_SHIFT;
+            kstar0 = edge > 0u ? edge - 1u : 0u;
+        }
+    }
+    __syncthreads();  // the histogram is read: its storage becomes the buffer again
+    if (tid == 0) {
+        sm->th_base = (kstar0 + 1u) >> 16;
+        if (kstar0 > 0u) {
+            set_threshold(sm, kstar0);
+        }
+    }
+    LILY_STAMP(PH_ROUND0);
+
+    // ---- B. ids on the bias / ban lists, each once (adjusted right away)
     if (c.has_special) {
         const uint32_t n_sp = c.bias_len + c.ban_len;
         for (uint32_t j = tid; j < n_sp; j += NT) {
@@ -1058,14 +1290,14 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             if (id < c.lo || id >= c.hi) {
                 continue;
             }
-            bool first = true;
-            for (uint32_t e = 0; e < j && first; ++e) {
+            bool first_of_id = true;
+            for (uint32_t e = 0; e < j && first_of_id; ++e) {
                 const uint32_t other = c.sp_in_smem
                                            ? sm->sp_ids[e]
                                            : (e < c.bias_len ? c.bias_ids[e] : c.ban_ids[e - c.bias_len]);
-                first = other != id;
+                first_of_id = other != id;
             }
-            if (first) {
+            if (first_of_id) {
                 const uint32_t key = adjusted_key(sm, id, widen(row_ptr[id]), true);
                 push(sm, key, id);
             }
@@ -1074,63 +1306,75 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         if (tid == 0) {
             sm->n_adj = min(sm->n, CAP);
         }
-        __syncthreads();
     }
-
+    __syncthreads();
     LILY_STAMP(PH_LISTS);
-    // ---- C. one streaming pass over the slice
-    const uint32_t span = c.hi - c.lo;
-    const uint32_t nrounds = (span + ROUND - 1u) / ROUND;
-    float c_raw = __uint_as_float(0x7FC00000u);  // NaN: nothing is rejected yet
-    uint32_t tau_key = 0;
-    bool have_tau = false;
-    const bool group_check = c.use_pen && !c.monotone;
-    for (uint32_t r0 = 0; r0 < nrounds; r0 += PF) {
+
+    // ---- C. the stream
+    // Rounds run without block barriers. Every RGROUP rounds the block meets:
+    // if a push found the buffer full, the buffer is cut back to the best k
+    // and the refused elements of those rounds are offered again (re-read
+    // from global memory, one round at a time); otherwise warp 0 tightens
+    // the threshold.
+    constexpr uint32_t RGROUP = 4;
+    const bool always_seen = c.use_pen && !c.monotone;  // penalties may raise a seen logit
+    uint32_t dropped = 0;  // 8 refused-element bits per round of the group
+    for (uint32_t r = 0; r < nrounds; ++r) {
+        Frag<T> cur;
+        const uint32_t base = c.lo + r * ROUND + tid * GROUP;
+        if (r == 0) {
+            cur = first;
+        } else {
+            issue(r + STAGES - 1);
+            if (VEC) {
+                cp_async_wait<STAGES - 1>();
 #pragma unroll
-        for (int d = 0; d < PF; ++d) {
-            const uint32_t r = r0 + d;
-            if (r < nrounds) {
-                const Frag<T> cur = ring[d];
-                load_frag<T, VEC>(ring[d], row_ptr, c.lo + (r + PF) * ROUND + tid * GROUP, c.hi);
-                const uint32_t base = c.lo + r * ROUND + tid * GROUP;
-                if (base < c.hi) {
-                    const uint32_t nvalid = min(GROUP, c.hi - base);
-                    bool all = nvalid < GROUP;
-                    if (group_check && !all) {
-                        const uint32_t off = base - c.lo;
-                        all = ((seen[off >> 5] >> (off & 31u)) & 0xFFu) != 0u;
-                    }
-                    if (all || !(frag_max(cur) <= c_raw)) {
-                        push_group<T>(sm, cur, base, nvalid, all, c_raw);
-                    }
+                for (int i = 0; i < NV; ++i) {
+                    cur.v[i] = ring[((r % STAGES) * NT + tid) * NV + i];
                 }
-                // Select when the next round could overflow the buffer, and
-                // once early, as soon as a first threshold can be had.
-                if (r == 0) LILY_STAMP(PH_ROUND0);
-                const uint32_t pending = *reinterpret_cast<volatile uint32_t *>(&sm->n);
-                const bool first = !have_tau && pending >= 2u * c.k && pending >= 1024u;
-                if (__syncthreads_or(pending > CAP - ROUND || first)) {
-                    adjust_pending(sm);
-                    select_topk(sm, min(sm->n, CAP), c.k);
-                    if (r == 0) LILY_STAMP(PH_SELECT0);
-                    if (tid == 0) {
-                        sm->c_raw = raw_threshold(sm->tau_key, c.T, c.argmax_mode);
-                        sm->have_tau = 1;
-                    }
-                    __syncthreads();
-                    if (r == 0) LILY_STAMP(PH_THRESH0);
-                    c_raw = sm->c_raw;
-                    tau_key = sm->tau_key;
-                    have_tau = true;
-                }
-                if (r == 1) LILY_STAMP(PH_R1);
-                if (r == 4) LILY_STAMP(PH_R4);
-                if (r == 8) LILY_STAMP(PH_R8);
-                if (r == 16) LILY_STAMP(PH_R16);
-                if (r == 32) LILY_STAMP(PH_R32);
+            } else {
+                load_frag_scalar<T>(cur, row_ptr, base, c.hi);
             }
         }
+        const float c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
+        if (base < c.hi) {
+            const uint32_t nvalid = min(GROUP, c.hi - base);
+            bool look = nvalid < GROUP || !(frag_max(cur) <= c_raw);
+            if (always_seen && !look) {
+                const uint32_t off = base - c.lo;
+                look = ((seen[off >> 5] >> (off & 31u)) & 0xFFu) != 0u;
+            }
+            if (look) {
+                const uint32_t failed =
+                    process_frag<T>(sm, c, cur, base, (1u << nvalid) - 1u, c_raw, always_seen);
+                dropped |= failed << (8u * (r % RGROUP));
+            }
+        }
+        if ((r % RGROUP) == RGROUP - 1u || r == nrounds - 1u) {
+            const uint32_t g0 = r - (r % RGROUP);
+            if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->overflow))) {
+                compact(sm);
+                for (uint32_t rr = g0; rr <= r; ++rr) {
+                    const uint32_t m = (dropped >> (8u * (rr - g0))) & 0xFFu;
+                    if (m != 0u) {
+                        Frag<T> again;
+                        const uint32_t b2 = c.lo + rr * ROUND + tid * GROUP;
+                        load_frag_scalar<T>(again, row_ptr, b2, c.hi);
+                        process_frag<T>(sm, c, again, b2, m, sm->c_raw, always_seen);
+                    }
+                    // Room for a whole round before the next one is offered.
+                    if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->n) >
+                                         CAP - ROUND)) {
+                        compact(sm);
+                    }
+                }
+            } else if (tid < 32u && *reinterpret_cast<volatile uint32_t *>(&sm->th_new) != 0u) {
+                tighten(sm);
+            }
+            dropped = 0;
+        }
     }
+    cp_async_wait<0>();
     __syncthreads();
 
     LILY_STAMP(PH_STREAM);
@@ -1157,7 +1401,12 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 
     uint32_t n = min(sm->n, CAP);
     __syncthreads();
-    if (n > c.k) {
+    bool sorted = false;
+    if (n <= RANKSORT_MAX) {
+        rank_sort(sm, n, c.k);
+        n = min(n, c.k);
+        sorted = true;
+    } else if (n > c.k) {
         select_topk(sm, n, c.k);
         n = c.k;
     }
@@ -1227,7 +1476,12 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         }
         __syncthreads();
         n = sm->n;
-        if (n > c.k) {
+        sorted = false;
+        if (n <= RANKSORT_MAX) {
+            rank_sort(sm, n, c.k);
+            n = min(n, c.k);
+            sorted = true;
+        } else if (n > c.k) {
             select_topk(sm, n, c.k);
             n = c.k;
         }
@@ -1251,13 +1505,17 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     if (n <= 64u) {
         // One warp finishes the row; the others are done.
         if (tid < 32u) {
-            sort_candidates<true>(sm, n);
+            if (!sorted) {
+                sort_candidates<true>(sm, n);
+            }
             LILY_STAMP(PH_SORT);
             finalize<true>(sm, a, row, n, P.seed);
             LILY_STAMP(PH_END);
         }
     } else {
-        sort_candidates<false>(sm, n);
+        if (!sorted) {
+            sort_candidates<false>(sm, n);
+        }
         LILY_STAMP(PH_SORT);
         finalize<false>(sm, a, row, n, P.seed);
         LILY_STAMP(PH_END);
