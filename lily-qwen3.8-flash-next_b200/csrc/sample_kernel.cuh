@@ -274,6 +274,53 @@ __device__ __noinline__ void adjust_pending(SmemFixed *sm) {
     __syncthreads();
 }
 
+// End of the stream: adjusts what is still raw and keeps only the entries
+// whose key reaches the threshold (at least k of them do), compacted to the
+// front in chunks so that no entry is overwritten before it is read.
+__device__ __noinline__ void filter_adjust(SmemFixed *sm) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t n = min(sm->n, CAP);
+    const uint32_t from = sm->n_adj;
+    const uint32_t kstar = sm->kstar;
+    if (tid == 0) {
+        sm->cnt = 0;
+    }
+    __syncthreads();
+    for (uint32_t c0 = 0; c0 < n; c0 += NT) {
+        const uint32_t i = c0 + tid;
+        bool alive = false;
+        uint32_t key = 0, id = 0;
+        if (i < n) {
+            id = sm->id[i];
+            key = sm->key[i];
+            if (i >= from) {
+                key = adjusted_key(sm, id, __uint_as_float(key), false);
+            }
+            alive = key >= kstar;
+        }
+        __syncthreads();  // the chunk is read: survivors may now land in it
+        if (alive) {
+            const unsigned act = __activemask();
+            const int lane = tid & 31;
+            const int leader = __ffs(act) - 1;
+            uint32_t base = 0;
+            if (lane == leader) {
+                base = atomicAdd(&sm->cnt, (uint32_t)__popc(act));
+            }
+            base = __shfl_sync(act, base, leader);
+            const uint32_t pos = base + __popc(act & ((1u << lane) - 1u));
+            sm->key[pos] = key;
+            sm->id[pos] = id;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        sm->n = sm->cnt;
+        sm->n_adj = sm->cnt;
+    }
+    __syncthreads();
+}
+
 constexpr uint32_t SEL_BITS = 11;
 constexpr uint32_t SEL_BINS = 1u << SEL_BITS;  // the select's histogram aliases tkey + tid
 
@@ -626,11 +673,35 @@ __device__ __noinline__ void finalize(SmemFixed *sm, const KArgs &a, uint32_t ro
         p[i] = exp_f32(__fsub_rn(float_of_key(sm->key[i]), top));
     }
     Team<SMALL>::sync();
-    if (me == 0) {
+    if (SMALL) {
+        // n <= 64: every lane runs the same sequential sum over values handed
+        // round by shuffles (rank order, one rounding per add), and keeps the
+        // prefixes of its own two slots.
+        const float p0 = me < n ? p[me] : 0.0f;
+        const float p1 = me + 32u < n ? p[me + 32u] : 0.0f;
+        float s = 0.0f, c0 = 0.0f, c1 = 0.0f;
+        for (uint32_t j = 0; j < n; ++j) {
+            const float v = __shfl_sync(0xFFFFFFFFu, j < 32u ? p0 : p1, (int)(j & 31u));
+            s = __fadd_rn(s, v);
+            c0 = j == me ? s : c0;
+            c1 = j == me + 32u ? s : c1;
+        }
+        if (me < n) {
+            cum[me] = c0;
+        }
+        if (me + 32u < n) {
+            cum[me + 32u] = c1;
+        }
+        if (me == 0) {
+            sm->n_keep = n;
+        }
+    } else if (me == 0) {
+        const float *__restrict__ pr = p;
+        float *__restrict__ cw = cum;
         float s = 0.0f;
         for (uint32_t i = 0; i < n; ++i) {
-            s = __fadd_rn(s, p[i]);
-            cum[i] = s;
+            s = __fadd_rn(s, pr[i]);
+            cw[i] = s;
         }
         sm->n_keep = n;
     }
@@ -762,13 +833,20 @@ __device__ __forceinline__ void set_threshold(SmemFixed *sm, uint32_t kstar) {
 
 // One warp tightens the threshold from the histogram of the keys pushed so
 // far: the highest bin edge that at least k counted (untouched) logits reach.
+// Only the bins at and above the current threshold can matter.
 __device__ __noinline__ void tighten(SmemFixed *sm) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t k = sm->ctx.k;
-    // Lane l owns bins [32 l, 32 l + 32), scanned from the top bin down.
+    const uint32_t base = sm->th_base;
+    const uint32_t cur16 = (sm->kstar + 1u) >> 16;
+    const uint32_t lo_bin = cur16 > base ? min(cur16 - base, TH_BINS - 1u) : 0u;
+    const uint32_t per = (TH_BINS - lo_bin + 31u) / 32u;  // bins per lane, from the top down
     uint32_t sum = 0;
-    for (uint32_t j = 0; j < TH_BINS / 32u; ++j) {
-        sum += sm->thist[TH_BINS - 1u - (lane * (TH_BINS / 32u) + j)];
+    for (uint32_t j = 0; j < per; ++j) {
+        const uint32_t pos = lane * per + j;
+        if (pos < TH_BINS - lo_bin) {
+            sum += sm->thist[TH_BINS - 1u - pos];
+        }
     }
     uint32_t incl = sum;
 #pragma unroll
@@ -781,13 +859,17 @@ __device__ __noinline__ void tighten(SmemFixed *sm) {
     const uint32_t excl = incl - sum;
     if (excl < k && k <= incl) {
         uint32_t cum = excl;
-        for (uint32_t j = 0; j < TH_BINS / 32u; ++j) {
-            const uint32_t bin = TH_BINS - 1u - (lane * (TH_BINS / 32u) + j);
+        for (uint32_t j = 0; j < per; ++j) {
+            const uint32_t pos = lane * per + j;
+            if (pos >= TH_BINS - lo_bin) {
+                break;
+            }
+            const uint32_t bin = TH_BINS - 1u - pos;
             cum += sm->thist[bin];
             if (cum >= k) {
                 // At least k counted logits have a key of (base + bin) << 16
                 // or more: nothing below that can be among the best k.
-                const uint32_t edge = (sm->th_base + bin) << 16;
+                const uint32_t edge = (base + bin) << 16;
                 if (edge > 0u) {
                     set_threshold(sm, edge - 1u);
                 }
@@ -922,6 +1004,19 @@ __device__ __forceinline__ void load_frag_scalar(Frag<T> &f, const T *row, uint3
     }
 }
 
+// Element e of a fragment, e not known at compile time.
+__device__ __forceinline__ float frag_pick(const Frag<float> &f, uint32_t e) {
+    const uint4 q = e < 4u ? f.v[0] : f.v[1];
+    const uint32_t i = e & 3u;
+    return __uint_as_float(i == 0u ? q.x : i == 1u ? q.y : i == 2u ? q.z : q.w);
+}
+
+__device__ __forceinline__ float frag_pick(const Frag<__nv_bfloat16> &f, uint32_t e) {
+    const uint32_t i = e >> 1;
+    const uint32_t w = i == 0u ? f.v[0].x : i == 1u ? f.v[0].y : i == 2u ? f.v[0].z : f.v[0].w;
+    return (e & 1u) ? bf16_hi(w) : bf16_lo(w);
+}
+
 // One thread's eight logits of a round: those in `mask` that beat the raw
 // threshold (or, when penalties may raise a logit, are in the history) go
 // into the buffer as raw bits; ids on the bias / ban list were handled up
@@ -931,32 +1026,35 @@ template <typename T>
 __device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c,
                                                  const Frag<T> &cur, uint32_t base, uint32_t mask,
                                                  float c_raw, bool always_seen) {
-    uint32_t failed = 0;
+    uint32_t pass = 0;
 #pragma unroll
     for (int e = 0; e < (int)GROUP; ++e) {
-        if ((mask >> e) & 1u) {
-            const float l = frag_get<T>(cur, e);
-            const uint32_t id = base + e;
-            const bool pass = !(l <= c_raw);
-            bool seen_here = false;
-            if (c.use_pen && (pass || always_seen)) {
-                seen_here = seen_bit(c, id);
-            }
-            if (pass || (always_seen && seen_here)) {
-                if (!(c.has_special && is_special(sm, c, id))) {
-                    if (push(sm, __float_as_uint(l), id)) {
-                        if (!seen_here) {
-                            const uint32_t k16 = plain_key(l, c.T, c.argmax_mode) >> 16;
-                            const uint32_t b16 = sm->th_base;
-                            if (k16 >= b16) {
-                                atomicAdd(&sm->thist[min(k16 - b16, TH_BINS - 1u)], 1u);
-                                sm->th_new = 1;
-                            }
-                        }
-                    } else {
-                        failed |= 1u << e;
-                    }
-                }
+        pass |= (!(frag_get<T>(cur, e) <= c_raw) ? 1u : 0u) << e;
+    }
+    if (always_seen) {
+        const uint32_t off = base - c.lo;
+        pass |= (c.seen[off >> 5] >> (off & 31u)) & 0xFFu;
+    }
+    pass &= mask;
+    uint32_t failed = 0;
+    while (pass != 0u) {
+        const uint32_t e = (uint32_t)__ffs(pass) - 1u;
+        pass &= pass - 1u;
+        const float l = frag_pick(cur, e);
+        const uint32_t id = base + e;
+        if (c.has_special && is_special(sm, c, id)) {
+            continue;
+        }
+        if (!push(sm, __float_as_uint(l), id)) {
+            failed |= 1u << e;
+            continue;
+        }
+        if (!(c.use_pen && seen_bit(c, id))) {
+            const uint32_t k16 = plain_key(l, c.T, c.argmax_mode) >> 16;
+            const uint32_t b16 = sm->th_base;
+            if (k16 >= b16) {
+                atomicAdd(&sm->thist[min(k16 - b16, TH_BINS - 1u)], 1u);
+                sm->th_new = 1;
             }
         }
     }
@@ -1113,8 +1211,16 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     constexpr int STAGES = RING_BYTES / (NT * 16 * NV);            // 4 for bf16, 2 for f32
     const uint32_t span = c.hi - c.lo;
     const uint32_t nrounds = (span + ROUND - 1u) / ROUND;
+    const uint32_t nfull = span / ROUND;  // rounds in which every thread has eight logits
+    const char *my_src = reinterpret_cast<const char *>(row_ptr + c.lo + tid * GROUP);
     auto issue = [&](uint32_t r) {
-        if (VEC && r < nrounds) {
+        if (VEC && r < nfull) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                cp_async_16(&ring[((r % STAGES) * NT + tid) * NV + i],
+                            my_src + (size_t)r * (ROUND * sizeof(T)) + 16 * i, 16u);
+            }
+        } else if (VEC && r < nrounds) {
             const uint32_t base = c.lo + r * ROUND + tid * GROUP;
             const uint32_t left = base < c.hi ? (c.hi - base) * (uint32_t)sizeof(T) : 0u;
 #pragma unroll
@@ -1314,8 +1420,8 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // Rounds run without block barriers. Every RGROUP rounds the block meets:
     // if a push found the buffer full, the buffer is cut back to the best k
     // and the refused elements of those rounds are offered again (re-read
-    // from global memory, one round at a time); otherwise warp 0 tightens
-    // the threshold.
+    // from global memory, one round at a time). The warps take turns
+    // tightening the threshold, one per round.
     constexpr uint32_t RGROUP = 4;
     const bool always_seen = c.use_pen && !c.monotone;  // penalties may raise a seen logit
     uint32_t dropped = 0;  // 8 refused-element bits per round of the group
@@ -1337,23 +1443,49 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             }
         }
         const float c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
-        if (base < c.hi) {
-            const uint32_t nvalid = min(GROUP, c.hi - base);
-            bool look = nvalid < GROUP || !(frag_max(cur) <= c_raw);
+        if (r < nfull) {
+            // Every thread holds eight valid logits.
+            bool look = !(frag_max(cur) <= c_raw);
             if (always_seen && !look) {
                 const uint32_t off = base - c.lo;
                 look = ((seen[off >> 5] >> (off & 31u)) & 0xFFu) != 0u;
             }
             if (look) {
-                const uint32_t failed =
-                    process_frag<T>(sm, c, cur, base, (1u << nvalid) - 1u, c_raw, always_seen);
-                dropped |= failed << (8u * (r % RGROUP));
+                dropped |= process_frag<T>(sm, c, cur, base, 0xFFu, c_raw, always_seen)
+                           << (8u * (r % RGROUP));
+            }
+        } else if (base < c.hi) {
+            const uint32_t nvalid = min(GROUP, c.hi - base);
+            dropped |= process_frag<T>(sm, c, cur, base, (1u << nvalid) - 1u, c_raw, always_seen)
+                       << (8u * (r % RGROUP));
+        }
+        if ((tid >> 5) == (r & (NT / 32 - 1u))) {
+            // The lanes may come out of the divergent pushes apart: meet
+            // first, then let ONE lane's reading decide for the whole warp
+            // (the flag can change between two lanes' readings).
+            __syncwarp();
+            uint32_t go = 0;
+            if ((tid & 31u) == 0u) {
+                go = *reinterpret_cast<volatile uint32_t *>(&sm->th_new);
+            }
+            go = __shfl_sync(0xFFFFFFFFu, go, 0);
+            if (go != 0u) {
+                tighten(sm);
             }
         }
         if ((r % RGROUP) == RGROUP - 1u || r == nrounds - 1u) {
             const uint32_t g0 = r - (r % RGROUP);
             if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->overflow))) {
                 compact(sm);
+                // What is left to offer fits at once when the refused elements
+                // are fewer than the room the selection made.
+                if (tid == 0) {
+                    sm->cnt = 0;
+                }
+                __syncthreads();
+                atomicAdd(&sm->cnt, (uint32_t)__popc(dropped));
+                __syncthreads();
+                const bool at_once = sm->n + sm->cnt <= CAP;
                 for (uint32_t rr = g0; rr <= r; ++rr) {
                     const uint32_t m = (dropped >> (8u * (rr - g0))) & 0xFFu;
                     if (m != 0u) {
@@ -1362,14 +1494,13 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                         load_frag_scalar<T>(again, row_ptr, b2, c.hi);
                         process_frag<T>(sm, c, again, b2, m, sm->c_raw, always_seen);
                     }
-                    // Room for a whole round before the next one is offered.
-                    if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->n) >
+                    // Otherwise: room for a whole round before the next one.
+                    if (!at_once &&
+                        __syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->n) >
                                          CAP - ROUND)) {
                         compact(sm);
                     }
                 }
-            } else if (tid < 32u && *reinterpret_cast<volatile uint32_t *>(&sm->th_new) != 0u) {
-                tighten(sm);
             }
             dropped = 0;
         }
@@ -1378,7 +1509,11 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     __syncthreads();
 
     LILY_STAMP(PH_STREAM);
-    adjust_pending(sm);  // reads the count table: before it is cleared
+    if (tid < 32u && sm->th_new != 0u) {
+        tighten(sm);
+    }
+    __syncthreads();
+    filter_adjust(sm);  // reads the count table: before it is cleared
     // The count table goes back to all zero (history-list mode only).
     if (c.need_counts && !table_mode) {
         const uint32_t total = hist_len + extra_len;
