@@ -188,8 +188,8 @@ uint32_t choose_slices(const lily_sampler *h, uint32_t rows) {
     if (s > lily::MAX_SLICES) {
         s = lily::MAX_SLICES;
     }
-    // Slices shorter than one round of 4096 logits buy nothing.
-    const uint32_t by_len = (h->vocab + lily::ROUND - 1u) / lily::ROUND;
+    // Slices shorter than 4096 logits buy nothing.
+    const uint32_t by_len = (h->vocab + lily::MIN_SLICE - 1u) / lily::MIN_SLICE;
     if (s > by_len) {
         s = by_len;
     }

@@ -37,17 +37,26 @@
 namespace lily {
 
 constexpr int NT = 512;                 // threads per block
-constexpr uint32_t GROUP = 8;           // logits per thread per round
-constexpr uint32_t ROUND = NT * GROUP;  // logits per block per round
+constexpr uint32_t FRAG_BYTES = 32;     // logit bytes per thread per round
 constexpr uint32_t KCAP = LILY_K_CAP;
-constexpr uint32_t CAP = ROUND + KCAP;  // candidate buffer entries
-constexpr uint32_t RING_BYTES = 32768;  // cp.async ring: 4 rounds of bf16, 2 of f32
+constexpr uint32_t CAP = 4096;          // candidate buffer entries
+constexpr int STAGES = 2;               // rounds in flight in the cp.async ring
+constexpr uint32_t RING_BYTES = STAGES * NT * FRAG_BYTES;
 constexpr uint32_t SP_SMEM = 256;       // bias + ban entries staged in shared memory
 constexpr uint32_t MAX_SLICES = LILY_MAX_SLICES;
-constexpr uint32_t H0_SHIFT = 19;       // first-round histogram: key >> 19, 8192 bins
+constexpr uint32_t MIN_SLICE = 4096;    // slices shorter than this buy nothing
+constexpr uint32_t H0_SHIFT = 19;       // first-round histogram: raw key >> 19, 8192 bins
 constexpr uint32_t H0_BINS = 1u << (32 - H0_SHIFT);
-constexpr uint32_t TH_BINS = 1024;      // tightening histogram: key >> 16 above a base
+constexpr uint32_t TH_BINS = 1024;      // tightening histogram: raw key >> 16 above a base
 constexpr uint32_t RANKSORT_MAX = 384;  // candidate counts up to this are rank-sorted
+
+// Per logit type: 16 bf16 or 8 f32 per thread per round.
+template <typename T>
+struct Geo {
+    static constexpr uint32_t GROUP = FRAG_BYTES / sizeof(T);
+    static constexpr uint32_t ROUND = NT * GROUP;
+    static constexpr uint32_t RGROUP = 32u / GROUP;  // rounds between block-wide checks
+};
 
 // Row status bits OR-ed into the handle's status word.
 constexpr uint32_t ROW_INTERNAL = 8;  // candidate buffer overflow: a bug, never expected
@@ -154,8 +163,8 @@ struct alignas(16) SmemFixed {
     RowCtx ctx;  // the row's parameters, for the out-of-line helpers
 };
 
-static_assert(sizeof(uint32_t) * 2 * CAP >= sizeof(uint32_t) * H0_BINS,
-              "the first-round histogram aliases the candidate buffer");
+static_assert(2 * CAP >= H0_BINS, "the first-round histogram aliases the candidate buffer");
+static_assert(CAP >= KCAP + NT, "a selection must leave room for one push per thread");
 
 __device__ __forceinline__ float neg_inf() { return __uint_as_float(0xFF800000u); }
 
@@ -821,25 +830,50 @@ __device__ __noinline__ void finalize(SmemFixed *sm, const KArgs &a, uint32_t ro
 }
 
 
-// Sets the threshold to `kstar` (thread 0): logits whose plain key is at or
-// below it are not looked at any more.
-__device__ __forceinline__ void set_threshold(SmemFixed *sm, uint32_t kstar) {
-    const RowCtx &c = sm->ctx;
+// Raises the raw threshold to `c` (pass iff l > c) and the adjusted-key
+// threshold to `kstar` (survivors have key >= kstar). Any single thread;
+// concurrent callers only ever store valid thresholds.
+__device__ __forceinline__ void raise_threshold(SmemFixed *sm, float c, uint32_t kstar) {
+    if (c == c && !(c <= sm->c_raw)) {
+        sm->c_raw = c;
+    }
     if (kstar > sm->kstar) {
         sm->kstar = kstar;
-        sm->c_raw = raw_threshold(kstar, c.T, c.argmax_mode);
     }
 }
 
-// One warp tightens the threshold from the histogram of the keys pushed so
-// far: the highest bin edge that at least k counted (untouched) logits reach.
-// Only the bins at and above the current threshold can matter.
+// After an exact selection: the k-th key is the new threshold.
+__device__ __forceinline__ void set_exact_threshold(SmemFixed *sm, uint32_t kth_key) {
+    const RowCtx &c = sm->ctx;
+    raise_threshold(sm, raw_threshold(kth_key, c.T, c.argmax_mode), kth_key);
+}
+
+// At least k untouched logits have a raw key of `edge_key` or more: no logit
+// below that value can be among the best k (scaling keeps the order).
+__device__ __forceinline__ void set_raw_edge(SmemFixed *sm, uint32_t edge_key) {
+    const RowCtx &c = sm->ctx;
+    if (edge_key == 0u) {
+        return;
+    }
+    float below = float_of_key(edge_key - 1u);
+    if (below == 0.0f) {
+        below = __uint_as_float(0x80000001u);  // the float compare cannot tell the zeros apart
+    }
+    const uint32_t pk = plain_key(float_of_key(edge_key), c.T, c.argmax_mode);
+    raise_threshold(sm, below, pk > 0u ? pk - 1u : 0u);
+}
+
+// One warp tightens the threshold from the histogram of the raw keys pushed
+// so far: the highest bin edge that at least k counted (untouched) logits
+// reach. Only the bins at and above the current threshold can matter.
 __device__ __noinline__ void tighten(SmemFixed *sm) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t k = sm->ctx.k;
     const uint32_t base = sm->th_base;
-    const uint32_t cur16 = (sm->kstar + 1u) >> 16;
-    const uint32_t lo_bin = cur16 > base ? min(cur16 - base, TH_BINS - 1u) : 0u;
+    const uint32_t cur16 = key_of(sm->c_raw) >> 16;  // a NaN threshold maps above every bin
+    const uint32_t lo_bin = (sm->c_raw == sm->c_raw && cur16 > base)
+                                ? min(cur16 - base, TH_BINS - 1u)
+                                : 0u;
     const uint32_t per = (TH_BINS - lo_bin + 31u) / 32u;  // bins per lane, from the top down
     uint32_t sum = 0;
     for (uint32_t j = 0; j < per; ++j) {
@@ -867,12 +901,9 @@ __device__ __noinline__ void tighten(SmemFixed *sm) {
             const uint32_t bin = TH_BINS - 1u - pos;
             cum += sm->thist[bin];
             if (cum >= k) {
-                // At least k counted logits have a key of (base + bin) << 16
-                // or more: nothing below that can be among the best k.
-                const uint32_t edge = (base + bin) << 16;
-                if (edge > 0u) {
-                    set_threshold(sm, edge - 1u);
-                }
+                // (The top bin also holds everything above it; its lower
+                // edge is as valid a bound.)
+                set_raw_edge(sm, (base + bin) << 16);
                 break;
             }
         }
@@ -925,38 +956,54 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-template <typename T>
-struct Frag;
-
-template <>
-struct Frag<float> {
+// One thread's logits of a round: 32 bytes, 16 bf16 or 8 f32.
+struct Frag {
     uint4 v[2];
 };
 
-template <>
-struct Frag<__nv_bfloat16> {
-    uint4 v[1];
-};
-
 template <typename T>
-__device__ __forceinline__ float frag_get(const Frag<T> &f, int e);
+__device__ __forceinline__ float frag_get(const Frag &f, int e);
 
 template <>
-__device__ __forceinline__ float frag_get<float>(const Frag<float> &f, int e) {
+__device__ __forceinline__ float frag_get<float>(const Frag &f, int e) {
     const uint4 &q = f.v[e >> 2];
     const uint32_t w = (e & 3) == 0 ? q.x : (e & 3) == 1 ? q.y : (e & 3) == 2 ? q.z : q.w;
     return __uint_as_float(w);
 }
 
 template <>
-__device__ __forceinline__ float frag_get<__nv_bfloat16>(const Frag<__nv_bfloat16> &f, int e) {
-    const uint4 &q = f.v[0];
-    const uint32_t w = (e >> 1) == 0 ? q.x : (e >> 1) == 1 ? q.y : (e >> 1) == 2 ? q.z : q.w;
+__device__ __forceinline__ float frag_get<__nv_bfloat16>(const Frag &f, int e) {
+    const uint4 &q = f.v[e >> 3];
+    const int i = (e >> 1) & 3;
+    const uint32_t w = i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
     return (e & 1) ? bf16_hi(w) : bf16_lo(w);
 }
 
-// The NaN-propagating maximum of the fragment's eight logits.
-__device__ __forceinline__ float frag_max(const Frag<float> &f) {
+// Element e of a fragment, e not known at compile time.
+template <typename T>
+__device__ __forceinline__ float frag_pick(const Frag &f, uint32_t e);
+
+template <>
+__device__ __forceinline__ float frag_pick<float>(const Frag &f, uint32_t e) {
+    const uint4 q = e < 4u ? f.v[0] : f.v[1];
+    const uint32_t i = e & 3u;
+    return __uint_as_float(i == 0u ? q.x : i == 1u ? q.y : i == 2u ? q.z : q.w);
+}
+
+template <>
+__device__ __forceinline__ float frag_pick<__nv_bfloat16>(const Frag &f, uint32_t e) {
+    const uint4 q = e < 8u ? f.v[0] : f.v[1];
+    const uint32_t i = (e >> 1) & 3u;
+    const uint32_t w = i == 0u ? q.x : i == 1u ? q.y : i == 2u ? q.z : q.w;
+    return (e & 1u) ? bf16_hi(w) : bf16_lo(w);
+}
+
+// The NaN-propagating maximum of the fragment's logits.
+template <typename T>
+__device__ __forceinline__ float frag_max(const Frag &f);
+
+template <>
+__device__ __forceinline__ float frag_max<float>(const Frag &f) {
     const float a = max_nan_f32(__uint_as_float(f.v[0].x), __uint_as_float(f.v[0].y));
     const float b = max_nan_f32(__uint_as_float(f.v[0].z), __uint_as_float(f.v[0].w));
     const float c = max_nan_f32(__uint_as_float(f.v[1].x), __uint_as_float(f.v[1].y));
@@ -964,30 +1011,31 @@ __device__ __forceinline__ float frag_max(const Frag<float> &f) {
     return max_nan_f32(max_nan_f32(a, b), max_nan_f32(c, d));
 }
 
-__device__ __forceinline__ float frag_max(const Frag<__nv_bfloat16> &f) {
+template <>
+__device__ __forceinline__ float frag_max<__nv_bfloat16>(const Frag &f) {
     const uint32_t a = max_nan_bf16x2(f.v[0].x, f.v[0].y);
     const uint32_t b = max_nan_bf16x2(f.v[0].z, f.v[0].w);
-    const uint32_t m = max_nan_bf16x2(a, b);
+    const uint32_t c = max_nan_bf16x2(f.v[1].x, f.v[1].y);
+    const uint32_t d = max_nan_bf16x2(f.v[1].z, f.v[1].w);
+    const uint32_t m = max_nan_bf16x2(max_nan_bf16x2(a, b), max_nan_bf16x2(c, d));
     return max_nan_f32(bf16_lo(m), bf16_hi(m));
 }
 
 __device__ __forceinline__ float widen(float x) { return x; }
 __device__ __forceinline__ float widen(__nv_bfloat16 x) { return __bfloat162float(x); }
 
-// Scalar fallback for rows that are not 16-byte aligned: the eight logits
-// [base, base + 8), slots at or past `hi` zero.
+// Plain loads (any alignment) of the logits [base, base + GROUP) of a row;
+// slots at or past `hi` zero.
 template <typename T>
-__device__ __forceinline__ void load_frag_scalar(Frag<T> &f, const T *row, uint32_t base,
+__device__ __forceinline__ void load_frag_scalar(Frag &f, const T *row, uint32_t base,
                                                  uint32_t hi) {
-    constexpr int NV = sizeof(Frag<T>) / 16;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        f.v[i] = make_uint4(0, 0, 0, 0);
-    }
+    constexpr int G = (int)Geo<T>::GROUP;
+    f.v[0] = make_uint4(0, 0, 0, 0);
+    f.v[1] = make_uint4(0, 0, 0, 0);
     uint32_t *words = reinterpret_cast<uint32_t *>(&f);
     if (sizeof(T) == 4) {
 #pragma unroll
-        for (int e = 0; e < (int)GROUP; ++e) {
+        for (int e = 0; e < G; ++e) {
             if (base + e < hi) {
                 words[e] = __float_as_uint(widen(row[base + e]));
             }
@@ -995,7 +1043,7 @@ __device__ __forceinline__ void load_frag_scalar(Frag<T> &f, const T *row, uint3
     } else {
         const uint16_t *r16 = reinterpret_cast<const uint16_t *>(row);
 #pragma unroll
-        for (int e = 0; e < (int)GROUP; ++e) {
+        for (int e = 0; e < G; ++e) {
             if (base + e < hi) {
                 const uint32_t b = r16[base + e];
                 words[e >> 1] |= (e & 1) ? (b << 16) : b;
@@ -1004,43 +1052,31 @@ __device__ __forceinline__ void load_frag_scalar(Frag<T> &f, const T *row, uint3
     }
 }
 
-// Element e of a fragment, e not known at compile time.
-__device__ __forceinline__ float frag_pick(const Frag<float> &f, uint32_t e) {
-    const uint4 q = e < 4u ? f.v[0] : f.v[1];
-    const uint32_t i = e & 3u;
-    return __uint_as_float(i == 0u ? q.x : i == 1u ? q.y : i == 2u ? q.z : q.w);
-}
-
-__device__ __forceinline__ float frag_pick(const Frag<__nv_bfloat16> &f, uint32_t e) {
-    const uint32_t i = e >> 1;
-    const uint32_t w = i == 0u ? f.v[0].x : i == 1u ? f.v[0].y : i == 2u ? f.v[0].z : f.v[0].w;
-    return (e & 1u) ? bf16_hi(w) : bf16_lo(w);
-}
-
-// One thread's eight logits of a round: those in `mask` that beat the raw
+// One thread's logits of a round: those in `mask` that beat the raw
 // threshold (or, when penalties may raise a logit, are in the history) go
 // into the buffer as raw bits; ids on the bias / ban list were handled up
 // front and are skipped. Untouched logits also count in the tightening
 // histogram. Returns the mask of elements the full buffer refused.
 template <typename T>
-__device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c,
-                                                 const Frag<T> &cur, uint32_t base, uint32_t mask,
-                                                 float c_raw, bool always_seen) {
+__device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c, const Frag &cur,
+                                                 uint32_t base, uint32_t mask, float c_raw,
+                                                 bool always_seen) {
+    constexpr int G = (int)Geo<T>::GROUP;
     uint32_t pass = 0;
 #pragma unroll
-    for (int e = 0; e < (int)GROUP; ++e) {
+    for (int e = 0; e < G; ++e) {
         pass |= (!(frag_get<T>(cur, e) <= c_raw) ? 1u : 0u) << e;
     }
     if (always_seen) {
-        const uint32_t off = base - c.lo;
-        pass |= (c.seen[off >> 5] >> (off & 31u)) & 0xFFu;
+        const uint32_t off = base - c.lo;  // a multiple of GROUP: the bits sit in one word
+        pass |= (c.seen[off >> 5] >> (off & 31u)) & ((1u << G) - 1u);
     }
     pass &= mask;
     uint32_t failed = 0;
     while (pass != 0u) {
         const uint32_t e = (uint32_t)__ffs(pass) - 1u;
         pass &= pass - 1u;
-        const float l = frag_pick(cur, e);
+        const float l = frag_pick<T>(cur, e);
         const uint32_t id = base + e;
         if (c.has_special && is_special(sm, c, id)) {
             continue;
@@ -1050,7 +1086,7 @@ __device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c,
             continue;
         }
         if (!(c.use_pen && seen_bit(c, id))) {
-            const uint32_t k16 = plain_key(l, c.T, c.argmax_mode) >> 16;
+            const uint32_t k16 = key_of(l) >> 16;
             const uint32_t b16 = sm->th_base;
             if (k16 >= b16) {
                 atomicAdd(&sm->thist[min(k16 - b16, TH_BINS - 1u)], 1u);
@@ -1070,7 +1106,7 @@ __device__ __noinline__ void compact(SmemFixed *sm) {
     if (n > k) {
         select_topk(sm, n, k);
         if (threadIdx.x == 0) {
-            set_threshold(sm, sm->tau_key);
+            set_exact_threshold(sm, sm->tau_key);
         }
     }
     if (threadIdx.x == 0) {
@@ -1206,37 +1242,47 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     const T *row_ptr = reinterpret_cast<const T *>(a.logits) + (uint64_t)row * a.logits_ld;
 
     // The ring: STAGES rounds of this block's logits in flight, each thread
-    // copying (and later reading back) its own 16-byte pieces.
-    constexpr int NV = sizeof(Frag<T>) / 16;                       // 16-byte pieces per thread-round
-    constexpr int STAGES = RING_BYTES / (NT * 16 * NV);            // 4 for bf16, 2 for f32
+    // copying (and later reading back) its own 32 bytes.
+    constexpr uint32_t GROUP = Geo<T>::GROUP;
+    constexpr uint32_t ROUND = Geo<T>::ROUND;
+    constexpr uint32_t RGROUP = Geo<T>::RGROUP;
     const uint32_t span = c.hi - c.lo;
     const uint32_t nrounds = (span + ROUND - 1u) / ROUND;
-    const uint32_t nfull = span / ROUND;  // rounds in which every thread has eight logits
+    const uint32_t nfull = span / ROUND;  // rounds in which every thread has all its logits
     const char *my_src = reinterpret_cast<const char *>(row_ptr + c.lo + tid * GROUP);
     auto issue = [&](uint32_t r) {
+        uint4 *dst = &ring[((r % STAGES) * NT + tid) * 2u];
         if (VEC && r < nfull) {
-#pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                cp_async_16(&ring[((r % STAGES) * NT + tid) * NV + i],
-                            my_src + (size_t)r * (ROUND * sizeof(T)) + 16 * i, 16u);
-            }
+            const char *src = my_src + (size_t)r * (ROUND * sizeof(T));
+            cp_async_16(dst, src, 16u);
+            cp_async_16(dst + 1, src + 16, 16u);
         } else if (VEC && r < nrounds) {
             const uint32_t base = c.lo + r * ROUND + tid * GROUP;
             const uint32_t left = base < c.hi ? (c.hi - base) * (uint32_t)sizeof(T) : 0u;
 #pragma unroll
-            for (int i = 0; i < NV; ++i) {
+            for (int i = 0; i < 2; ++i) {
                 const uint32_t off = 16u * i;
                 const uint32_t bytes = left > off ? min(16u, left - off) : 0u;
                 const char *src = bytes ? reinterpret_cast<const char *>(row_ptr + base) + off
                                         : reinterpret_cast<const char *>(row_ptr);
-                cp_async_16(&ring[((r % STAGES) * NT + tid) * NV + i], src, bytes);
+                cp_async_16(dst + i, src, bytes);
             }
         }
         cp_async_commit();
     };
+    auto fetch = [&](uint32_t r, Frag &f) {
+        if (VEC) {
+            cp_async_wait<STAGES - 1>();
+            const uint4 *src = &ring[((r % STAGES) * NT + tid) * 2u];
+            f.v[0] = src[0];
+            f.v[1] = src[1];
+        } else {
+            load_frag_scalar<T>(f, row_ptr, c.lo + r * ROUND + tid * GROUP, c.hi);
+        }
+    };
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        issue((uint32_t)s);
+    for (int st = 0; st < STAGES - 1; ++st) {
+        issue((uint32_t)st);
     }
 
     // ---- A. bitmaps
@@ -1274,42 +1320,59 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     __syncthreads();
     LILY_STAMP(PH_START);
     if (hist_len + extra_len > 0u) {
-        const uint32_t total = hist_len + extra_len;
-        constexpr int HB = 16;  // ids in flight per thread
-        for (uint32_t i0 = 0; i0 < total; i0 += NT * HB) {
-            uint32_t ids[HB];
+        auto mark = [&](uint32_t id) {
+            const bool mine = id >= c.lo && id < c.hi;
+            if (mine) {
+                // Real histories repeat a few ids very often: skip the atomic
+                // when the bit is already up.
+                const uint32_t off = id - c.lo;
+                const uint32_t bit = 1u << (off & 31u);
+                if (!(*reinterpret_cast<volatile uint32_t *>(&seen[off >> 5]) & bit)) {
+                    atomicOr(&seen[off >> 5], bit);
+                }
+            }
+            if (c.need_counts) {
+                // One global atomic per distinct id of the warp.
+                const unsigned live = __ballot_sync(0xFFFFFFFFu, mine);
+                if (mine) {
+                    const unsigned peers = __match_any_sync(live, id);
+                    if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
+                        atomicAdd(counts_rw + id, (uint32_t)__popc(peers));
+                    }
+                }
+            }
+        };
+        // The bulk of the list in 16-byte loads, four in flight per thread.
+        const bool hvec = (reinterpret_cast<uintptr_t>(hist) & 15u) == 0u;
+        const uint32_t n4 = hvec ? hist_len / 4u : 0u;
+        const uint4 *h4 = reinterpret_cast<const uint4 *>(hist);
+        constexpr int HB = 4;
+        for (uint32_t i0 = 0; i0 < n4; i0 += NT * HB) {
+            uint4 q[HB];
 #pragma unroll
             for (int j = 0; j < HB; ++j) {
                 const uint32_t i = i0 + (uint32_t)j * NT + tid;
-                ids[j] = 0xFFFFFFFFu;
-                if (i < total) {
-                    ids[j] = i < hist_len ? __ldg(hist + i) : a.extra_ids[i - hist_len];
+                q[j] = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+                if (i < n4) {
+                    q[j] = __ldg(h4 + i);
                 }
             }
 #pragma unroll
             for (int j = 0; j < HB; ++j) {
-                const uint32_t id = ids[j];
-                const bool mine = id >= c.lo && id < c.hi;
-                if (mine) {
-                    // Real histories repeat a few ids very often: skip the
-                    // atomic when the bit is already up.
-                    const uint32_t off = id - c.lo;
-                    const uint32_t bit = 1u << (off & 31u);
-                    if (!(*reinterpret_cast<volatile uint32_t *>(&seen[off >> 5]) & bit)) {
-                        atomicOr(&seen[off >> 5], bit);
-                    }
-                }
-                if (c.need_counts) {
-                    // One global atomic per distinct id of the warp.
-                    const unsigned live = __ballot_sync(0xFFFFFFFFu, mine);
-                    if (mine) {
-                        const unsigned peers = __match_any_sync(live, id);
-                        if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
-                            atomicAdd(counts_rw + id, (uint32_t)__popc(peers));
-                        }
-                    }
-                }
+                mark(q[j].x);
+                mark(q[j].y);
+                mark(q[j].z);
+                mark(q[j].w);
             }
+        }
+        const uint32_t total = hist_len + extra_len;
+        for (uint32_t i0 = n4 * 4u; i0 < total; i0 += NT) {
+            const uint32_t i = i0 + tid;
+            uint32_t id = 0xFFFFFFFFu;
+            if (i < total) {
+                id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
+            }
+            mark(id);
         }
     }
     if (c.has_special) {
@@ -1328,46 +1391,36 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 
     // ---- C0. the first round: a threshold from a fine histogram
     // The candidate buffer is still empty: its storage holds an 8192-bin
-    // histogram of the keys of the round's untouched logits. The bin in which
-    // the count from the top reaches k gives the first threshold; only the
-    // logits at or above it enter the buffer.
+    // histogram of the raw keys of the round's untouched logits. The bin in
+    // which the count from the top reaches k gives the first threshold.
     issue((uint32_t)(STAGES - 1));
     uint32_t *hist0 = sm->key;
     for (uint32_t b = tid; b < H0_BINS; b += NT) {
         hist0[b] = 0;
     }
     __syncthreads();
-    Frag<T> first;
-    const uint32_t base0 = c.lo + tid * GROUP;
-    const uint32_t nvalid0 = base0 < c.hi ? min(GROUP, c.hi - base0) : 0u;
-    if (VEC) {
-        cp_async_wait<STAGES - 1>();
+    Frag first;
+    fetch(0u, first);
+    {
+        const uint32_t base0 = c.lo + tid * GROUP;
+        const uint32_t nvalid0 = base0 < c.hi ? min(GROUP, c.hi - base0) : 0u;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            first.v[i] = ring[(0 * NT + tid) * NV + i];
-        }
-    } else {
-        load_frag_scalar<T>(first, row_ptr, base0, c.hi);
-    }
-    uint32_t keys0[GROUP];
-#pragma unroll
-    for (int e = 0; e < (int)GROUP; ++e) {
-        keys0[e] = 0;
-        if ((uint32_t)e < nvalid0) {
-            const uint32_t id = base0 + e;
-            keys0[e] = plain_key(frag_get<T>(first, e), c.T, c.argmax_mode);
-            // Possibly on the bias / ban list counts as touched (no list scan here).
-            const bool touched = (c.use_pen && seen_bit(c, id)) ||
-                                 (c.has_special &&
-                                  ((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u));
-            if (!touched) {
-                atomicAdd(&hist0[keys0[e] >> H0_SHIFT], 1u);
+        for (int e = 0; e < (int)GROUP; ++e) {
+            if ((uint32_t)e < nvalid0) {
+                const uint32_t id = base0 + e;
+                // Possibly on the bias / ban list counts as touched (no list scan here).
+                const bool touched = (c.use_pen && seen_bit(c, id)) ||
+                                     (c.has_special &&
+                                      ((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u));
+                if (!touched) {
+                    atomicAdd(&hist0[key_of(frag_get<T>(first, e)) >> H0_SHIFT], 1u);
+                }
             }
         }
     }
     __syncthreads();
-    find_bin<H0_BINS / NT>(sm, hist0, H0_BINS, c.k, true);  // sets sel_digit when k untouched logits exist
-    uint32_t kstar0 = 0;
+    find_bin<H0_BINS / NT>(sm, hist0, H0_BINS, c.k, true);  // sets sel_digit if k untouched logits exist
+    uint32_t edge0 = 0;
     {
         // The total is below k when find_bin found no bin: then no threshold.
         uint32_t total = 0;
@@ -1375,16 +1428,13 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             total += sm->warp_sums[w];
         }
         if (total >= c.k) {
-            const uint32_t edge = sm->sel_digit << H0_SHIFT;
-            kstar0 = edge > 0u ? edge - 1u : 0u;
+            edge0 = sm->sel_digit << H0_SHIFT;
         }
     }
     __syncthreads();  // the histogram is read: its storage becomes the buffer again
     if (tid == 0) {
-        sm->th_base = (kstar0 + 1u) >> 16;
-        if (kstar0 > 0u) {
-            set_threshold(sm, kstar0);
-        }
+        sm->th_base = edge0 >> 16;
+        set_raw_edge(sm, edge0);
     }
     LILY_STAMP(PH_ROUND0);
 
@@ -1420,46 +1470,40 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // Rounds run without block barriers. Every RGROUP rounds the block meets:
     // if a push found the buffer full, the buffer is cut back to the best k
     // and the refused elements of those rounds are offered again (re-read
-    // from global memory, one round at a time). The warps take turns
-    // tightening the threshold, one per round.
-    constexpr uint32_t RGROUP = 4;
+    // from global memory). On a thinning schedule of rounds one warp, a
+    // different one each time, tightens the threshold.
     const bool always_seen = c.use_pen && !c.monotone;  // penalties may raise a seen logit
-    uint32_t dropped = 0;  // 8 refused-element bits per round of the group
+    uint32_t dropped = 0;  // GROUP refused-element bits per round of the group
     for (uint32_t r = 0; r < nrounds; ++r) {
-        Frag<T> cur;
+        Frag cur;
         const uint32_t base = c.lo + r * ROUND + tid * GROUP;
         if (r == 0) {
             cur = first;
         } else {
             issue(r + STAGES - 1);
-            if (VEC) {
-                cp_async_wait<STAGES - 1>();
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    cur.v[i] = ring[((r % STAGES) * NT + tid) * NV + i];
-                }
-            } else {
-                load_frag_scalar<T>(cur, row_ptr, base, c.hi);
-            }
+            fetch(r, cur);
         }
         const float c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
         if (r < nfull) {
-            // Every thread holds eight valid logits.
-            bool look = !(frag_max(cur) <= c_raw);
+            bool look = !(frag_max<T>(cur) <= c_raw);
             if (always_seen && !look) {
                 const uint32_t off = base - c.lo;
-                look = ((seen[off >> 5] >> (off & 31u)) & 0xFFu) != 0u;
+                look = ((seen[off >> 5] >> (off & 31u)) & ((1u << GROUP) - 1u)) != 0u;
             }
             if (look) {
-                dropped |= process_frag<T>(sm, c, cur, base, 0xFFu, c_raw, always_seen)
-                           << (8u * (r % RGROUP));
+                dropped |= process_frag<T>(sm, c, cur, base, (1u << GROUP) - 1u, c_raw, always_seen)
+                           << (GROUP * (r % RGROUP));
             }
         } else if (base < c.hi) {
             const uint32_t nvalid = min(GROUP, c.hi - base);
             dropped |= process_frag<T>(sm, c, cur, base, (1u << nvalid) - 1u, c_raw, always_seen)
-                       << (8u * (r % RGROUP));
+                       << (GROUP * (r % RGROUP));
         }
-        if ((tid >> 5) == (r & (NT / 32 - 1u))) {
+        // Rounds 0, 1, 2, 3, 4, 6, 8, 12, 16, 24, ...: the threshold moves
+        // ever more slowly as the row goes by.
+        const uint32_t r3 = r / 3u;
+        const bool due = r < 5u || (r & (r - 1u)) == 0u || (r3 * 3u == r && (r3 & (r3 - 1u)) == 0u);
+        if (due && (tid >> 5) == (r & (NT / 32 - 1u))) {
             // The lanes may come out of the divergent pushes apart: meet
             // first, then let ONE lane's reading decide for the whole warp
             // (the flag can change between two lanes' readings).
@@ -1478,7 +1522,8 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->overflow))) {
                 compact(sm);
                 // What is left to offer fits at once when the refused elements
-                // are fewer than the room the selection made.
+                // are fewer than the room the selection made; otherwise one
+                // element per thread at a time, with room made in between.
                 if (tid == 0) {
                     sm->cnt = 0;
                 }
@@ -1486,21 +1531,34 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 atomicAdd(&sm->cnt, (uint32_t)__popc(dropped));
                 __syncthreads();
                 const bool at_once = sm->n + sm->cnt <= CAP;
-                for (uint32_t rr = g0; rr <= r; ++rr) {
-                    const uint32_t m = (dropped >> (8u * (rr - g0))) & 0xFFu;
-                    if (m != 0u) {
-                        Frag<T> again;
-                        const uint32_t b2 = c.lo + rr * ROUND + tid * GROUP;
-                        load_frag_scalar<T>(again, row_ptr, b2, c.hi);
-                        process_frag<T>(sm, c, again, b2, m, sm->c_raw, always_seen);
+                for (uint32_t b = 0; b < 32u; ++b) {
+                    const bool mine = (dropped >> b) & 1u;
+                    if (!at_once) {
+                        if (!__syncthreads_or(mine)) {
+                            continue;
+                        }
+                        if (*reinterpret_cast<volatile uint32_t *>(&sm->n) > CAP - NT) {
+                            __syncthreads();
+                            compact(sm);
+                        }
                     }
-                    // Otherwise: room for a whole round before the next one.
-                    if (!at_once &&
-                        __syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->n) >
-                                         CAP - ROUND)) {
-                        compact(sm);
+                    if (mine) {
+                        const uint32_t rr = g0 + b / GROUP;
+                        const uint32_t id = c.lo + rr * ROUND + tid * GROUP + (b % GROUP);
+                        Frag one;
+                        one.v[0] = make_uint4(__float_as_uint(widen(row_ptr[id])), 0, 0, 0);
+                        one.v[1] = make_uint4(0, 0, 0, 0);
+                        if (sizeof(T) == 2) {
+                            // frag_get reads element 0 from the low half-word.
+                            one.v[0].x = (uint32_t)reinterpret_cast<const uint16_t *>(row_ptr)[id];
+                        }
+                        // No second test against the threshold: a refused element
+                        // may tie with the k-th key and win the tie by its lower id.
+                        process_frag<T>(sm, c, one, id, 1u, __uint_as_float(0x7FC00000u),
+                                        always_seen);
                     }
                 }
+                __syncthreads();
             }
             dropped = 0;
         }
