@@ -137,6 +137,7 @@ struct alignas(16) SmemFixed {
     uint32_t tid[KCAP];   // select's histogram / staging; later the prefix sums
     uint32_t thist[TH_BINS];
     uint32_t warp_sums[NT / 32];
+    uint4 wscratch[NT / 32][2];  // per warp: one thread's fragment, looked at by 16 lanes
     uint32_t sp_ids[SP_SMEM];
     float sp_vals[SP_SMEM];
     uint32_t n;      // buffered candidates
@@ -1404,15 +1405,41 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     {
         const uint32_t base0 = c.lo + tid * GROUP;
         const uint32_t nvalid0 = base0 < c.hi ? min(GROUP, c.hi - base0) : 0u;
+        // Which of the thread's logits are touched (in the history, or
+        // possibly on the bias / ban list: the bloom filter, no list scan).
+        uint32_t touched = 0;
+        if (c.use_pen && nvalid0 > 0u) {
+            const uint32_t off = base0 - c.lo;
+            touched = (seen[off >> 5] >> (off & 31u)) & ((1u << GROUP) - 1u);
+        }
+        if (c.has_special) {
 #pragma unroll
-        for (int e = 0; e < (int)GROUP; ++e) {
-            if ((uint32_t)e < nvalid0) {
+            for (int e = 0; e < (int)GROUP; ++e) {
                 const uint32_t id = base0 + e;
-                // Possibly on the bias / ban list counts as touched (no list scan here).
-                const bool touched = (c.use_pen && seen_bit(c, id)) ||
-                                     (c.has_special &&
-                                      ((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u));
-                if (!touched) {
+                touched |= ((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u) << e;
+            }
+        }
+        if (c.k <= 128u) {
+            // Small k: the k-th largest of the 512 per-thread maxima (over
+            // untouched logits) is nearly the k-th largest logit, and costs
+            // one histogram update per thread instead of one per logit.
+            float best = neg_inf();
+            bool any = false;
+#pragma unroll
+            for (int e = 0; e < (int)GROUP; ++e) {
+                if ((uint32_t)e < nvalid0 && !((touched >> e) & 1u)) {
+                    const float l = frag_get<T>(first, e);
+                    best = any ? max_nan_f32(best, l) : l;
+                    any = true;
+                }
+            }
+            if (any) {
+                atomicAdd(&hist0[key_of(best) >> H0_SHIFT], 1u);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < (int)GROUP; ++e) {
+                if ((uint32_t)e < nvalid0 && !((touched >> e) & 1u)) {
                     atomicAdd(&hist0[key_of(frag_get<T>(first, e)) >> H0_SHIFT], 1u);
                 }
             }
@@ -1484,20 +1511,63 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             fetch(r, cur);
         }
         const float c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
-        if (r < nfull) {
-            bool look = !(frag_max<T>(cur) <= c_raw);
-            if (always_seen && !look) {
-                const uint32_t off = base - c.lo;
-                look = ((seen[off >> 5] >> (off & 31u)) & ((1u << GROUP) - 1u)) != 0u;
+        // A thread is hit when its largest logit beats the threshold (in the
+        // last, partial round: when it holds any logit at all).
+        bool hit = r < nfull ? !(frag_max<T>(cur) <= c_raw) : base < c.hi;
+        if (always_seen && !hit && r < nfull) {
+            const uint32_t off = base - c.lo;
+            hit = ((seen[off >> 5] >> (off & 31u)) & ((1u << GROUP) - 1u)) != 0u;
+        }
+        // Hits are rare and scattered: the warp takes the hit threads one at
+        // a time, the hit thread parks its 32 bytes in the warp's scratch and
+        // lanes 0..GROUP-1 look at one logit each.
+        unsigned hits = __ballot_sync(0xFFFFFFFFu, hit);
+        while (hits != 0u) {
+            const int src = __ffs(hits) - 1;
+            hits &= hits - 1u;
+            const uint32_t lane = tid & 31u;
+            uint4 *scr = sm->wscratch[tid >> 5];
+            if ((int)lane == src) {
+                scr[0] = cur.v[0];
+                scr[1] = cur.v[1];
             }
-            if (look) {
-                dropped |= process_frag<T>(sm, c, cur, base, (1u << GROUP) - 1u, c_raw, always_seen)
-                           << (GROUP * (r % RGROUP));
+            __syncwarp();
+            const uint32_t sbase = __shfl_sync(0xFFFFFFFFu, base, src);
+            bool refused = false;
+            if (lane < GROUP) {
+                const uint32_t id = sbase + lane;
+                float l;
+                if (sizeof(T) == 2) {
+                    l = __uint_as_float(
+                        (uint32_t)reinterpret_cast<const uint16_t *>(scr)[lane] << 16);
+                } else {
+                    l = __uint_as_float(reinterpret_cast<const uint32_t *>(scr)[lane]);
+                }
+                if (id < c.hi) {
+                    const bool seen_here = c.use_pen && seen_bit(c, id);
+                    if ((!(l <= c_raw) || (always_seen && seen_here)) &&
+                        !(c.has_special && is_special(sm, c, id))) {
+                        if (push(sm, __float_as_uint(l), id)) {
+                            if (!seen_here) {
+                                // An untouched logit counts towards the next threshold.
+                                const uint32_t k16 = key_of(l) >> 16;
+                                const uint32_t b16 = sm->th_base;
+                                if (k16 >= b16) {
+                                    atomicAdd(&sm->thist[min(k16 - b16, TH_BINS - 1u)], 1u);
+                                    sm->th_new = 1;
+                                }
+                            }
+                        } else {
+                            refused = true;
+                        }
+                    }
+                }
             }
-        } else if (base < c.hi) {
-            const uint32_t nvalid = min(GROUP, c.hi - base);
-            dropped |= process_frag<T>(sm, c, cur, base, (1u << nvalid) - 1u, c_raw, always_seen)
-                       << (GROUP * (r % RGROUP));
+            const unsigned rb = __ballot_sync(0xFFFFFFFFu, refused);
+            if ((int)lane == src) {
+                dropped |= rb << (GROUP * (r % RGROUP));
+            }
+            __syncwarp();  // the scratch is free for the next hit thread
         }
         // Rounds 0, 1, 2, 3, 4, 6, 8, 12, 16, 24, ...: the threshold moves
         // ever more slowly as the row goes by.
