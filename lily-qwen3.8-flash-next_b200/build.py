@@ -48,7 +48,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", LIB, *sources()]
+    extra = os.environ.get("LILY_NVCC_EXTRA", "").split()  # e.g. -DLILY_DEBUG for device printf
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", INCLUDE, "-o", LIB, *sources()]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

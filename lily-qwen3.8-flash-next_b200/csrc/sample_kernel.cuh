@@ -30,6 +30,9 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#ifdef LILY_DEBUG
+#include <cstdio>
+#endif
 
 #include "../../include/lily_sampler.h"
 #include "lily_math.cuh"
@@ -137,7 +140,6 @@ struct alignas(16) SmemFixed {
     uint32_t tid[KCAP];   // select's histogram / staging; later the prefix sums
     uint32_t thist[TH_BINS];
     uint32_t warp_sums[NT / 32];
-    uint4 wscratch[NT / 32][2];  // per warp: one thread's fragment, looked at by 16 lanes
     uint32_t sp_ids[SP_SMEM];
     float sp_vals[SP_SMEM];
     uint32_t n;      // buffered candidates
@@ -161,6 +163,9 @@ struct alignas(16) SmemFixed {
     float p_d;
     float q_d;
     uint32_t bloom[32];
+#ifdef LILY_DEBUG
+    uint32_t dbg_hits, dbg_hit_warps, dbg_tighten;
+#endif
     RowCtx ctx;  // the row's parameters, for the out-of-line helpers
 };
 
@@ -325,6 +330,12 @@ __device__ __noinline__ void filter_adjust(SmemFixed *sm) {
     }
     __syncthreads();
     if (tid == 0) {
+#ifdef LILY_DEBUG
+        if (blockIdx.y < 2) {
+            printf("filter_adjust: n %u alive %u hits %u hit_warp_rounds %u tightens %u c_raw %g\n", n,
+                   sm->cnt, sm->dbg_hits, sm->dbg_hit_warps, sm->dbg_tighten, sm->c_raw);
+        }
+#endif
         sm->n = sm->cnt;
         sm->n_adj = sm->cnt;
     }
@@ -520,6 +531,10 @@ __device__ __noinline__ void select_topk(SmemFixed *sm, uint32_t n, uint32_t k) 
     if (tid == 0) {
         if (sm->cnt != k) {
             sm->err = ROW_INTERNAL;
+#ifdef LILY_DEBUG
+            printf("select_topk: n %u k %u cnt %u kstar %08x istar %08x count_eq %u remaining %u\n", n, k,
+                   sm->cnt, kstar, istar, count_eq, remaining);
+#endif
         }
         sm->n = k;
         sm->n_adj = k;
@@ -904,7 +919,9 @@ __device__ __noinline__ void tighten(SmemFixed *sm) {
             if (cum >= k) {
                 // (The top bin also holds everything above it; its lower
                 // edge is as valid a bound.)
-                set_raw_edge(sm, (base + bin) << 16);
+                if (base + bin <= 0xFFFFu) {
+                    set_raw_edge(sm, (base + bin) << 16);
+                }
                 break;
             }
         }
@@ -1053,26 +1070,52 @@ __device__ __forceinline__ void load_frag_scalar(Frag &f, const T *row, uint32_t
     }
 }
 
-// One thread's logits of a round: those in `mask` that beat the raw
-// threshold (or, when penalties may raise a logit, are in the history) go
-// into the buffer as raw bits; ids on the bias / ban list were handled up
-// front and are skipped. Untouched logits also count in the tightening
-// histogram. Returns the mask of elements the full buffer refused.
+// Which of a fragment's logits beat the raw threshold (a NaN always does).
 template <typename T>
-__device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c, const Frag &cur,
-                                                 uint32_t base, uint32_t mask, float c_raw,
-                                                 bool always_seen) {
-    constexpr int G = (int)Geo<T>::GROUP;
-    uint32_t pass = 0;
+__device__ __forceinline__ uint32_t pass_mask(const Frag &f, float c_raw);
+
+template <>
+__device__ __forceinline__ uint32_t pass_mask<float>(const Frag &f, float c_raw) {
+    uint32_t m = 0;
 #pragma unroll
-    for (int e = 0; e < G; ++e) {
-        pass |= (!(frag_get<T>(cur, e) <= c_raw) ? 1u : 0u) << e;
+    for (int e = 0; e < 8; ++e) {
+        m |= (!(frag_get<float>(f, e) <= c_raw) ? 1u : 0u) << e;
     }
-    if (always_seen) {
-        const uint32_t off = base - c.lo;  // a multiple of GROUP: the bits sit in one word
-        pass |= (c.seen[off >> 5] >> (off & 31u)) & ((1u << G) - 1u);
+    return m;
+}
+
+template <>
+__device__ __forceinline__ uint32_t pass_mask<__nv_bfloat16>(const Frag &f, float c_raw) {
+    // For a bf16 logit l: l > c  <=>  l > (the largest bf16 not above c), so
+    // two logits are tested at a time against that value, unordered-greater
+    // (a NaN on either side passes).
+    uint32_t cb = __float_as_uint(c_raw);
+    if (c_raw == c_raw) {
+        const uint32_t low = cb & 0xFFFFu;
+        cb &= 0xFFFF0000u;
+        if ((cb >> 31) && low != 0u) {
+            cb += 0x10000u;  // negative: truncation went up, step down
+        }
     }
-    pass &= mask;
+    const uint32_t c2 = (cb >> 16) | (cb & 0xFFFF0000u);
+    const uint32_t w[8] = {f.v[0].x, f.v[0].y, f.v[0].z, f.v[0].w,
+                           f.v[1].x, f.v[1].y, f.v[1].z, f.v[1].w};
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        uint32_t d;
+        asm("set.gtu.u32.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(w[i]), "r"(c2));
+        m |= ((d & 1u) | ((d >> 15) & 2u)) << (2 * i);
+    }
+    return m;
+}
+
+// Pushes the logits of `pass` as raw bits; ids on the bias / ban list were
+// handled up front and are skipped. Untouched logits also count in the
+// tightening histogram. Returns the mask of elements the full buffer refused.
+template <typename T>
+__device__ __forceinline__ uint32_t push_masked(SmemFixed *sm, const RowCtx &c, const Frag &cur,
+                                                uint32_t base, uint32_t pass) {
     uint32_t failed = 0;
     while (pass != 0u) {
         const uint32_t e = (uint32_t)__ffs(pass) - 1u;
@@ -1086,7 +1129,9 @@ __device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c,
             failed |= 1u << e;
             continue;
         }
-        if (!(c.use_pen && seen_bit(c, id))) {
+        // An untouched logit counts towards the next threshold. (A NaN never
+        // does: its raw key is the highest, its adjusted key is not.)
+        if (!(c.use_pen && seen_bit(c, id)) && l == l) {
             const uint32_t k16 = key_of(l) >> 16;
             const uint32_t b16 = sm->th_base;
             if (k16 >= b16) {
@@ -1096,6 +1141,22 @@ __device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c,
         }
     }
     return failed;
+}
+
+// One thread's logits of a round: those in `mask` that beat the raw
+// threshold (or, when penalties may raise a logit, are in the history) are
+// pushed. Returns the mask of elements the full buffer refused.
+template <typename T>
+__device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c, const Frag &cur,
+                                                 uint32_t base, uint32_t mask, float c_raw,
+                                                 bool always_seen) {
+    constexpr int G = (int)Geo<T>::GROUP;
+    uint32_t pass = pass_mask<T>(cur, c_raw);
+    if (always_seen) {
+        const uint32_t off = base - c.lo;  // a multiple of GROUP: the bits sit in one word
+        pass |= (c.seen[off >> 5] >> (off & 31u)) & ((1u << G) - 1u);
+    }
+    return push_masked<T>(sm, c, cur, base, pass & mask);
 }
 
 // Block-wide: adjusts what the stream pushed, keeps the exact best k and
@@ -1299,6 +1360,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         sm->th_base = 0;
         sm->th_new = 0;
         sm->overflow = 0;
+#ifdef LILY_DEBUG
+        sm->dbg_hits = sm->dbg_hit_warps = sm->dbg_tighten = 0;
+#endif
     }
     if (tid < 32) {
         sm->bloom[tid] = 0;
@@ -1428,9 +1492,13 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 #pragma unroll
             for (int e = 0; e < (int)GROUP; ++e) {
                 if ((uint32_t)e < nvalid0 && !((touched >> e) & 1u)) {
+                    // A NaN never counts: its raw key is the highest, its
+                    // adjusted key is not (an error row, or never the argmax).
                     const float l = frag_get<T>(first, e);
-                    best = any ? max_nan_f32(best, l) : l;
-                    any = true;
+                    if (l == l) {
+                        best = any ? fmaxf(best, l) : l;
+                        any = true;
+                    }
                 }
             }
             if (any) {
@@ -1439,8 +1507,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         } else {
 #pragma unroll
             for (int e = 0; e < (int)GROUP; ++e) {
-                if ((uint32_t)e < nvalid0 && !((touched >> e) & 1u)) {
-                    atomicAdd(&hist0[key_of(frag_get<T>(first, e)) >> H0_SHIFT], 1u);
+                const float l = frag_get<T>(first, e);
+                if ((uint32_t)e < nvalid0 && !((touched >> e) & 1u) && l == l) {
+                    atomicAdd(&hist0[key_of(l) >> H0_SHIFT], 1u);
                 }
             }
         }
@@ -1511,63 +1580,18 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             fetch(r, cur);
         }
         const float c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
-        // A thread is hit when its largest logit beats the threshold (in the
-        // last, partial round: when it holds any logit at all).
+        // A thread looks closer when its largest logit beats the threshold
+        // (in the last, partial round: when it holds any logit at all).
         bool hit = r < nfull ? !(frag_max<T>(cur) <= c_raw) : base < c.hi;
         if (always_seen && !hit && r < nfull) {
             const uint32_t off = base - c.lo;
             hit = ((seen[off >> 5] >> (off & 31u)) & ((1u << GROUP) - 1u)) != 0u;
         }
-        // Hits are rare and scattered: the warp takes the hit threads one at
-        // a time, the hit thread parks its 32 bytes in the warp's scratch and
-        // lanes 0..GROUP-1 look at one logit each.
-        unsigned hits = __ballot_sync(0xFFFFFFFFu, hit);
-        while (hits != 0u) {
-            const int src = __ffs(hits) - 1;
-            hits &= hits - 1u;
-            const uint32_t lane = tid & 31u;
-            uint4 *scr = sm->wscratch[tid >> 5];
-            if ((int)lane == src) {
-                scr[0] = cur.v[0];
-                scr[1] = cur.v[1];
-            }
-            __syncwarp();
-            const uint32_t sbase = __shfl_sync(0xFFFFFFFFu, base, src);
-            bool refused = false;
-            if (lane < GROUP) {
-                const uint32_t id = sbase + lane;
-                float l;
-                if (sizeof(T) == 2) {
-                    l = __uint_as_float(
-                        (uint32_t)reinterpret_cast<const uint16_t *>(scr)[lane] << 16);
-                } else {
-                    l = __uint_as_float(reinterpret_cast<const uint32_t *>(scr)[lane]);
-                }
-                if (id < c.hi) {
-                    const bool seen_here = c.use_pen && seen_bit(c, id);
-                    if ((!(l <= c_raw) || (always_seen && seen_here)) &&
-                        !(c.has_special && is_special(sm, c, id))) {
-                        if (push(sm, __float_as_uint(l), id)) {
-                            if (!seen_here) {
-                                // An untouched logit counts towards the next threshold.
-                                const uint32_t k16 = key_of(l) >> 16;
-                                const uint32_t b16 = sm->th_base;
-                                if (k16 >= b16) {
-                                    atomicAdd(&sm->thist[min(k16 - b16, TH_BINS - 1u)], 1u);
-                                    sm->th_new = 1;
-                                }
-                            }
-                        } else {
-                            refused = true;
-                        }
-                    }
-                }
-            }
-            const unsigned rb = __ballot_sync(0xFFFFFFFFu, refused);
-            if ((int)lane == src) {
-                dropped |= rb << (GROUP * (r % RGROUP));
-            }
-            __syncwarp();  // the scratch is free for the next hit thread
+        if (hit) {
+            const uint32_t nvalid = min(GROUP, c.hi - base);
+            const uint32_t valid = nvalid >= 32u ? 0xFFFFFFFFu : (1u << nvalid) - 1u;
+            dropped |= process_frag<T>(sm, c, cur, base, valid, c_raw, always_seen)
+                       << (GROUP * (r % RGROUP));
         }
         // Rounds 0, 1, 2, 3, 4, 6, 8, 12, 16, 24, ...: the threshold moves
         // ever more slowly as the row goes by.
@@ -1584,6 +1608,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             }
             go = __shfl_sync(0xFFFFFFFFu, go, 0);
             if (go != 0u) {
+#ifdef LILY_DEBUG
+                if ((tid & 31u) == 0u) atomicAdd(&sm->dbg_tighten, 1u);
+#endif
                 tighten(sm);
             }
         }
@@ -1607,8 +1634,10 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                         if (!__syncthreads_or(mine)) {
                             continue;
                         }
-                        if (*reinterpret_cast<volatile uint32_t *>(&sm->n) > CAP - NT) {
-                            __syncthreads();
+                        // Nobody pushes between the two barriers: every thread
+                        // reads the same count and takes the same branch.
+                        if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->n) >
+                                             CAP - NT)) {
                             compact(sm);
                         }
                     }

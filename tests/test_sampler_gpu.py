@@ -102,6 +102,20 @@ def test_argmax_route_ignores_nan_and_ties_zeros(cuda, lily, W):
     assert list(res.ids) == [9, 100, 0]
     assert [oracle.argmax(x[r]) for r in range(3)] == [9, 100, 0]
     s.close()
+    # The same with several rounds and several slices per row, the NaN in the
+    # first round, in a later one, and at the very end.
+    for vocab in (4096, 5000, 40_000):
+        for at in (5, vocab // 2, vocab - 1):
+            y = np.full((1, vocab), -1.0, dtype=np.float32)
+            y[0, at] = np.nan
+            want = 9 if at != 9 else 10
+            y[0, want] = 2.0
+            for bf16 in (False, True):
+                b = W.Batch(W.to_bf16_bits(y) if bf16 else y, bf16, [dict()], np.zeros(1, np.float32))
+                s = lily.SamplerScratch(vocab)
+                res = run_batch(cuda, lily, s, b)
+                assert res.ids[0] == want and res.status[0] == 0, (vocab, at, bf16)
+                s.close()
 
 
 @pytest.mark.parametrize("bf16", [False, True])
