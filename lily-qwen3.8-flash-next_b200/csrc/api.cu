@@ -5,6 +5,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -208,6 +209,10 @@ void base_args(const lily_sampler *h, lily::KArgs *a) {
     a->tickets = h->tickets;
     a->status_word = h->status_word;
     a->phase_clocks = h->phase_clocks;
+#ifdef LILY_DEBUG
+    const char *stop = std::getenv("LILY_DEBUG_STOP");
+    a->debug_stop = stop ? (uint32_t)std::atoi(stop) : 0u;
+#endif
 }
 
 int32_t ensure_counts_scratch(lily_sampler *h) {

@@ -32,6 +32,7 @@
 #include <stdint.h>
 #ifdef LILY_DEBUG
 #include <cstdio>
+static __device__ const bool a_debug_print = false;
 #endif
 
 #include "../../include/lily_sampler.h"
@@ -115,6 +116,7 @@ struct KArgs {
     uint32_t *tickets;             // [max_rows], zero between launches
     uint32_t *status_word;
     long long *phase_clocks;       // optional [max_rows, MAX_SLICES, LILY_PHASES] SM clock stamps
+    uint32_t debug_stop;           // debug builds only: leave after this phase (0 = run all)
     SpecArgs spec;
 };
 
@@ -331,7 +333,7 @@ __device__ __noinline__ void filter_adjust(SmemFixed *sm) {
     __syncthreads();
     if (tid == 0) {
 #ifdef LILY_DEBUG
-        if (blockIdx.y < 2) {
+        if (blockIdx.y < 2 && a_debug_print) {
             printf("filter_adjust: n %u alive %u hits %u hit_warp_rounds %u tightens %u c_raw %g\n", n,
                    sm->cnt, sm->dbg_hits, sm->dbg_hit_warps, sm->dbg_tighten, sm->c_raw);
         }
@@ -1115,12 +1117,14 @@ __device__ __forceinline__ uint32_t pass_mask<__nv_bfloat16>(const Frag &f, floa
 // tightening histogram. Returns the mask of elements the full buffer refused.
 template <typename T>
 __device__ __forceinline__ uint32_t push_masked(SmemFixed *sm, const RowCtx &c, const Frag &cur,
-                                                uint32_t base, uint32_t pass) {
+                                                const T *in_smem, uint32_t base, uint32_t pass) {
     uint32_t failed = 0;
     while (pass != 0u) {
         const uint32_t e = (uint32_t)__ffs(pass) - 1u;
         pass &= pass - 1u;
-        const float l = frag_pick<T>(cur, e);
+        // The fragment still sits in the thread's ring slot: one load picks
+        // element e (without it: a chain of selects over the registers).
+        const float l = in_smem != nullptr ? widen(in_smem[e]) : frag_pick<T>(cur, e);
         const uint32_t id = base + e;
         if (c.has_special && is_special(sm, c, id)) {
             continue;
@@ -1148,15 +1152,15 @@ __device__ __forceinline__ uint32_t push_masked(SmemFixed *sm, const RowCtx &c, 
 // pushed. Returns the mask of elements the full buffer refused.
 template <typename T>
 __device__ __forceinline__ uint32_t process_frag(SmemFixed *sm, const RowCtx &c, const Frag &cur,
-                                                 uint32_t base, uint32_t mask, float c_raw,
-                                                 bool always_seen) {
+                                                 const T *in_smem, uint32_t base, uint32_t mask,
+                                                 float c_raw, bool always_seen) {
     constexpr int G = (int)Geo<T>::GROUP;
     uint32_t pass = pass_mask<T>(cur, c_raw);
     if (always_seen) {
         const uint32_t off = base - c.lo;  // a multiple of GROUP: the bits sit in one word
         pass |= (c.seen[off >> 5] >> (off & 31u)) & ((1u << G) - 1u);
     }
-    return push_masked<T>(sm, c, cur, base, pass & mask);
+    return push_masked<T>(sm, c, cur, in_smem, base, pass & mask);
 }
 
 // Block-wide: adjusts what the stream pushed, keeps the exact best k and
@@ -1385,25 +1389,36 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     __syncthreads();
     LILY_STAMP(PH_START);
     if (hist_len + extra_len > 0u) {
+        const uint32_t lo = c.lo;
+        const uint32_t width = c.hi - c.lo;
+        // One unsigned compare covers both ends of the slice. Real histories
+        // repeat a few ids very often: the atomic is skipped when the bit is
+        // already up.
         auto mark = [&](uint32_t id) {
-            const bool mine = id >= c.lo && id < c.hi;
-            if (mine) {
-                // Real histories repeat a few ids very often: skip the atomic
-                // when the bit is already up.
-                const uint32_t off = id - c.lo;
+            const uint32_t off = id - lo;
+            if (off < width) {
                 const uint32_t bit = 1u << (off & 31u);
-                if (!(*reinterpret_cast<volatile uint32_t *>(&seen[off >> 5]) & bit)) {
-                    atomicOr(&seen[off >> 5], bit);
+                uint32_t *word = &seen[off >> 5];
+                if (!(*reinterpret_cast<volatile uint32_t *>(word) & bit)) {
+                    atomicOr(word, bit);
                 }
             }
-            if (c.need_counts) {
-                // One global atomic per distinct id of the warp.
-                const unsigned live = __ballot_sync(0xFFFFFFFFu, mine);
-                if (mine) {
-                    const unsigned peers = __match_any_sync(live, id);
-                    if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
-                        atomicAdd(counts_rw + id, (uint32_t)__popc(peers));
-                    }
+        };
+        // With the frequency penalty the multiplicities go to the row's
+        // count table as well: one global atomic per distinct id of the warp.
+        auto mark_count = [&](uint32_t id) {
+            const uint32_t off = id - lo;
+            const bool mine = off < width;
+            const unsigned live = __ballot_sync(0xFFFFFFFFu, mine);
+            if (mine) {
+                const uint32_t bit = 1u << (off & 31u);
+                uint32_t *word = &seen[off >> 5];
+                if (!(*reinterpret_cast<volatile uint32_t *>(word) & bit)) {
+                    atomicOr(word, bit);
+                }
+                const unsigned peers = __match_any_sync(live, id);
+                if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
+                    atomicAdd(counts_rw + id, (uint32_t)__popc(peers));
                 }
             }
         };
@@ -1422,12 +1437,22 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                     q[j] = __ldg(h4 + i);
                 }
             }
+            if (c.need_counts) {
 #pragma unroll
-            for (int j = 0; j < HB; ++j) {
-                mark(q[j].x);
-                mark(q[j].y);
-                mark(q[j].z);
-                mark(q[j].w);
+                for (int j = 0; j < HB; ++j) {
+                    mark_count(q[j].x);
+                    mark_count(q[j].y);
+                    mark_count(q[j].z);
+                    mark_count(q[j].w);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < HB; ++j) {
+                    mark(q[j].x);
+                    mark(q[j].y);
+                    mark(q[j].z);
+                    mark(q[j].w);
+                }
             }
         }
         const uint32_t total = hist_len + extra_len;
@@ -1437,7 +1462,11 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             if (i < total) {
                 id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
             }
-            mark(id);
+            if (c.need_counts) {
+                mark_count(id);
+            } else {
+                mark(id);
+            }
         }
     }
     if (c.has_special) {
@@ -1453,6 +1482,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     }
     __syncthreads();
     LILY_STAMP(PH_BITMAPS);
+#ifdef LILY_DEBUG
+    if (a.debug_stop == 1u) return;
+#endif
 
     // ---- C0. the first round: a threshold from a fine histogram
     // The candidate buffer is still empty: its storage holds an 8192-bin
@@ -1533,6 +1565,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         set_raw_edge(sm, edge0);
     }
     LILY_STAMP(PH_ROUND0);
+#ifdef LILY_DEBUG
+    if (a.debug_stop == 2u) return;
+#endif
 
     // ---- B. ids on the bias / ban lists, each once (adjusted right away)
     if (c.has_special) {
@@ -1566,38 +1601,85 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // Rounds run without block barriers. Every RGROUP rounds the block meets:
     // if a push found the buffer full, the buffer is cut back to the best k
     // and the refused elements of those rounds are offered again (re-read
-    // from global memory). On a thinning schedule of rounds one warp, a
-    // different one each time, tightens the threshold.
+    // from global memory). After those meetings, on a thinning schedule, one
+    // warp (a different one each time) tightens the threshold.
     const bool always_seen = c.use_pen && !c.monotone;  // penalties may raise a seen logit
     uint32_t dropped = 0;  // GROUP refused-element bits per round of the group
-    for (uint32_t r = 0; r < nrounds; ++r) {
-        Frag cur;
-        const uint32_t base = c.lo + r * ROUND + tid * GROUP;
-        if (r == 0) {
-            cur = first;
-        } else {
-            issue(r + STAGES - 1);
-            fetch(r, cur);
-        }
-        const float c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
-        // A thread looks closer when its largest logit beats the threshold
-        // (in the last, partial round: when it holds any logit at all).
-        bool hit = r < nfull ? !(frag_max<T>(cur) <= c_raw) : base < c.hi;
-        if (always_seen && !hit && r < nfull) {
+    float c_raw = sm->c_raw;
+    auto look = [&](const Frag &cur, uint32_t r, uint32_t base, bool full) {
+        // A thread looks closer when its largest logit beats the threshold (in
+        // a partial round: when it holds any logit at all).
+        c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
+#ifdef LILY_DEBUG
+        if (a.debug_stop == 5u) c_raw = -neg_inf();  // nothing passes: the bare streaming loop
+#endif
+        bool hit = full ? !(frag_max<T>(cur) <= c_raw) : base < c.hi;
+        if (always_seen && !hit && full) {
             const uint32_t off = base - c.lo;
             hit = ((seen[off >> 5] >> (off & 31u)) & ((1u << GROUP) - 1u)) != 0u;
         }
         if (hit) {
             const uint32_t nvalid = min(GROUP, c.hi - base);
             const uint32_t valid = nvalid >= 32u ? 0xFFFFFFFFu : (1u << nvalid) - 1u;
-            dropped |= process_frag<T>(sm, c, cur, base, valid, c_raw, always_seen)
+            const T *slot = VEC ? reinterpret_cast<const T *>(&ring[((r % STAGES) * NT + tid) * 2u])
+                                : nullptr;
+            dropped |= process_frag<T>(sm, c, cur, slot, base, valid, c_raw, always_seen)
                        << (GROUP * (r % RGROUP));
         }
-        // Rounds 0, 1, 2, 3, 4, 6, 8, 12, 16, 24, ...: the threshold moves
-        // ever more slowly as the row goes by.
-        const uint32_t r3 = r / 3u;
-        const bool due = r < 5u || (r & (r - 1u)) == 0u || (r3 * 3u == r && (r3 & (r3 - 1u)) == 0u);
-        if (due && (tid >> 5) == (r & (NT / 32 - 1u))) {
+    };
+    auto meet = [&](uint32_t r) {
+        // End of a group of rounds (r is its last round).
+        const uint32_t g0 = r - (r % RGROUP);
+        const uint32_t g = r / RGROUP;
+        if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->overflow))) {
+            compact(sm);
+            // What is left to offer fits at once when the refused elements
+            // are fewer than the room the selection made; otherwise one
+            // element per thread at a time, with room made in between.
+            if (tid == 0) {
+                sm->cnt = 0;
+            }
+            __syncthreads();
+            atomicAdd(&sm->cnt, (uint32_t)__popc(dropped));
+            __syncthreads();
+            const bool at_once = sm->n + sm->cnt <= CAP;
+            for (uint32_t b = 0; b < 32u; ++b) {
+                const bool mine = (dropped >> b) & 1u;
+                if (!at_once) {
+                    if (!__syncthreads_or(mine)) {
+                        continue;
+                    }
+                    // Nobody pushes between the two barriers: every thread
+                    // reads the same count and takes the same branch.
+                    if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->n) >
+                                         CAP - NT)) {
+                        compact(sm);
+                    }
+                }
+                if (mine) {
+                    const uint32_t rr = g0 + b / GROUP;
+                    const uint32_t id = c.lo + rr * ROUND + tid * GROUP + (b % GROUP);
+                    Frag one;
+                    one.v[0] = make_uint4(__float_as_uint(widen(row_ptr[id])), 0, 0, 0);
+                    one.v[1] = make_uint4(0, 0, 0, 0);
+                    if (sizeof(T) == 2) {
+                        // frag_get reads element 0 from the low half-word.
+                        one.v[0].x = (uint32_t)reinterpret_cast<const uint16_t *>(row_ptr)[id];
+                    }
+                    // No second test against the threshold: a refused element
+                    // may tie with the k-th key and win the tie by its lower id.
+                    process_frag<T>(sm, c, one, nullptr, id, 1u, __uint_as_float(0x7FC00000u),
+                                    always_seen);
+                }
+            }
+            __syncthreads();
+        }
+        dropped = 0;
+        // Groups 0, 1, 2, 3, 4, 6, 8, 12, 16, ...: the threshold moves ever
+        // more slowly as the row goes by.
+        const uint32_t g3 = g / 3u;
+        const bool due = g < 5u || (g & (g - 1u)) == 0u || (g3 * 3u == g && (g3 & (g3 - 1u)) == 0u);
+        if (due && (tid >> 5) == (g & (NT / 32 - 1u))) {
             // The lanes may come out of the divergent pushes apart: meet
             // first, then let ONE lane's reading decide for the whole warp
             // (the flag can change between two lanes' readings).
@@ -1608,64 +1690,66 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             }
             go = __shfl_sync(0xFFFFFFFFu, go, 0);
             if (go != 0u) {
-#ifdef LILY_DEBUG
-                if ((tid & 31u) == 0u) atomicAdd(&sm->dbg_tighten, 1u);
-#endif
                 tighten(sm);
             }
         }
-        if ((r % RGROUP) == RGROUP - 1u || r == nrounds - 1u) {
-            const uint32_t g0 = r - (r % RGROUP);
-            if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->overflow))) {
-                compact(sm);
-                // What is left to offer fits at once when the refused elements
-                // are fewer than the room the selection made; otherwise one
-                // element per thread at a time, with room made in between.
-                if (tid == 0) {
-                    sm->cnt = 0;
-                }
-                __syncthreads();
-                atomicAdd(&sm->cnt, (uint32_t)__popc(dropped));
-                __syncthreads();
-                const bool at_once = sm->n + sm->cnt <= CAP;
-                for (uint32_t b = 0; b < 32u; ++b) {
-                    const bool mine = (dropped >> b) & 1u;
-                    if (!at_once) {
-                        if (!__syncthreads_or(mine)) {
-                            continue;
-                        }
-                        // Nobody pushes between the two barriers: every thread
-                        // reads the same count and takes the same branch.
-                        if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->n) >
-                                             CAP - NT)) {
-                            compact(sm);
-                        }
-                    }
-                    if (mine) {
-                        const uint32_t rr = g0 + b / GROUP;
-                        const uint32_t id = c.lo + rr * ROUND + tid * GROUP + (b % GROUP);
-                        Frag one;
-                        one.v[0] = make_uint4(__float_as_uint(widen(row_ptr[id])), 0, 0, 0);
-                        one.v[1] = make_uint4(0, 0, 0, 0);
-                        if (sizeof(T) == 2) {
-                            // frag_get reads element 0 from the low half-word.
-                            one.v[0].x = (uint32_t)reinterpret_cast<const uint16_t *>(row_ptr)[id];
-                        }
-                        // No second test against the threshold: a refused element
-                        // may tie with the k-th key and win the tie by its lower id.
-                        process_frag<T>(sm, c, one, id, 1u, __uint_as_float(0x7FC00000u),
-                                        always_seen);
-                    }
-                }
-                __syncthreads();
-            }
-            dropped = 0;
+    };
+
+    // Round 0 is in `first` already.
+    if (nrounds > 0u) {
+        look(first, 0u, c.lo + tid * GROUP, nfull > 0u);
+        if (RGROUP == 1u || nrounds == 1u) {
+            meet(0u);
         }
+    }
+    // The full rounds: the hot loop.
+    {
+        const uint32_t ring_me = (uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES;
+        const char *src = my_src + (size_t)STAGES * (ROUND * sizeof(T));  // round r + STAGES - 1, r = 1
+        uint32_t base = c.lo + ROUND + tid * GROUP;
+        for (uint32_t r = 1; r < nfull; ++r) {
+            if (VEC) {
+                // Prefetch round r + STAGES - 1 (STAGES == 2: the other slot).
+                if (r + STAGES - 1 < nfull) {
+                    const uint32_t dst = ring_me + ((r + STAGES - 1) % STAGES) * (NT * FRAG_BYTES);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src)
+                                 : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16u),
+                                 "l"(src + 16)
+                                 : "memory");
+                } else {
+                    issue(r + STAGES - 1);  // the partial round, or nothing: commits below too
+                }
+                if (r + STAGES - 1 < nfull) {
+                    cp_async_commit();
+                }
+                src += ROUND * sizeof(T);
+            }
+            Frag cur;
+            fetch(r, cur);
+            look(cur, r, base, true);
+            base += ROUND;
+            if ((r % RGROUP) == RGROUP - 1u || r == nrounds - 1u) {
+                meet(r);
+            }
+        }
+    }
+    // The last, partial round (if any).
+    if (nrounds > nfull && nfull > 0u) {
+        const uint32_t r = nfull;
+        issue(r + STAGES - 1);
+        Frag cur;
+        fetch(r, cur);
+        look(cur, r, c.lo + r * ROUND + tid * GROUP, false);
+        meet(r);
     }
     cp_async_wait<0>();
     __syncthreads();
 
     LILY_STAMP(PH_STREAM);
+#ifdef LILY_DEBUG
+    if (a.debug_stop == 3u) return;
+#endif
     if (tid < 32u && sm->th_new != 0u) {
         tighten(sm);
     }
@@ -1703,6 +1787,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         n = c.k;
     }
     LILY_STAMP(PH_LOCAL_SELECT);
+#ifdef LILY_DEBUG
+    if (a.debug_stop == 4u) return;
+#endif
 
     // ---- D. merge the slices
     if (n_slices > 1u) {
