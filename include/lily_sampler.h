@@ -224,6 +224,40 @@ typedef struct lily_sample_args {
 int32_t lily_sample_batch(lily_sampler_t *h, void *stream, const lily_sample_args_t *args);
 
 /*
+ * The same draw for callers that cannot allocate device memory. (No
+ * counterpart in the reference.)
+ *
+ * Some host programs run with allocation closed: an engine whose memory plan
+ * was fixed at start-up and hands every byte of the device to its own pool, a
+ * plugin loaded into a process that forbids cudaMalloc after initialisation,
+ * or code that must not disturb a stream capture in progress elsewhere with
+ * an allocation. lily_sampler_create (which allocates the scratch a handle
+ * owns) is of no use to them. This entry point takes no handle and calls no
+ * cudaMalloc / cudaFree or any other allocating routine: the scratch the
+ * kernel needs (the slices' candidate lists, their counters and tickets, the
+ * staged parameters) lives in one array of static device storage inside the
+ * library, LILY_NOALLOC_SCRATCH_BYTES large, which every GPU that loads the
+ * library holds until the process exits.
+ *
+ * Limits: rows <= LILY_NOALLOC_MAX_ROWS; `params` (and `steps`) HOST arrays;
+ * no histogram slots (`count_slots` must be NULL); a history-list row may not
+ * use a frequency penalty (that needs a vocabulary-sized count table): such
+ * calls are refused with LILY_ERR_CAPACITY. Results are the same as
+ * lily_sample_batch's.
+ *
+ * The first call on a device looks the array's device address up
+ * (cudaGetSymbolAddress) and raises the kernel's shared-memory limit; make it
+ * before any stream capture. All calls share the one array: it keeps the last
+ * call's contents (the entry point clears the words that must start at zero),
+ * and two calls that overlap on the GPU, on any streams, race on it.
+ * `vocab` is the row length; errors are written to err[0..err_cap).
+ */
+#define LILY_NOALLOC_MAX_ROWS 8u
+#define LILY_NOALLOC_SCRATCH_BYTES (LILY_NOALLOC_MAX_ROWS * (4096u * 8u + 128u * 4u + 64u) + 256u)
+int32_t lily_sample_batch_noalloc(void *stream, uint32_t vocab, const lily_sample_args_t *args,
+                                  char *err, uint32_t err_cap);
+
+/*
  * src/kernels/elementwise.rs:297-308 argmax_f32 for each row: first maximum,
  * lowest index on ties, NaN never wins.
  */

@@ -164,6 +164,8 @@ def lib():
                                        C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32,
                                        C.c_uint32, C.c_uint32]
         L.lily_debug_exp.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]
+        L.lily_sample_batch_noalloc.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(SampleArgs),
+                                                C.c_char_p, C.c_uint32]
         L.lily_sampler_read_phase_clocks.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = L
     return _lib
@@ -413,6 +415,54 @@ class SamplerScratch:
         """src/kernels/spec.rs:52-91."""
         self._check(lib().lily_spec_accept(self._h, _stream_ptr(stream), _ptr(draws), _ptr(ids),
                                            draws.numel(), _ptr(ctrl), pos0, ratio, chain, stride))
+
+
+NOALLOC_MAX_ROWS = 8
+
+
+def sample_batch_noalloc(vocab, logits, params, out_ids, *, uniforms=None, steps=None,
+                         history_ids=None, history_len=None, bias_ids=None, bias_vals=None,
+                         bias_len=None, ban_ids=None, ban_len=None, forced_ids=None,
+                         out_status=None, kept_n=None, kept_ids=None, kept_probs=None,
+                         stream=None):
+    """lily_sample_batch_noalloc: the draw of `SamplerScratch.sample_batch` for hosts
+    that may not allocate device memory. No handle: the kernel's scratch is static
+    device storage inside the library, shared by all calls (calls that overlap on
+    the GPU race on it). `params` is a list of at most NOALLOC_MAX_ROWS
+    SamplingParams; histogram slots and a frequency penalty over a history list
+    are not available here."""
+    rows = logits.shape[0] if logits.dim() == 2 else 1
+    a = SampleArgs()
+    a.struct_size = C.sizeof(SampleArgs)
+    a.rows = rows
+    a.logits = _ptr(logits)
+    a.logits_dtype = _dtype_code(logits)
+    a.logits_ld = _ld(logits)
+    arr = (SamplingParams * rows)(*params)
+    a.params = C.cast(arr, C.c_void_p)
+    sarr = None
+    if steps is not None:
+        sarr = (C.c_uint32 * rows)(*[int(s) for s in steps])
+        a.steps = C.cast(sarr, C.c_void_p)
+    a.uniforms = _ptr(uniforms)
+    if history_ids is not None:
+        a.history_ids, a.history_len = _ptr(history_ids), _ptr(history_len)
+        a.history_ld = _ld(history_ids)
+    if bias_ids is not None:
+        a.bias_ids, a.bias_vals, a.bias_len = _ptr(bias_ids), _ptr(bias_vals), _ptr(bias_len)
+        a.bias_ld = _ld(bias_ids)
+    if ban_ids is not None:
+        a.ban_ids, a.ban_len = _ptr(ban_ids), _ptr(ban_len)
+        a.ban_ld = _ld(ban_ids)
+    a.forced_ids = _ptr(forced_ids)
+    a.out_ids, a.out_status = _ptr(out_ids), _ptr(out_status)
+    if kept_n is not None:
+        a.kept_n, a.kept_ids, a.kept_probs = _ptr(kept_n), _ptr(kept_ids), _ptr(kept_probs)
+        a.kept_ld = _ld(kept_ids)
+    err = C.create_string_buffer(256)
+    st = lib().lily_sample_batch_noalloc(_stream_ptr(stream), vocab, C.byref(a), err, len(err))
+    if st != OK:
+        raise LilyError(st, err.value.decode("utf-8", "replace"))
 
 
 # -- single-row conveniences with the reference's call shapes ------------------

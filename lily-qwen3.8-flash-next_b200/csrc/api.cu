@@ -854,6 +854,208 @@ int32_t lily_spec_accept(lily_sampler_t *h, void *stream_, const uint32_t *draws
     return LILY_OK;
 }
 
+// ------------------------------------------------ allocation-free draw --
+
+}  // extern "C"
+
+namespace {
+
+// Everything the kernel needs beyond its inputs and outputs, for up to
+// LILY_NOALLOC_MAX_ROWS rows. The layout is what the kernel indexes:
+// part[row][CAP], part_n[row][MAX_SLICES], tickets[row].
+struct NoAllocScratch {
+    uint2 part[LILY_NOALLOC_MAX_ROWS][lily::CAP];
+    uint32_t part_n[LILY_NOALLOC_MAX_ROWS][lily::MAX_SLICES];
+    uint32_t tickets[LILY_NOALLOC_MAX_ROWS];
+    uint32_t status_word;
+    uint32_t steps[LILY_NOALLOC_MAX_ROWS];
+    lily_sampling_params_t params[LILY_NOALLOC_MAX_ROWS];
+};
+static_assert(sizeof(NoAllocScratch) <= LILY_NOALLOC_SCRATCH_BYTES, "stated size too small");
+
+// Static device storage: no allocation call ever makes or frees it. In host
+// code this name is only a stand-in for the array, not a device address: the
+// address comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[LILY_NOALLOC_SCRATCH_BYTES];
+
+struct NoAllocDevice {
+    bool ready = false;
+    NoAllocScratch *scratch = nullptr;  // device address on this device
+    int sm_count = 0;
+    int max_smem = 0;
+    uint32_t attr_mask = 0;
+};
+NoAllocDevice g_noalloc_devices[64];
+
+int32_t noalloc_fail(int32_t code, const char *msg, char *err, uint32_t err_cap) {
+    if (err != nullptr && err_cap > 0u) {
+        std::snprintf(err, err_cap, "%s", msg);
+    }
+    return code;
+}
+
+template <typename T, bool VEC>
+cudaError_t noalloc_launch_one(NoAllocDevice *d, cudaStream_t stream, const lily::KArgs &a,
+                               uint32_t rows, size_t smem) {
+    auto kernel = lily::sample_rows_kernel<T, VEC>;
+    const uint32_t bit = 1u << ((sizeof(T) == 4 ? 0 : 2) + (VEC ? 1 : 0));
+    if (!(d->attr_mask & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(
+            kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d->max_smem);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        d->attr_mask |= bit;
+    }
+    dim3 grid(a.n_slices, rows, 1);
+    kernel<<<grid, lily::NT, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t lily_sample_batch_noalloc(void *stream_, uint32_t vocab, const lily_sample_args_t *args,
+                                  char *err, uint32_t err_cap) {
+    if (args == nullptr || args->struct_size != sizeof(lily_sample_args_t)) {
+        return noalloc_fail(LILY_ERR_ARG, "args is null or of another ABI version", err, err_cap);
+    }
+    const lily_sample_args_t &g = *args;
+    if (g.rows == 0u || g.rows > LILY_NOALLOC_MAX_ROWS) {
+        return noalloc_fail(LILY_ERR_CAPACITY, "rows outside 1..LILY_NOALLOC_MAX_ROWS", err, err_cap);
+    }
+    if (vocab == 0u || vocab > (1u << 24) || g.logits == nullptr || g.out_ids == nullptr ||
+        g.params == nullptr || g.logits_ld < vocab || g.logits_dtype > LILY_BF16) {
+        return noalloc_fail(LILY_ERR_ARG,
+                            "logits must be F32 or BF16 [rows, ld >= vocab]; out and params set",
+                            err, err_cap);
+    }
+    if (g.params_on_device != 0u || g.count_slots != nullptr) {
+        return noalloc_fail(LILY_ERR_ARG,
+                            "the allocation-free draw takes host params and no histogram slots",
+                            err, err_cap);
+    }
+    if (g.uniforms == nullptr && g.steps == nullptr) {
+        return noalloc_fail(LILY_ERR_ARG, "either uniforms or steps must be given", err, err_cap);
+    }
+    if ((g.history_ids != nullptr) != (g.history_len != nullptr) ||
+        (g.bias_ids != nullptr) != (g.bias_len != nullptr) ||
+        (g.bias_ids != nullptr) != (g.bias_vals != nullptr) ||
+        (g.ban_ids != nullptr) != (g.ban_len != nullptr)) {
+        return noalloc_fail(LILY_ERR_ARG, "a list needs both its ids and its lengths", err, err_cap);
+    }
+    if (g.kept_n != nullptr &&
+        (g.kept_ids == nullptr || g.kept_probs == nullptr || g.kept_ld < LILY_K_CAP)) {
+        return noalloc_fail(LILY_ERR_ARG, "kept_n needs kept_ids, kept_probs and kept_ld >= 1024",
+                            err, err_cap);
+    }
+    for (uint32_t r = 0; r < g.rows; ++r) {
+        if (!params_ok(g.params[r])) {
+            return noalloc_fail(LILY_ERR_PARAMS, "invalid sampling parameters", err, err_cap);
+        }
+        if (g.history_ids != nullptr && uses_penalties(g.params[r]) &&
+            g.params[r].frequency_penalty != 0.0f) {
+            return noalloc_fail(LILY_ERR_CAPACITY,
+                                "a frequency penalty over a history list needs a vocabulary-sized "
+                                "count table, which the allocation-free draw does not carry",
+                                err, err_cap);
+        }
+    }
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+        return noalloc_fail(LILY_ERR_CUDA, "no current CUDA device", err, err_cap);
+    }
+    NoAllocDevice *d = &g_noalloc_devices[device];
+    if (!d->ready) {
+        // Set-up, once per device, with that device current: the array's
+        // address ON THIS DEVICE. (Passing the host-side name to the kernel
+        // instead would hand it a host address.)
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            return noalloc_fail(LILY_ERR_CUDA, "cudaGetSymbolAddress failed for the static scratch",
+                                err, err_cap);
+        }
+        if (cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, device) !=
+                cudaSuccess ||
+            cudaDeviceGetAttribute(&d->max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) !=
+                cudaSuccess) {
+            return noalloc_fail(LILY_ERR_CUDA, "device attributes unavailable", err, err_cap);
+        }
+        d->scratch = static_cast<NoAllocScratch *>(p);
+        d->ready = true;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    NoAllocScratch *sc = d->scratch;
+    // The array keeps the last call's contents: the tickets and the status
+    // word must start at zero; the parameters are overwritten.
+    if (cudaMemsetAsync(sc->tickets, 0, sizeof(sc->tickets) + sizeof(sc->status_word), stream) !=
+            cudaSuccess ||
+        cudaMemcpyAsync(sc->params, g.params, sizeof(lily_sampling_params_t) * g.rows,
+                        cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+        (g.steps != nullptr &&
+         cudaMemcpyAsync(sc->steps, g.steps, sizeof(uint32_t) * g.rows, cudaMemcpyHostToDevice,
+                         stream) != cudaSuccess)) {
+        return noalloc_fail(LILY_ERR_CUDA, "staging the parameters failed", err, err_cap);
+    }
+    lily::KArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.vocab = vocab;
+    a.part = &sc->part[0][0];
+    a.part_n = &sc->part_n[0][0];
+    a.tickets = sc->tickets;
+    a.status_word = &sc->status_word;
+    a.logits = g.logits;
+    a.logits_ld = g.logits_ld;
+    a.rows = g.rows;
+    a.params = sc->params;
+    a.uniforms = g.uniforms;
+    a.steps = g.steps != nullptr ? sc->steps : nullptr;
+    a.history_ids = g.history_ids;
+    a.history_len = g.history_len;
+    a.history_ld = g.history_ld;
+    a.bias_ids = g.bias_ids;
+    a.bias_vals = g.bias_vals;
+    a.bias_len = g.bias_len;
+    a.bias_ld = g.bias_ld;
+    a.ban_ids = g.ban_ids;
+    a.ban_len = g.ban_len;
+    a.ban_ld = g.ban_ld;
+    a.forced_ids = g.forced_ids;
+    a.out_ids = g.out_ids;
+    a.out_status = g.out_status;
+    a.kept_n = g.kept_n;
+    a.kept_ids = g.kept_ids;
+    a.kept_probs = g.kept_probs;
+    a.kept_ld = g.kept_ld;
+    uint32_t slices = 2u * (uint32_t)d->sm_count / g.rows;
+    const uint32_t by_len = (vocab + lily::MIN_SLICE - 1u) / lily::MIN_SLICE;
+    slices = slices > lily::MAX_SLICES ? lily::MAX_SLICES : slices;
+    slices = slices > by_len ? by_len : slices;
+    a.n_slices = slices < 1u ? 1u : slices;
+    const size_t smem = smem_bytes(vocab, a.n_slices);
+    if (smem > (size_t)d->max_smem) {
+        return noalloc_fail(LILY_ERR_CAPACITY, "vocabulary too large for the shared-memory bitmap",
+                            err, err_cap);
+    }
+    const size_t esize = g.logits_dtype == LILY_F32 ? 4 : 2;
+    const bool vec = (reinterpret_cast<uintptr_t>(a.logits) % 16u == 0u) &&
+                     ((a.logits_ld * esize) % 16u == 0u);
+    cudaError_t e;
+    if (g.logits_dtype == LILY_F32) {
+        e = vec ? noalloc_launch_one<float, true>(d, stream, a, g.rows, smem)
+                : noalloc_launch_one<float, false>(d, stream, a, g.rows, smem);
+    } else {
+        e = vec ? noalloc_launch_one<__nv_bfloat16, true>(d, stream, a, g.rows, smem)
+                : noalloc_launch_one<__nv_bfloat16, false>(d, stream, a, g.rows, smem);
+    }
+    if (e != cudaSuccess) {
+        return noalloc_fail(LILY_ERR_CUDA, cudaGetErrorString(e), err, err_cap);
+    }
+    return LILY_OK;
+}
+
 int32_t lily_debug_exp(void *stream_, const float *in, float *out, uint64_t n) {
     if (in == nullptr || out == nullptr) {
         return LILY_ERR_ARG;
