@@ -322,6 +322,85 @@ int32_t lily_spec_accept(lily_sampler_t *h, void *stream, const uint32_t *draws,
                          const uint32_t *ids, uint32_t m, uint32_t *ctrl, uint32_t pos0,
                          uint32_t ratio, uint32_t chain, uint32_t stride);
 
+/* ------------------------------------------- 8-bit LM head, vocab shards -- */
+
+/*
+ * The projection that produces the logits the sampler reads, for a head
+ * stored in 8 bits. In the reference this is gemv_quant
+ * (src/kernels/quant.rs:141-175) called per row from
+ * src/qwen4exp/model.rs:2999-3006 on MLX affine 4/8-bit weights; the format
+ * here is the symmetric one of the vocab-sharded configuration:
+ *
+ *   logits[t, n] = sum_g scale[n, g] * sum_{c in group g} w[n, c] * hidden[t, c]
+ *
+ * w int8 [rows, hidden], scale bf16 [rows, hidden / 64] (one per 64 columns),
+ * hidden bf16 [tokens, hidden_ld], all sums in binary32 (group sums on the
+ * tensor cores, exact products, then scaled and added in group order).
+ * tokens <= 64, hidden a multiple of 512, every pointer 16-byte aligned.
+ */
+typedef struct lily_lmhead {
+    uint32_t struct_size;        /* sizeof(lily_lmhead_t) */
+    uint32_t rows;               /* vocabulary rows held here (a shard, or all) */
+    uint32_t hidden;             /* columns */
+    uint32_t group;              /* columns per scale: 64 */
+    const int8_t *weights;       /* device [rows, hidden] */
+    const void *scales_bf16;     /* device [rows, hidden / group] */
+} lily_lmhead_t;
+
+/* out_logits: device F32 [tokens, out_ld >= rows]. Needs no handle state
+ * beyond the status word; any handle of the device serves. */
+int32_t lily_lmhead_logits(lily_sampler_t *h, void *stream, const lily_lmhead_t *head,
+                           const void *hidden_bf16, uint64_t hidden_ld, uint32_t tokens,
+                           float *out_logits, uint64_t out_ld);
+
+/*
+ * Vocabulary shards (no counterpart in the reference, which keeps the whole
+ * head on one GPU; its two-phase select, src/kernels/metal/sample.metal:
+ * 664-701, is the same idea inside one device). Shard s holds the logits of
+ * ids [first_id, first_id + vocab) and runs lily_shard_candidates: per row it
+ * keeps its best LILY_SHARD_CANDIDATES candidates (a greedy row: 1), sorted,
+ * with the shard's largest adjusted logit and sum of exponentials, as one
+ * 520-byte record. The caller gathers all shards' records onto every rank
+ * (an all-gather of tokens * 520 bytes per rank) and calls lily_merge_draw,
+ * which selects, cuts and draws over the union: the same token on every
+ * rank, and the token one pass over the whole vocabulary draws, because the
+ * global top-k lies inside the union of the shards' top-64.
+ *
+ * Limits: params are HOST arrays; sampled rows need 1 <= top_k <= 64; no
+ * penalties, bias, ban or forced ids (their ids would be global, the shard's
+ * logits are local): refused with LILY_ERR_ARG.
+ */
+#define LILY_SHARD_CANDIDATES 64u
+#define LILY_SHARD_RECORD_BYTES 520u
+
+/*
+ * args: logits (this shard's, [rows, ld >= handle vocab]), logits_dtype,
+ * rows, params; everything else must be NULL / 0. records: device
+ * [rows] x 520 bytes. want_sums != 0 also fills each record's sum of
+ * exponentials (one more pass over the logits).
+ */
+int32_t lily_shard_candidates(lily_sampler_t *h, void *stream, const lily_sample_args_t *args,
+                              uint32_t first_id, int32_t want_sums, void *records);
+
+/* lily_lmhead_logits into the handle's own logits scratch (created with
+ * LILY_FLAG_LMHEAD: F32 [64, vocab]) followed by lily_shard_candidates on it.
+ * head->rows must equal the handle's vocab. */
+#define LILY_FLAG_LMHEAD 4u
+int32_t lily_lmhead_shard_candidates(lily_sampler_t *h, void *stream, const lily_lmhead_t *head,
+                                     const void *hidden_bf16, uint64_t hidden_ld,
+                                     const lily_sample_args_t *args, uint32_t first_id,
+                                     int32_t want_sums, void *records);
+
+/*
+ * gathered: device [n_shards, shard_stride >= rows] records, shard-major.
+ * args: rows, params, uniforms or steps, out_ids, and optionally out_status
+ * and kept_*; logits and lists NULL. out_lse: optional device [rows], the log
+ * of the sum over the whole vocabulary of exp(adjusted logit), valid when the
+ * records were made with want_sums. n_shards <= 64.
+ */
+int32_t lily_merge_draw(lily_sampler_t *h, void *stream, const void *gathered, uint32_t n_shards,
+                        uint64_t shard_stride, const lily_sample_args_t *args, float *out_lse);
+
 /* ------------------------------------------------------------------ test -- */
 
 /*

@@ -97,6 +97,18 @@ class SampleArgs(C.Structure):
     ]
 
 
+class LmHead(C.Structure):
+    """lily_lmhead_t: an 8-bit head (or one vocabulary shard of it) on the device."""
+
+    _fields_ = [("struct_size", C.c_uint32), ("rows", C.c_uint32), ("hidden", C.c_uint32),
+                ("group", C.c_uint32), ("weights", C.c_void_p), ("scales_bf16", C.c_void_p)]
+
+
+SHARD_CANDIDATES = 64
+SHARD_RECORD_BYTES = 520
+FLAG_LMHEAD = 4
+
+
 class SpecArgs(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32), ("m", C.c_uint32),
@@ -167,6 +179,15 @@ def lib():
         L.lily_sample_batch_noalloc.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(SampleArgs),
                                                 C.c_char_p, C.c_uint32]
         L.lily_sampler_read_phase_clocks.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.lily_lmhead_logits.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(LmHead), C.c_void_p,
+                                         C.c_uint64, C.c_uint32, C.c_void_p, C.c_uint64]
+        L.lily_shard_candidates.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SampleArgs),
+                                            C.c_uint32, C.c_int32, C.c_void_p]
+        L.lily_lmhead_shard_candidates.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(LmHead),
+                                                   C.c_void_p, C.c_uint64, C.POINTER(SampleArgs),
+                                                   C.c_uint32, C.c_int32, C.c_void_p]
+        L.lily_merge_draw.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64,
+                                      C.POINTER(SampleArgs), C.c_void_p]
         _lib = L
     return _lib
 
@@ -242,7 +263,7 @@ class SamplerScratch:
 
     def __init__(self, vocab: int, max_rows: int = 1, max_history: int = 1 << 16,
                  max_list: int = 256, counts_table: bool = False, device: int | None = None,
-                 phase_clocks: bool = False):
+                 phase_clocks: bool = False, lmhead: bool = False):
         import torch
 
         if device is None:
@@ -252,7 +273,8 @@ class SamplerScratch:
         self.max_rows = max_rows
         st = lib().lily_sampler_create(device, vocab, max_rows, max_history, max_list,
                                        (FLAG_COUNTS_TABLE if counts_table else 0)
-                                       | (FLAG_PHASE_CLOCKS if phase_clocks else 0),
+                                       | (FLAG_PHASE_CLOCKS if phase_clocks else 0)
+                                       | (FLAG_LMHEAD if lmhead else 0),
                                        C.byref(self._h))
         if st != OK:
             raise LilyError(st, "lily_sampler_create failed (is a CUDA device present?)")
@@ -373,6 +395,75 @@ class SamplerScratch:
             a.kept_n, a.kept_ids, a.kept_probs = _ptr(kept_n), _ptr(kept_ids), _ptr(kept_probs)
             a.kept_ld = _ld(kept_ids)
         self._check(lib().lily_sample_batch(self._h, _stream_ptr(stream), C.byref(a)))
+
+    # -- 8-bit LM head and vocabulary shards
+    @staticmethod
+    def _head(weights, scales, group: int = 64) -> LmHead:
+        hd = LmHead()
+        hd.struct_size = C.sizeof(LmHead)
+        hd.rows, hd.hidden = int(weights.shape[0]), int(weights.shape[1])
+        hd.group = group
+        hd.weights = _ptr(weights)
+        hd.scales_bf16 = _ptr(scales)
+        return hd
+
+    def _shard_args(self, rows, params, steps, keep):
+        a = SampleArgs()
+        a.struct_size = C.sizeof(SampleArgs)
+        a.rows = rows
+        arr = (SamplingParams * rows)(*params)
+        keep.append(arr)
+        a.params = C.cast(arr, C.c_void_p)
+        if steps is not None:
+            sarr = (C.c_uint32 * rows)(*[int(s) for s in steps])
+            keep.append(sarr)
+            a.steps = C.cast(sarr, C.c_void_p)
+        return a
+
+    def lmhead_logits(self, weights, scales, hidden, out_logits, stream=None):
+        """lily_lmhead_logits: int8 `weights` [rows, hidden], bf16 `scales`
+        [rows, hidden/64], bf16 `hidden` [tokens, hidden] -> F32 out [tokens, >= rows]."""
+        hd = self._head(weights, scales)
+        self._check(lib().lily_lmhead_logits(self._h, _stream_ptr(stream), C.byref(hd), _ptr(hidden),
+                                             _ld(hidden), int(hidden.shape[0]), _ptr(out_logits),
+                                             _ld(out_logits)))
+
+    def shard_candidates(self, logits, params, records, first_id: int = 0, want_sums: bool = False,
+                         stream=None):
+        """lily_shard_candidates: this shard's records (uint8 [rows, 520]) of `logits`."""
+        rows = logits.shape[0]
+        keep = []
+        a = self._shard_args(rows, params, None, keep)
+        a.logits, a.logits_dtype, a.logits_ld = _ptr(logits), _dtype_code(logits), _ld(logits)
+        self._check(lib().lily_shard_candidates(self._h, _stream_ptr(stream), C.byref(a), first_id,
+                                                int(want_sums), _ptr(records)))
+
+    def lmhead_shard_candidates(self, weights, scales, hidden, params, records, first_id: int = 0,
+                                want_sums: bool = False, stream=None):
+        """lily_lmhead_shard_candidates: head projection into the handle's own
+        logits, then this shard's records (needs lmhead=True at creation)."""
+        rows = int(hidden.shape[0])
+        keep = []
+        a = self._shard_args(rows, params, None, keep)
+        hd = self._head(weights, scales)
+        self._check(lib().lily_lmhead_shard_candidates(self._h, _stream_ptr(stream), C.byref(hd),
+                                                       _ptr(hidden), _ld(hidden), C.byref(a),
+                                                       first_id, int(want_sums), _ptr(records)))
+
+    def merge_draw(self, gathered, params, out_ids, *, uniforms=None, steps=None, out_status=None,
+                   kept_n=None, kept_ids=None, kept_probs=None, out_lse=None, stream=None):
+        """lily_merge_draw over `gathered` (uint8 [n_shards, rows, 520])."""
+        n_shards, rows = int(gathered.shape[0]), int(gathered.shape[1])
+        keep = []
+        a = self._shard_args(rows, params, steps, keep)
+        a.uniforms = _ptr(uniforms)
+        a.out_ids = _ptr(out_ids)
+        a.out_status = _ptr(out_status)
+        if kept_n is not None:
+            a.kept_n, a.kept_ids, a.kept_probs = _ptr(kept_n), _ptr(kept_ids), _ptr(kept_probs)
+            a.kept_ld = _ld(kept_ids)
+        self._check(lib().lily_merge_draw(self._h, _stream_ptr(stream), _ptr(gathered), n_shards,
+                                          rows, C.byref(a), _ptr(out_lse)))
 
     def argmax_batch(self, logits, out_ids, stream=None):
         """src/kernels/elementwise.rs:297-308 argmax_f32 for each row."""

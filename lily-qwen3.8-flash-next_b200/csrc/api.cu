@@ -12,6 +12,7 @@
 
 #include "../../include/lily_sampler.h"
 #include "sample_kernel.cuh"
+#include "lmhead_kernel.cuh"
 
 namespace {
 
@@ -61,6 +62,9 @@ struct lily_sampler {
     uint32_t *h_status = nullptr;
     uint32_t attr_mask = 0;  // kernel variants whose shared-memory limit is raised
     long long *phase_clocks = nullptr;
+    float *lm_logits = nullptr;  // LILY_FLAG_LMHEAD: F32 [64, lm_ld]
+    uint64_t lm_ld = 0;
+    bool lm_attr = false, merge_attr = false;
 };
 
 namespace {
@@ -351,6 +355,13 @@ int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
             return bail(e, "histogram slots");
         }
     }
+    if (flags & LILY_FLAG_LMHEAD) {
+        h->lm_ld = ((uint64_t)vocab + 3u) & ~uint64_t(3);
+        if ((e = cudaMalloc(&h->lm_logits, (size_t)lily_head::TOK * h->lm_ld * sizeof(float))) !=
+            cudaSuccess) {
+            return bail(e, "LM head logits");
+        }
+    }
     if (flags & LILY_FLAG_PHASE_CLOCKS) {
         const size_t pb = (size_t)max_rows * LILY_MAX_SLICES * LILY_PHASES * sizeof(long long);
         if ((e = cudaMalloc(&h->phase_clocks, pb)) != cudaSuccess ||
@@ -386,6 +397,7 @@ void lily_sampler_destroy(lily_sampler_t *h) {
     cudaFree(h->counts_table);
     cudaFree(h->seen_table);
     cudaFree(h->phase_clocks);
+    cudaFree(h->lm_logits);
     if (h->h_status) {
         cudaFreeHost(h->h_status);
     }
@@ -695,6 +707,262 @@ int32_t lily_argmax_batch(lily_sampler_t *h, void *stream_, const void *logits,
     a.out_ids = out_ids;
     a.n_slices = choose_slices(h, rows);
     return launch(h, static_cast<cudaStream_t>(stream_), a, rows, logits_dtype);
+}
+
+// ------------------------------------------------ LM head, vocab shards --
+
+namespace {
+
+int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t *head,
+                      const void *hidden, uint64_t hidden_ld, uint32_t tokens, float *out,
+                      uint64_t out_ld) {
+    if (head == nullptr || head->struct_size != sizeof(lily_lmhead_t)) {
+        return fail(h, LILY_ERR_ARG, "head is null or of another ABI version");
+    }
+    if (head->weights == nullptr || head->scales_bf16 == nullptr || hidden == nullptr || out == nullptr) {
+        return fail(h, LILY_ERR_ARG, "weights, scales, hidden and out must be set");
+    }
+    if (head->group != (uint32_t)lily_head::GROUP_K || head->hidden == 0u || head->hidden % 512u != 0u) {
+        return fail(h, LILY_ERR_ARG, "group must be 64 and hidden a multiple of 512");
+    }
+    if (tokens == 0u || tokens > (uint32_t)lily_head::TOK) {
+        return fail(h, LILY_ERR_CAPACITY, "tokens outside 1..64");
+    }
+    if (head->rows == 0u || out_ld < head->rows || hidden_ld < head->hidden) {
+        return fail(h, LILY_ERR_ARG, "out_ld < rows or hidden_ld < hidden");
+    }
+    if (reinterpret_cast<uintptr_t>(head->weights) % 16u || reinterpret_cast<uintptr_t>(head->scales_bf16) % 16u ||
+        reinterpret_cast<uintptr_t>(hidden) % 16u || (hidden_ld * 2u) % 16u) {
+        return fail(h, LILY_ERR_ARG, "weights, scales and hidden rows must be 16-byte aligned");
+    }
+    if (!h->lm_attr) {
+        CU(h, cudaFuncSetAttribute(lily_head::lmhead_int8_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)lily_head::Smem::BYTES));
+        h->lm_attr = true;
+    }
+    lily_head::Args a;
+    a.w = head->weights;
+    a.ldw = head->hidden;
+    a.scales = static_cast<const __nv_bfloat16 *>(head->scales_bf16);
+    a.hidden = static_cast<const __nv_bfloat16 *>(hidden);
+    a.ldh = hidden_ld;
+    a.tokens = tokens;
+    a.k = head->hidden;
+    a.rows = head->rows;
+    a.out = out;
+    a.ldo = out_ld;
+    a.status_word = h->status_word;
+    const uint32_t tiles = (head->rows + lily_head::TILE_ROWS - 1) / lily_head::TILE_ROWS;
+    const uint32_t grid = tiles < (uint32_t)h->sm_count ? tiles : (uint32_t)h->sm_count;
+    lily_head::lmhead_int8_kernel<<<grid, lily_head::THREADS, lily_head::Smem::BYTES, stream>>>(a);
+    CU(h, cudaGetLastError());
+    return LILY_OK;
+}
+
+// Host parameters of a sharded call: checked, then staged to the device.
+int32_t stage_shard_params(lily_sampler *h, cudaStream_t stream, const lily_sample_args_t &g,
+                           const lily_sampling_params_t **d_params, const uint32_t **d_steps,
+                           int *slot_out) {
+    if (g.rows == 0u || g.rows > h->max_rows) {
+        return fail(h, LILY_ERR_CAPACITY, "rows outside 1..max_rows");
+    }
+    if (g.params == nullptr || g.params_on_device) {
+        return fail(h, LILY_ERR_ARG, "sharded calls take host params");
+    }
+    if (g.history_ids || g.history_len || g.bias_ids || g.bias_vals || g.bias_len || g.ban_ids ||
+        g.ban_len || g.forced_ids || g.count_slots) {
+        return fail(h, LILY_ERR_ARG, "no penalties state, lists or forced ids in sharded calls");
+    }
+    for (uint32_t r = 0; r < g.rows; ++r) {
+        const lily_sampling_params_t &p = g.params[r];
+        if (!params_ok(p)) {
+            return fail(h, LILY_ERR_PARAMS, "invalid sampling parameters");
+        }
+        if (uses_penalties(p)) {
+            return fail(h, LILY_ERR_ARG, "no penalties in sharded calls");
+        }
+        if (!is_greedy(p) && (p.top_k == 0u || p.top_k > LILY_SHARD_CANDIDATES)) {
+            return fail(h, LILY_ERR_ARG, "sharded sampling needs 1 <= top_k <= 64");
+        }
+    }
+    int slot = -1;
+    int32_t st = next_stage(h, &slot);
+    if (st != LILY_OK) {
+        return st;
+    }
+    char *hs = h->h_stage[slot];
+    std::memcpy(hs + h->layout.params, g.params, sizeof(lily_sampling_params_t) * g.rows);
+    *d_params = reinterpret_cast<const lily_sampling_params_t *>(h->d_stage[slot] + h->layout.params);
+    *d_steps = nullptr;
+    if (g.steps != nullptr) {
+        std::memcpy(hs + h->layout.steps, g.steps, sizeof(uint32_t) * g.rows);
+        *d_steps = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.steps);
+    }
+    CU(h, cudaMemcpyAsync(h->d_stage[slot], h->h_stage[slot], h->layout.total, cudaMemcpyHostToDevice,
+                          stream));
+    *slot_out = slot;
+    return LILY_OK;
+}
+
+int32_t shard_candidates(lily_sampler *h, cudaStream_t stream, const lily_sample_args_t &g,
+                         uint32_t first_id, int32_t want_sums, void *records) {
+    if (g.logits == nullptr || records == nullptr || g.logits_ld < h->vocab || g.logits_dtype > LILY_BF16) {
+        return fail(h, LILY_ERR_ARG, "logits must be F32 or BF16 [rows, ld >= vocab]; records set");
+    }
+    if ((uint64_t)first_id + h->vocab > 0xFFFFFFFFull) {
+        return fail(h, LILY_ERR_ARG, "first_id + vocab overflows an id");
+    }
+    const lily_sampling_params_t *d_params = nullptr;
+    const uint32_t *d_steps = nullptr;
+    int slot = -1;
+    int32_t st = stage_shard_params(h, stream, g, &d_params, &d_steps, &slot);
+    if (st != LILY_OK) {
+        return st;
+    }
+    lily::KArgs a;
+    base_args(h, &a);
+    a.logits = g.logits;
+    a.logits_ld = g.logits_ld;
+    a.rows = g.rows;
+    a.params = d_params;
+    a.steps = d_steps;
+    a.out_ids = nullptr;
+    a.shard_k = LILY_SHARD_CANDIDATES;
+    a.id_offset = first_id;
+    a.cand_out = static_cast<lily::ShardRecord *>(records);
+    a.n_slices = choose_slices(h, g.rows);
+    st = launch(h, stream, a, g.rows, g.logits_dtype);
+    if (st == LILY_OK && want_sums) {
+        if (g.logits_dtype == LILY_F32) {
+            lily::shard_sums_kernel<float><<<g.rows, 1024, 0, stream>>>(
+                static_cast<const float *>(g.logits), g.logits_ld, h->vocab, d_params, a.cand_out);
+        } else {
+            lily::shard_sums_kernel<__nv_bfloat16><<<g.rows, 1024, 0, stream>>>(
+                static_cast<const __nv_bfloat16 *>(g.logits), g.logits_ld, h->vocab, d_params, a.cand_out);
+        }
+        CU(h, cudaGetLastError());
+    }
+    CU(h, cudaEventRecord(h->ev[slot], stream));
+    return st;
+}
+
+}  // namespace
+
+int32_t lily_lmhead_logits(lily_sampler_t *h, void *stream_, const lily_lmhead_t *head,
+                           const void *hidden_bf16, uint64_t hidden_ld, uint32_t tokens,
+                           float *out_logits, uint64_t out_ld) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    DeviceGuard guard(h->device);
+    return lmhead_launch(h, static_cast<cudaStream_t>(stream_), head, hidden_bf16, hidden_ld, tokens,
+                         out_logits, out_ld);
+}
+
+int32_t lily_shard_candidates(lily_sampler_t *h, void *stream_, const lily_sample_args_t *args,
+                              uint32_t first_id, int32_t want_sums, void *records) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (args == nullptr || args->struct_size != sizeof(lily_sample_args_t)) {
+        return fail(h, LILY_ERR_ARG, "args is null or of another ABI version");
+    }
+    DeviceGuard guard(h->device);
+    return shard_candidates(h, static_cast<cudaStream_t>(stream_), *args, first_id, want_sums, records);
+}
+
+int32_t lily_lmhead_shard_candidates(lily_sampler_t *h, void *stream_, const lily_lmhead_t *head,
+                                     const void *hidden_bf16, uint64_t hidden_ld,
+                                     const lily_sample_args_t *args, uint32_t first_id,
+                                     int32_t want_sums, void *records) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (args == nullptr || args->struct_size != sizeof(lily_sample_args_t)) {
+        return fail(h, LILY_ERR_ARG, "args is null or of another ABI version");
+    }
+    if (h->lm_logits == nullptr) {
+        return fail(h, LILY_ERR_ARG, "the sampler was not created with LILY_FLAG_LMHEAD");
+    }
+    if (head == nullptr || head->rows != h->vocab) {
+        return fail(h, LILY_ERR_VOCAB, "the head's rows must equal the sampler's vocabulary");
+    }
+    if (args->logits != nullptr) {
+        return fail(h, LILY_ERR_ARG, "the logits come from the head: args->logits must be NULL");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    st = lmhead_launch(h, stream, head, hidden_bf16, hidden_ld, args->rows, h->lm_logits, h->lm_ld);
+    if (st != LILY_OK) {
+        return st;
+    }
+    lily_sample_args_t g = *args;
+    g.logits = h->lm_logits;
+    g.logits_dtype = LILY_F32;
+    g.logits_ld = h->lm_ld;
+    return shard_candidates(h, stream, g, first_id, want_sums, records);
+}
+
+int32_t lily_merge_draw(lily_sampler_t *h, void *stream_, const void *gathered, uint32_t n_shards,
+                        uint64_t shard_stride, const lily_sample_args_t *args, float *out_lse) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (args == nullptr || args->struct_size != sizeof(lily_sample_args_t)) {
+        return fail(h, LILY_ERR_ARG, "args is null or of another ABI version");
+    }
+    const lily_sample_args_t &g = *args;
+    if (gathered == nullptr || n_shards == 0u || n_shards > 64u || shard_stride < g.rows ||
+        g.out_ids == nullptr || g.logits != nullptr) {
+        return fail(h, LILY_ERR_ARG, "records and out_ids set, 1..64 shards, stride >= rows, no logits");
+    }
+    if (g.uniforms == nullptr && g.steps == nullptr) {
+        return fail(h, LILY_ERR_ARG, "either uniforms or steps must be given");
+    }
+    if (g.kept_n != nullptr &&
+        (g.kept_ids == nullptr || g.kept_probs == nullptr || g.kept_ld < LILY_SHARD_CANDIDATES)) {
+        return fail(h, LILY_ERR_ARG, "kept_n needs kept_ids, kept_probs and kept_ld >= 64");
+    }
+    DeviceGuard guard(h->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const lily_sampling_params_t *d_params = nullptr;
+    const uint32_t *d_steps = nullptr;
+    int slot = -1;
+    st = stage_shard_params(h, stream, g, &d_params, &d_steps, &slot);
+    if (st != LILY_OK) {
+        return st;
+    }
+    if (!h->merge_attr) {
+        CU(h, cudaFuncSetAttribute(lily::merge_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)sizeof(lily::SmemFixed)));
+        h->merge_attr = true;
+    }
+    lily::KArgs a;
+    base_args(h, &a);
+    a.vocab = 0xFFFFFFFFu;  // ids are global here
+    a.rows = g.rows;
+    a.params = d_params;
+    a.uniforms = g.uniforms;
+    a.steps = d_steps;
+    a.out_ids = g.out_ids;
+    a.out_status = g.out_status;
+    a.kept_n = g.kept_n;
+    a.kept_ids = g.kept_ids;
+    a.kept_probs = g.kept_probs;
+    a.kept_ld = g.kept_ld;
+    a.merge_in = static_cast<const lily::ShardRecord *>(gathered);
+    a.merge_shards = n_shards;
+    a.merge_stride = shard_stride;
+    a.out_lse = out_lse;
+    lily::merge_rows_kernel<<<g.rows, lily::NT, sizeof(lily::SmemFixed), stream>>>(a);
+    CU(h, cudaGetLastError());
+    CU(h, cudaEventRecord(h->ev[slot], stream));
+    return LILY_OK;
 }
 
 // ----------------------------------------------------------- speculation --

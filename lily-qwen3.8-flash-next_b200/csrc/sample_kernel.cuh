@@ -65,6 +65,17 @@ struct Geo {
 // Row status bits OR-ed into the handle's status word.
 constexpr uint32_t ROW_INTERNAL = 8;  // candidate buffer overflow: a bug, never expected
 
+// What one vocabulary shard tells the others about a row: its best candidates
+// in order (monotone key of the adjusted logit, vocabulary id; unused entries
+// have id 0xFFFFFFFF), the largest adjusted logit of the shard and the sum of
+// exp(adjusted - that) over the whole shard. 520 bytes.
+struct ShardRecord {
+    uint2 cand[LILY_SHARD_CANDIDATES];
+    float max_adj;
+    float sum_exp;
+};
+static_assert(sizeof(ShardRecord) == LILY_SHARD_RECORD_BYTES, "record layout is part of the ABI");
+
 struct SpecArgs {
     const uint32_t *draft_ids;  // [n_spec]
     const float *q_dense;       // [n_spec, q_ld] or null
@@ -117,6 +128,16 @@ struct KArgs {
     uint32_t *status_word;
     long long *phase_clocks;       // optional [max_rows, MAX_SLICES, LILY_PHASES] SM clock stamps
     uint32_t debug_stop;           // debug builds only: leave after this phase (0 = run all)
+    // Vocabulary shards. A shard launch (cand_out set) keeps each row's best
+    // shard_k candidates and writes them, sorted, as a ShardRecord instead of
+    // drawing; the merge kernel draws from the records of all shards.
+    uint32_t shard_k;              // candidates a sampled row keeps per shard (greedy rows keep 1)
+    uint32_t id_offset;            // vocabulary id of this shard's logit 0
+    ShardRecord *cand_out;         // [rows]
+    const ShardRecord *merge_in;   // [merge_shards, merge_stride >= rows]
+    uint32_t merge_shards;
+    uint64_t merge_stride;         // records between two shards
+    float *out_lse;                // optional [rows]: log of the sum over the vocabulary of exp(adjusted)
     SpecArgs spec;
 };
 
@@ -1262,6 +1283,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 P.repetition_penalty != 1.0f;
     c.T = greedy ? 1.0f : P.temperature;
     c.k = greedy ? 1u : (P.top_k == 0u ? KCAP : min(P.top_k, KCAP));
+    if (a.cand_out && !greedy) {
+        c.k = a.shard_k;  // the host made sure that top_k fits
+    }
     c.rep = P.repetition_penalty;
     c.presence = P.presence_penalty;
     c.frequency = P.frequency_penalty;
@@ -1865,6 +1889,19 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             n = c.k;
         }
     }
+    if (n == 0u && a.cand_out) {
+        // An empty record; the status word carries the reason.
+        ShardRecord *rec = a.cand_out + row;
+        for (uint32_t i = tid; i < LILY_SHARD_CANDIDATES; i += NT) {
+            rec->cand[i] = make_uint2(0u, 0xFFFFFFFFu);
+        }
+        if (tid == 0) {
+            rec->max_adj = neg_inf();
+            rec->sum_exp = 0.0f;
+            atomicOr(a.status_word, 1u << ((sm->err ? sm->err : ROW_INTERNAL) & 31u));
+        }
+        return;
+    }
     if (n == 0u) {
         // Nothing but NaNs reached the buffer (or a bug): an error row.
         if (tid == 0) {
@@ -1881,6 +1918,27 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         return;
     }
     LILY_STAMP(PH_MERGE);
+    if (a.cand_out) {
+        // A shard launch ends here: the sorted candidates are the row's record.
+        if (tid < 32u) {
+            if (!sorted) {
+                sort_candidates<true>(sm, n);
+            }
+            ShardRecord *rec = a.cand_out + row;
+            for (uint32_t i = tid; i < LILY_SHARD_CANDIDATES; i += 32u) {
+                rec->cand[i] = i < n ? make_uint2(sm->key[i], sm->id[i] + a.id_offset)
+                                     : make_uint2(0u, 0xFFFFFFFFu);
+            }
+            if (tid == 0) {
+                rec->max_adj = float_of_key(sm->key[0]);
+                rec->sum_exp = 0.0f;
+                if (sm->err) {
+                    atomicOr(a.status_word, 1u << (sm->err & 31u));
+                }
+            }
+        }
+        return;
+    }
     if (n <= 64u) {
         // One warp finishes the row; the others are done.
         if (tid < 32u) {
@@ -1898,6 +1956,147 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         LILY_STAMP(PH_SORT);
         finalize<false>(sm, a, row, n, P.seed);
         LILY_STAMP(PH_END);
+    }
+}
+
+// The draw of a vocabulary-sharded row: the shards' records hold every
+// candidate the row's top-k can contain (each shard kept its own best
+// shard_k >= k), so selecting, cutting and drawing over their union gives
+// what one pass over the whole vocabulary gives. One block per row.
+__global__ void __launch_bounds__(NT, 2) merge_rows_kernel(const __grid_constant__ KArgs a) {
+    extern __shared__ uint4 smem_raw[];
+    SmemFixed *sm = reinterpret_cast<SmemFixed *>(smem_raw);
+    const uint32_t tid = threadIdx.x;
+    const uint32_t row = a.row0 + blockIdx.x;
+    const lily_sampling_params_t P = a.params[row];
+    const bool greedy = P.temperature <= 0.0f || P.top_k == 1u;
+    if (tid == 0) {
+        RowCtx c;
+        c.T = greedy ? 1.0f : P.temperature;
+        c.k = greedy ? 1u : (P.top_k == 0u ? KCAP : min(P.top_k, KCAP));
+        c.rep = 1.0f;
+        c.presence = c.frequency = 0.0f;
+        c.top_p = P.top_p;
+        c.min_p = P.min_p;
+        c.use_pen = c.need_counts = c.has_special = false;
+        c.monotone = true;
+        c.argmax_mode = greedy;
+        c.lo = 0;
+        c.hi = a.vocab;
+        c.seen = nullptr;
+        c.counts = nullptr;
+        c.bias_ids = c.ban_ids = nullptr;
+        c.bias_vals = nullptr;
+        c.bias_len = c.ban_len = 0;
+        c.sp_in_smem = true;
+        sm->ctx = c;
+        sm->n = 0;
+        sm->err = 0;
+    }
+    __syncthreads();
+    const uint32_t slots = a.merge_shards * LILY_SHARD_CANDIDATES;
+    for (uint32_t i = tid; i < slots; i += NT) {
+        const ShardRecord *rec = a.merge_in + (uint64_t)(i / LILY_SHARD_CANDIDATES) * a.merge_stride + row;
+        const uint2 e = rec->cand[i % LILY_SHARD_CANDIDATES];
+        if (e.y != 0xFFFFFFFFu) {
+            const uint32_t at = atomicAdd(&sm->n, 1u);
+            sm->key[at] = e.x;
+            sm->id[at] = e.y;
+        }
+    }
+    if (a.out_lse && tid == 0) {
+        // Shards in order: the largest maximum, then the sums rescaled to it.
+        float top = neg_inf();
+        for (uint32_t s = 0; s < a.merge_shards; ++s) {
+            top = fmaxf(top, a.merge_in[(uint64_t)s * a.merge_stride + row].max_adj);
+        }
+        float sum = 0.0f;
+        for (uint32_t s = 0; s < a.merge_shards; ++s) {
+            const ShardRecord *rec = a.merge_in + (uint64_t)s * a.merge_stride + row;
+            sum += rec->sum_exp * expf(rec->max_adj - top);
+        }
+        a.out_lse[row] = top + logf(sum);
+    }
+    __syncthreads();
+    uint32_t n = sm->n;
+    const uint32_t k = sm->ctx.k;
+    if (n == 0u) {
+        if (tid == 0) {
+            a.out_ids[row] = 0xFFFFFFFFu;
+            if (a.out_status) {
+                a.out_status[row] = ROW_INTERNAL;
+            }
+            if (a.kept_n) {
+                a.kept_n[row] = 0;
+            }
+            atomicOr(a.status_word, 1u << ROW_INTERNAL);
+        }
+        return;
+    }
+    if (tid == 0) {
+        sm->n_adj = n;
+    }
+    __syncthreads();
+    bool sorted = false;
+    if (n <= RANKSORT_MAX) {
+        rank_sort(sm, n, k);
+        n = min(n, k);
+        sorted = true;
+    } else if (n > k) {
+        select_topk(sm, n, k);
+        n = k;
+    }
+    if (n <= 64u) {
+        if (tid < 32u) {
+            if (!sorted) {
+                sort_candidates<true>(sm, n);
+            }
+            finalize<true>(sm, a, row, n, P.seed);
+        }
+    } else {
+        if (!sorted) {
+            sort_candidates<false>(sm, n);
+        }
+        finalize<false>(sm, a, row, n, P.seed);
+    }
+}
+
+// Sum over a shard row of exp(adjusted - the shard's maximum), for records
+// made without penalties or lists: adjusted = l / T (l for a greedy row). One
+// block per row; the tree of adds is fixed, so the sum is reproducible.
+template <typename T>
+__global__ void __launch_bounds__(1024) shard_sums_kernel(const T *logits, uint64_t ld, uint32_t vocab,
+                                                           const lily_sampling_params_t *params,
+                                                           ShardRecord *records) {
+    __shared__ float warp_part[32];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const lily_sampling_params_t P = params[row];
+    const bool greedy = P.temperature <= 0.0f || P.top_k == 1u;
+    const float temp = greedy ? 1.0f : P.temperature;
+    const float top = records[row].max_adj;
+    const T *src = logits + (uint64_t)row * ld;
+    float s = 0.0f;
+    for (uint32_t i = tid; i < vocab; i += 1024u) {
+        const float adj = __fdiv_rn(widen(src[i]), temp);
+        if (adj == adj) {
+            s += expf(adj - top);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    }
+    if ((tid & 31u) == 0u) {
+        warp_part[tid >> 5] = s;
+    }
+    __syncthreads();
+    if (tid < 32u) {
+        s = warp_part[tid];
+        for (int o = 16; o > 0; o >>= 1) {
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        }
+        if (tid == 0) {
+            records[row].sum_exp = s;
+        }
     }
 }
 

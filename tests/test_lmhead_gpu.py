@@ -1,0 +1,262 @@
+"""The 8-bit LM head and the vocabulary-sharded draw, on the GPU through the
+C ABI, against the oracle.
+
+The head's group sums run on the tensor cores, whose order of additions is
+not the oracle's sequential one: logits are compared by tolerance (and bit for
+bit on inputs whose sums are exact in binary32 in any order). The sharded
+draw is then checked bit for bit: the oracle samples the very logits the GPU
+produced, one pass over the whole row, and the shards' merged draw has to
+give the same token, kept set and probabilities."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import oracle
+from gpu_util import np_u32, t_f32
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(torch, bits):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16).cuda()
+
+
+def _to_bf16_bits(x):
+    import lily_b200.workloads as wl
+
+    return wl.to_bf16_bits(np.asarray(x, dtype=np.float32))
+
+
+def _head_inputs(torch, rng, tokens, hidden, rows, exact=False):
+    if exact:
+        # Small integers times powers of two: every partial sum is exact.
+        h = _to_bf16_bits(rng.integers(-4, 5, size=(tokens, hidden)).astype(np.float32))
+        s = _to_bf16_bits(2.0 ** rng.integers(-6, -2, size=(rows, hidden // 64)).astype(np.float32))
+        w = rng.integers(-128, 128, size=(rows, hidden), dtype=np.int8)
+    else:
+        h = _to_bf16_bits(rng.standard_normal((tokens, hidden), dtype=np.float32))
+        s = _to_bf16_bits(rng.uniform(0.002, 0.02, size=(rows, hidden // 64)).astype(np.float32))
+        w = rng.integers(-127, 128, size=(rows, hidden), dtype=np.int8)
+    return h, w, s
+
+
+def _gpu_logits(torch, lily, scratch, h, w, s):
+    rows, tokens = w.shape[0], h.shape[0]
+    out = torch.full((tokens, rows), float("nan"), dtype=torch.float32, device="cuda")
+    scratch.lmhead_logits(torch.from_numpy(w).cuda(), _bf16(torch, s), _bf16(torch, h), out)
+    torch.cuda.synchronize()
+    assert scratch.status() == 0
+    return out
+
+
+@pytest.mark.parametrize("tokens,hidden,rows", [(64, 512, 256), (64, 1024, 1000), (5, 512, 257),
+                                                (1, 2048, 4096), (33, 512, 40_000)])
+def test_head_is_exact_where_the_sums_are(cuda, lily, tokens, hidden, rows):
+    torch = cuda
+    rng = np.random.default_rng([71, tokens, hidden, rows])
+    h, w, s = _head_inputs(torch, rng, tokens, hidden, rows, exact=True)
+    scratch = lily.SamplerScratch(rows, max_rows=64)
+    got = _gpu_logits(cuda, lily, scratch, h, w, s).cpu().numpy()
+    want = oracle.lmhead_int8(h, w, s, 64, 0, rows)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("tokens,hidden,rows", [(64, 1024, 2048), (17, 4096, 777)])
+def test_head_matches_the_oracle_within_rounding(cuda, lily, tokens, hidden, rows):
+    torch = cuda
+    rng = np.random.default_rng([72, tokens, hidden, rows])
+    h, w, s = _head_inputs(torch, rng, tokens, hidden, rows)
+    scratch = lily.SamplerScratch(rows, max_rows=64)
+    got = _gpu_logits(cuda, lily, scratch, h, w, s).cpu().numpy()
+    want = oracle.lmhead_int8(h, w, s, 64, 0, rows)
+    # Same products, same group order; only the order of the 64 adds inside a
+    # group differs: a few ulp of the group sums.
+    tol = 4e-6 * np.abs(want).max()
+    assert np.abs(got - want).max() <= tol, (np.abs(got - want).max(), tol)
+
+
+def _records(torch, n_shards, rows):
+    return torch.zeros((n_shards, rows, 520), dtype=torch.uint8, device="cuda")
+
+
+def _sharded_draw(torch, lily, logits, params, uniforms, n_shards, want_sums=True):
+    """Shards run one after the other on this GPU: none waits for another."""
+    rows, vocab = logits.shape
+    assert vocab % n_shards == 0
+    per = vocab // n_shards
+    rec = _records(torch, n_shards, rows)
+    shard = lily.SamplerScratch(per, max_rows=rows)
+    for s in range(n_shards):
+        part = logits[:, s * per:(s + 1) * per].contiguous()
+        shard.shard_candidates(part, params, rec[s], first_id=s * per, want_sums=want_sums)
+    out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    status = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    kept_n = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    kept_ids = torch.zeros((rows, 64), dtype=torch.int32, device="cuda")
+    kept_probs = torch.zeros((rows, 64), dtype=torch.float32, device="cuda")
+    lse = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    shard.merge_draw(rec, params, out, uniforms=t_f32(torch, uniforms), out_status=status,
+                     kept_n=kept_n, kept_ids=kept_ids, kept_probs=kept_probs, out_lse=lse)
+    torch.cuda.synchronize()
+    assert shard.status() == 0
+    return (np_u32(out), np_u32(status), np_u32(kept_n), np_u32(kept_ids), kept_probs.cpu().numpy(),
+            lse.cpu().numpy())
+
+
+def _check_against_oracle(lf, plist, uniforms, got):
+    ids, status, kept_n, kept_ids, kept_probs, lse = got
+    for r in range(lf.shape[0]):
+        d = oracle.sample(lf[r], oracle.params(**plist[r]), float(uniforms[r]), mode=1)
+        assert status[r] == 0
+        assert ids[r] == d.token, f"row {r}"
+        n = len(d.kept_ids)
+        assert kept_n[r] == n, f"row {r}: kept {kept_n[r]} vs {n}"
+        assert np.array_equal(kept_ids[r, :n], d.kept_ids), f"row {r}: kept ids"
+        assert np.abs(kept_probs[r, :n] - d.kept_prob).max() <= 1e-5
+        p = plist[r]
+        greedy = p.get("temperature", 0.0) <= 0.0 or p.get("top_k", 1) == 1
+        adj = lf[r].astype(np.float64) / (1.0 if greedy else np.float32(p["temperature"]))
+        want_lse = adj.max() + np.log(np.exp(adj - adj.max()).sum())
+        assert abs(lse[r] - want_lse) <= 1e-3 * max(1.0, abs(want_lse)), (r, lse[r], want_lse)
+
+
+@pytest.mark.parametrize("n_shards", [1, 2, 8])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_sharded_draw_equals_the_whole_row_draw(cuda, lily, n_shards, dtype):
+    torch = cuda
+    import lily_b200.workloads as wl
+
+    rows, vocab = 12, 65_536
+    rng = np.random.default_rng([73, n_shards])
+    x = wl.zipf_logits(rng, rows, vocab)
+    plist = [dict(temperature=[0.7, 1.0, 0.0, 0.9][r % 4], top_k=[40, 64, 1, 7][r % 4],
+                  top_p=[0.95, 1.0, 1.0, 0.8][r % 4], min_p=[0.0, 0.02, 0.0, 0.0][r % 4], seed=r)
+             for r in range(rows)]
+    u = np.array([oracle.uniform_for(500 + r, 3) for r in range(rows)], dtype=np.float32)
+    if dtype == "bf16":
+        bits = wl.to_bf16_bits(x)
+        logits = _bf16(torch, bits)
+        lf = oracle.widen_bf16(bits)
+    else:
+        logits = t_f32(torch, x)
+        lf = x
+    params = [lily.SamplingParams(**p) for p in plist]
+    got = _sharded_draw(cuda, lily, logits, params, u, n_shards)
+    _check_against_oracle(lf, plist, u, got)
+
+
+def test_sharded_draw_with_ties_across_shards(cuda, lily):
+    """Equal logits in different shards: the lower id wins, as in one pass."""
+    torch = cuda
+    rows, vocab = 4, 32_768
+    x = np.full((rows, vocab), -3.0, dtype=np.float32)
+    x[:, 100::4096] = 2.0  # the same value once per 4096 ids
+    x[1, 20_000] = 2.0
+    plist = [dict(temperature=1.0, top_k=k, top_p=1.0, seed=1) for k in (3, 5, 8, 64)]
+    u = np.array([0.1, 0.5, 0.9, 0.999], dtype=np.float32)
+    params = [lily.SamplingParams(**p) for p in plist]
+    got = _sharded_draw(cuda, lily, t_f32(torch, x), params, u, 8)
+    _check_against_oracle(x, plist, u, got)
+
+
+def test_sharded_calls_refuse_what_they_cannot_do(cuda, lily):
+    torch = cuda
+    scratch = lily.SamplerScratch(4096, max_rows=4)
+    logits = torch.zeros((1, 4096), dtype=torch.float32, device="cuda")
+    rec = _records(torch, 1, 1)
+    with pytest.raises(lily.LilyError):
+        scratch.shard_candidates(logits, [lily.SamplingParams(temperature=1.0, top_k=0)], rec[0])
+    with pytest.raises(lily.LilyError):
+        scratch.shard_candidates(logits, [lily.SamplingParams(temperature=1.0, top_k=65)], rec[0])
+    with pytest.raises(lily.LilyError):
+        scratch.shard_candidates(logits, [lily.SamplingParams(temperature=1.0, top_k=8,
+                                                              repetition_penalty=1.2)], rec[0])
+    with pytest.raises(lily.LilyError):  # no LM head scratch on this handle
+        scratch.lmhead_shard_candidates(torch.zeros((4096, 512), dtype=torch.int8, device="cuda"),
+                                        torch.zeros((4096, 8), dtype=torch.bfloat16, device="cuda"),
+                                        torch.zeros((1, 512), dtype=torch.bfloat16, device="cuda"),
+                                        [lily.SamplingParams(temperature=1.0, top_k=8)], rec[0])
+
+
+@pytest.mark.parametrize("n_shards", [1, 4])
+def test_head_then_sharded_draw_small(cuda, lily, n_shards):
+    """The fused call of each shard (head into the handle's logits, then the
+    records), merged; the oracle draws from the logits the GPU head produced."""
+    torch = cuda
+    import lily_b200.workloads as wl
+
+    cfg = wl.config5(tokens=64, hidden=1024, vocab=16_384, seed=77)
+    rows, vocab = 64, 16_384
+    per = vocab // n_shards
+    w = torch.from_numpy(cfg.weight).cuda()
+    s = _bf16(torch, cfg.scales)
+    h = _bf16(torch, cfg.hidden)
+    plist = [dict(cfg.params, seed=cfg.params["seed"] + t) for t in range(rows)]
+    params = [lily.SamplingParams(**p) for p in plist]
+    rec = _records(torch, n_shards, rows)
+    shard = lily.SamplerScratch(per, max_rows=rows, lmhead=True)
+    for i in range(n_shards):
+        shard.lmhead_shard_candidates(w[i * per:(i + 1) * per], s[i * per:(i + 1) * per], h, params,
+                                      rec[i], first_id=i * per, want_sums=True)
+    out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    status = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    kept_n = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    kept_ids = torch.zeros((rows, 64), dtype=torch.int32, device="cuda")
+    kept_probs = torch.zeros((rows, 64), dtype=torch.float32, device="cuda")
+    lse = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    shard.merge_draw(rec, params, out, uniforms=t_f32(torch, cfg.uniforms), out_status=status,
+                     kept_n=kept_n, kept_ids=kept_ids, kept_probs=kept_probs, out_lse=lse)
+    torch.cuda.synchronize()
+    assert shard.status() == 0
+    whole = lily.SamplerScratch(vocab, max_rows=rows)
+    lf = _gpu_logits(cuda, lily, whole, cfg.hidden, cfg.weight, cfg.scales).cpu().numpy()
+    ref = oracle.lmhead_int8(cfg.hidden, cfg.weight, cfg.scales, 64, 0, vocab)
+    assert np.abs(lf - ref).max() <= 4e-6 * np.abs(ref).max()
+    got = (np_u32(out), np_u32(status), np_u32(kept_n), np_u32(kept_ids), kept_probs.cpu().numpy(),
+           lse.cpu().numpy())
+    _check_against_oracle(lf, plist, cfg.uniforms, got)
+
+
+def test_config5_full_size(cuda, lily):
+    """hidden [64, 4096] x int8 [262144, 4096], 8 shards run in turn on this
+    GPU. The head is checked on three bands of rows against the oracle; the
+    sharded draw against the oracle's draw from the GPU's own logits."""
+    torch = cuda
+    import lily_b200.workloads as wl
+
+    cfg = wl.config5()
+    rows, vocab, n_shards = 64, 262_144, 8
+    per = vocab // n_shards
+    w = torch.from_numpy(cfg.weight).cuda()
+    s = _bf16(torch, cfg.scales)
+    h = _bf16(torch, cfg.hidden)
+    plist = [dict(cfg.params, seed=cfg.params["seed"] + t) for t in range(rows)]
+    params = [lily.SamplingParams(**p) for p in plist]
+    rec = _records(torch, n_shards, rows)
+    shard = lily.SamplerScratch(per, max_rows=rows, lmhead=True)
+    for i in range(n_shards):
+        shard.lmhead_shard_candidates(w[i * per:(i + 1) * per], s[i * per:(i + 1) * per], h, params,
+                                      rec[i], first_id=i * per, want_sums=True)
+    out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    status = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    kept_n = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    kept_ids = torch.zeros((rows, 64), dtype=torch.int32, device="cuda")
+    kept_probs = torch.zeros((rows, 64), dtype=torch.float32, device="cuda")
+    lse = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    shard.merge_draw(rec, params, out, uniforms=t_f32(torch, cfg.uniforms), out_status=status,
+                     kept_n=kept_n, kept_ids=kept_ids, kept_probs=kept_probs, out_lse=lse)
+    torch.cuda.synchronize()
+    assert shard.status() == 0
+    whole = lily.SamplerScratch(vocab, max_rows=rows)
+    lf_t = torch.empty((rows, vocab), dtype=torch.float32, device="cuda")
+    whole.lmhead_logits(w, s, h, lf_t)
+    torch.cuda.synchronize()
+    assert whole.status() == 0
+    lf = lf_t.cpu().numpy()
+    for lo in (0, 131_000, vocab - 72):
+        ref = oracle.lmhead_int8(cfg.hidden, cfg.weight, cfg.scales, 64, lo, lo + 72)
+        assert np.abs(lf[:, lo:lo + 72] - ref[:, lo:lo + 72]).max() <= 4e-6 * np.abs(ref[:, lo:lo + 72]).max()
+    got = (np_u32(out), np_u32(status), np_u32(kept_n), np_u32(kept_ids), kept_probs.cpu().numpy(),
+           lse.cpu().numpy())
+    _check_against_oracle(lf, plist, cfg.uniforms, got)
