@@ -713,6 +713,26 @@ int32_t lily_argmax_batch(lily_sampler_t *h, void *stream_, const void *logits,
 
 namespace {
 
+// cuTensorMapEncodeTiled through the runtime's entry-point query: the library
+// does not link against the driver.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    }
+    return fn;
+}
+
 int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t *head,
                       const void *hidden, uint64_t hidden_ld, uint32_t tokens, float *out,
                       uint64_t out_ld) {
@@ -735,18 +755,56 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
         reinterpret_cast<uintptr_t>(hidden) % 16u || (hidden_ld * 2u) % 16u) {
         return fail(h, LILY_ERR_ARG, "weights, scales and hidden rows must be 16-byte aligned");
     }
+    auto kernel = lily_head::lmhead_int8_kernel<0>;
+#ifdef LILY_DEBUG
+    if (const char *v = std::getenv("LILY_LMHEAD_VARIANT")) {
+        const int variant = std::atoi(v);
+        kernel = variant == 1    ? lily_head::lmhead_int8_kernel<1>
+                 : variant == 2  ? lily_head::lmhead_int8_kernel<2>
+                 : variant == 3  ? lily_head::lmhead_int8_kernel<3>
+                 : variant == 11 ? lily_head::lmhead_int8_kernel<11>
+                 : variant == 19 ? lily_head::lmhead_int8_kernel<19>
+                 : variant == 27 ? lily_head::lmhead_int8_kernel<27>
+                                 : lily_head::lmhead_int8_kernel<0>;
+        h->lm_attr = false;
+    }
+#endif
     if (!h->lm_attr) {
-        CU(h, cudaFuncSetAttribute(lily_head::lmhead_int8_kernel,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CU(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)lily_head::Smem::BYTES));
         h->lm_attr = true;
     }
+    EncodeTiledFn encode = tensor_map_encoder();
+    if (encode == nullptr) {
+        return fail(h, LILY_ERR_CUDA, "the driver does not offer cuTensorMapEncodeTiled");
+    }
     lily_head::Args a;
-    a.w = head->weights;
-    a.ldw = head->hidden;
+    {
+        // Weights: uint8 [rows, hidden], boxes of 256 rows x 128 bytes.
+        const cuuint64_t dims[2] = {head->hidden, head->rows};
+        const cuuint64_t strides[1] = {head->hidden};
+        const cuuint32_t box[2] = {(cuuint32_t)(lily_head::GROUP_K * lily_head::RAW_GROUPS),
+                                   (cuuint32_t)lily_head::TILE_ROWS};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode(&a.w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(head->weights), dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            return fail(h, LILY_ERR_CUDA, "cuTensorMapEncodeTiled refused the weights");
+        }
+    }
+    {
+        // Hidden states: bf16 [tokens, hidden], boxes of 64 rows x 64 columns.
+        const cuuint64_t dims[2] = {head->hidden, tokens};
+        const cuuint64_t strides[1] = {hidden_ld * 2u};
+        const cuuint32_t box[2] = {(cuuint32_t)lily_head::GROUP_K, (cuuint32_t)lily_head::TOK};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode(&a.h_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(hidden), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            return fail(h, LILY_ERR_CUDA, "cuTensorMapEncodeTiled refused the hidden states");
+        }
+    }
     a.scales = static_cast<const __nv_bfloat16 *>(head->scales_bf16);
-    a.hidden = static_cast<const __nv_bfloat16 *>(hidden);
-    a.ldh = hidden_ld;
     a.tokens = tokens;
     a.k = head->hidden;
     a.rows = head->rows;
@@ -755,7 +813,7 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
     a.status_word = h->status_word;
     const uint32_t tiles = (head->rows + lily_head::TILE_ROWS - 1) / lily_head::TILE_ROWS;
     const uint32_t grid = tiles < (uint32_t)h->sm_count ? tiles : (uint32_t)h->sm_count;
-    lily_head::lmhead_int8_kernel<<<grid, lily_head::THREADS, lily_head::Smem::BYTES, stream>>>(a);
+    kernel<<<grid, lily_head::THREADS, lily_head::Smem::BYTES, stream>>>(a);
     CU(h, cudaGetLastError());
     return LILY_OK;
 }

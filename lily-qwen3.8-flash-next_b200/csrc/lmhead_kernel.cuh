@@ -8,28 +8,44 @@
 // configuration, so parity here is by tolerance against a binary32 CPU sum.
 //
 // sm_100a only. The weights are the only large operand (1 byte per
-// multiply-add), so the kernel is a stream of them through the tensor cores:
+// multiply-add), so the kernel is a stream of them through the tensor cores,
+// one persistent block per SM, warps specialised:
 //
-//   * a tile is 256 vocabulary rows; per 64-column group the int8 bytes of
-//     the tile (16 KB) arrive by cp.async, are widened to bf16 exactly (every
-//     int8 is a bf16) and stored in the 128-byte-swizzled K-major layout;
-//   * one thread issues, per group, 2 x 4 tcgen05.mma (M = 128 rows, N = 64
-//     tokens, K = 16) into a TMEM accumulator that starts from zero: products
-//     of two bf16 are exact in binary32, so only the order of the 64 adds
-//     differs from a sequential sum;
-//   * eight warps read each group's accumulator back with tcgen05.ld, multiply
-//     by the row's scale of that group and add into registers: the group sums
+//   * a tile is 256 vocabulary rows. One thread asks the copy engine (TMA,
+//     128-byte swizzle) for 256 rows x 128 bytes of int8 per stage, four
+//     stages deep, and for each group's 64 x 64 slice of the hidden states,
+//     which lands in the swizzled K-major layout the multiplier's B operand
+//     descriptor names;
+//   * eight warps own one tile row per thread: per 64-column group a thread
+//     widens its row's 64 bytes to bf16 exactly (every int8 is a bf16) and
+//     stores them with tcgen05.st into TENSOR MEMORY, where the multiplier
+//     reads its A operand (lane = row, two bf16 per column): the widened
+//     weights never touch shared memory;
+//   * two threads (one per 128 rows) issue, per group, 4 tcgen05.mma each
+//     (M = 128 rows, N = 64 tokens, K = 16) into a TMEM accumulator that
+//     starts from zero: products of two bf16 are exact in binary32, so only
+//     the order of the 64 adds differs from a sequential sum. One commit per
+//     thread and group completes the group's "done" barrier, which frees the
+//     group's operand slots and hands its sums to the epilogue;
+//   * sixteen warps read each group's sums back with tcgen05.ld, multiply by
+//     the row's scale of that group and add into registers: the group sums
 //     cannot stay in TMEM across groups because each has its own scale;
 //   * after the last group the tile's 256 x 64 logits go to global memory.
+//
+// Tensor memory: 3 accumulators of 128 columns, 2 operand slots of 64.
 //
 // Every wait on an mbarrier is bounded in time; a wait that runs out sets an
 // abort word, after which no wait blocks any more: the block runs to its end
 // (results are garbage, TMEM is freed) and the status word tells the host.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#ifdef LILY_DEBUG
+#include <cstdio>
+#endif
 
 namespace lily_head {
 
@@ -37,37 +53,49 @@ constexpr int TILE_ROWS = 256;   // two M = 128 accumulators
 constexpr int TOK = 64;          // MMA N: the most hidden rows per launch
 constexpr int GROUP_K = 64;      // columns per scale group = one 128-byte bf16 atom
 constexpr int RAW_GROUPS = 2;    // groups per stage of int8 bytes
-constexpr int RAW_STAGES = 3;
-constexpr int OP_SLOTS = 3;      // bf16 operand slots (A tile + hidden slice)
-constexpr int ACC_BUFS = 4;      // TMEM accumulators in flight
+constexpr int RAW_STAGES = 4;
+constexpr int H_SLOTS = 8;       // hidden slices in shared memory: as many groups as the stages hold
+static_assert(H_SLOTS == 8, "the hidden ring and the done ring share their indexing");
+constexpr int A_SLOTS = 2;       // bf16 weight tiles in tensor memory
+constexpr int ACC_BUFS = 3;      // accumulators in tensor memory
 constexpr uint32_t RAW_STAGE_BYTES = TILE_ROWS * GROUP_K * RAW_GROUPS;  // 32 KB
-constexpr uint32_t A_BYTES = TILE_ROWS * 128;                           // 32 KB
 constexpr uint32_t H_BYTES = TOK * 128;                                 // 8 KB
-constexpr uint32_t OP_BYTES = A_BYTES + H_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t ACC_COLS = 128;  // two row halves x 64 tokens
+constexpr uint32_t ACC_COLS = 128;           // two row halves x 64 tokens, binary32
+constexpr uint32_t A_COLS = 64;              // two row halves x 64 bf16 = 32 columns each
+constexpr uint32_t A_COL0 = ACC_BUFS * ACC_COLS;
+static_assert(A_COL0 + A_SLOTS * A_COLS <= TMEM_COLS, "tensor memory columns");
 
 constexpr int WARP_MMA = 0;
-constexpr int WARP_HIDDEN = 1;
+constexpr int WARP_LOAD = 1;
 constexpr int WARP_CONV0 = 2;
-constexpr int N_CONV_WARPS = 4;
-constexpr int WARP_EPI0 = 6;
-constexpr int N_EPI_WARPS = 8;
-constexpr int THREADS = 32 * (WARP_EPI0 + N_EPI_WARPS);  // 448
+constexpr int N_CONV_WARPS = 8;
+constexpr int WARP_EPI0 = WARP_CONV0 + N_CONV_WARPS;
+constexpr int N_EPI_WARPS = 16;  // a row's 64 tokens are split between two warps
+constexpr int WARP_MMA1 = WARP_EPI0 + N_EPI_WARPS;  // issues the multiplies of rows 128..255
+constexpr int THREADS = 32 * (WARP_MMA1 + 1);  // 864 (registers are granted as for 896)
+constexpr int DONE_SLOTS = 8;    // ring of "group q has been multiplied" barriers
 constexpr int CONV_THREADS = 32 * N_CONV_WARPS;
 constexpr int EPI_THREADS = 32 * N_EPI_WARPS;
+static_assert(CONV_THREADS == TILE_ROWS && EPI_THREADS == 2 * TILE_ROWS, "threads per tile row");
+static_assert(WARP_CONV0 % 2 == 0 && WARP_EPI0 % 2 == 0, "warp % 4 must cover all four lane quarters");
 
 constexpr uint32_t STATUS_TIMEOUT_BIT = 30;  // bit of the handle's status word
 
 struct Smem {
     // Offsets from a 1024-byte aligned base.
-    static constexpr uint32_t OPS = 0;
-    static constexpr uint32_t RAW = OPS + OP_SLOTS * OP_BYTES;
+    static constexpr uint32_t HID = 0;
+    static constexpr uint32_t RAW = HID + H_SLOTS * H_BYTES;
     static constexpr uint32_t BARS = RAW + RAW_STAGES * RAW_STAGE_BYTES;
-    static constexpr uint32_t FULL = BARS;                       // [OP_SLOTS]
-    static constexpr uint32_t EMPTY = FULL + 8 * OP_SLOTS;       // [OP_SLOTS]
-    static constexpr uint32_t ACC_FULL = EMPTY + 8 * OP_SLOTS;   // [ACC_BUFS]
-    static constexpr uint32_t ACC_EMPTY = ACC_FULL + 8 * ACC_BUFS;
+    static constexpr uint32_t RAW_FULL = BARS;                      // [RAW_STAGES]
+    static constexpr uint32_t RAW_EMPTY = RAW_FULL + 8 * RAW_STAGES;  // [RAW_STAGES]
+    static constexpr uint32_t A_FULL = RAW_EMPTY + 8 * RAW_STAGES;  // [A_SLOTS]
+    static constexpr uint32_t H_FULL = A_FULL + 8 * A_SLOTS;        // [H_SLOTS]
+    // DONE[q % 8] completes when both halves of group q have been multiplied:
+    // one commit per issuing thread tells the converters (slot of q free for
+    // q + 2), the loader (slot free for q + 8) and the epilogue (sums ready).
+    static constexpr uint32_t DONE = H_FULL + 8 * H_SLOTS;          // [DONE_SLOTS]
+    static constexpr uint32_t ACC_EMPTY = DONE + 8 * DONE_SLOTS;    // [ACC_BUFS]
     static constexpr uint32_t TMEM_ADDR = ACC_EMPTY + 8 * ACC_BUFS;
     static constexpr uint32_t ABORT = TMEM_ADDR + 4;
     static constexpr uint32_t END = ABORT + 4;
@@ -76,11 +104,12 @@ struct Smem {
 static_assert(Smem::BYTES <= 227 * 1024, "shared memory of one block");
 
 struct Args {
-    const int8_t *w;            // [rows, ldw]
-    uint64_t ldw;               // = hidden
+    // Tiled copies (TMA), both with the 128-byte swizzle: the weights as uint8
+    // [rows, k] in boxes of 256 rows x 128 bytes, the hidden states as bf16
+    // [tokens, k] in boxes of 64 rows x 64 columns. Rows past the end read 0.
+    CUtensorMap w_map;
+    CUtensorMap h_map;
     const __nv_bfloat16 *scales;  // [rows, hidden / 64]
-    const __nv_bfloat16 *hidden;  // [tokens, ldh]
-    uint64_t ldh;
     uint32_t tokens;            // <= 64
     uint32_t k;                 // hidden size, a multiple of 512
     uint32_t rows;              // vocabulary rows of this shard
@@ -138,18 +167,28 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
-                 : "memory");
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// One tile of a 2-D tensor map into shared memory; its bytes complete `bar`.
+// x (the inner coordinate) times the element size is a multiple of 16 bytes
+// at every call site.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x,
+                                            int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
 }
 
 __device__ __forceinline__ void fence_async_proxy() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// K-major operand, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024
-// bytes apart; the start address may be advanced by 32 bytes per K = 16 step
-// inside the (1024-byte aligned) atom.
+// K-major operand in shared memory, 128-byte swizzle, rows 128 bytes apart,
+// 8-row groups 1024 bytes apart; the start address may be advanced by 32
+// bytes per K = 16 step inside the (1024-byte aligned) atom.
 __device__ __forceinline__ uint64_t operand_desc(uint32_t addr) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
@@ -159,12 +198,14 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t addr) {
 constexpr uint32_t INSTR_DESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TOK >> 3) << 17) |
                                 ((128u >> 4) << 24);
 
-__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]^T.
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                            uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(INSTR_DESC), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(INSTR_DESC), "r"(accumulate)
         : "memory");
 }
 
@@ -173,22 +214,32 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                  : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-          "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-          "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-          "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          "=r"(v[15])
         : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -202,6 +253,8 @@ __device__ __forceinline__ void tc_fence_after() {
 // Four int8 in a word -> two words of bf16 pairs, exactly. With c = 0x43 in
 // the high byte, (0x4300 | b) & 0xFF7F is 128 + (b & 127) and
 // (0x4300 | b) & 0xFF80 is 128 or 256: their difference is the signed byte.
+// (A variant that trades the two masks for two bf16 fused multiply-adds and a
+// minimum was measured slower.)
 __device__ __forceinline__ void widen4(uint32_t x, uint32_t &lo, uint32_t &hi) {
     const uint32_t t01 = __byte_perm(x, 0x43434343u, 0x5140);
     const uint32_t t23 = __byte_perm(x, 0x43434343u, 0x5342);
@@ -211,6 +264,18 @@ __device__ __forceinline__ void widen4(uint32_t x, uint32_t &lo, uint32_t &hi) {
     asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(a23), "r"(b23));
 }
 
+#ifdef LILY_DEBUG
+#define LM_T0() long long t_mark = clock64()
+#define LM_ACC(var) do { const long long t_now = clock64(); var += t_now - t_mark; t_mark = t_now; } while (0)
+#else
+#define LM_T0() do {} while (0)
+#define LM_ACC(var) do {} while (0)
+#endif
+
+// VARIANT is 0 in the product; debug builds instantiate others that leave
+// out the epilogue's math (bit 0), the conversion (bit 1), the hidden-state
+// copies (bit 3) or the weight copies (bit 4) to time the rest.
+template <int VARIANT>
 __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_constant__ Args a) {
     extern __shared__ uint8_t smem_unaligned[];
     const uint32_t base = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
@@ -228,13 +293,21 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
     const uint32_t total_groups = my_tiles * groups;
 
     if (tid == 0) {
-        for (int s = 0; s < OP_SLOTS; ++s) {
-            mbar_init(base + Smem::FULL + 8 * s, CONV_THREADS + 1);
-            mbar_init(base + Smem::EMPTY + 8 * s, 1);
+        for (int s = 0; s < RAW_STAGES; ++s) {
+            mbar_init(base + Smem::RAW_FULL + 8 * s, 1);
+            mbar_init(base + Smem::RAW_EMPTY + 8 * s, N_CONV_WARPS);
+        }
+        for (int s = 0; s < A_SLOTS; ++s) {
+            mbar_init(base + Smem::A_FULL + 8 * s, N_CONV_WARPS);
+        }
+        for (int s = 0; s < H_SLOTS; ++s) {
+            mbar_init(base + Smem::H_FULL + 8 * s, 1);
+        }
+        for (int s = 0; s < DONE_SLOTS; ++s) {
+            mbar_init(base + Smem::DONE + 8 * s, 2);
         }
         for (int b = 0; b < ACC_BUFS; ++b) {
-            mbar_init(base + Smem::ACC_FULL + 8 * b, 1);
-            mbar_init(base + Smem::ACC_EMPTY + 8 * b, EPI_THREADS);
+            mbar_init(base + Smem::ACC_EMPTY + 8 * b, N_EPI_WARPS);
         }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -251,181 +324,239 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
     tc_fence_after();
     const uint32_t tmem = *tmem_word;
 
-    if (warp == WARP_MMA) {
-        // ---- the issuing thread
+    if (warp == WARP_MMA || warp == WARP_MMA1) {
+        // ---- two issuing threads, one per 128 rows of the tile (issuing a
+        // multiply costs its thread some 60 clocks: one thread cannot keep up)
         if (lane == 0) {
+            const uint32_t half = warp == WARP_MMA ? 0u : 1u;
+            long long tw_h = 0, tw_acc = 0, tw_a = 0, t_issue = 0, t_commit = 0;
+            LM_T0();
             for (uint32_t q = 0; q < total_groups; ++q) {
-                const uint32_t s = q % OP_SLOTS, b = q % ACC_BUFS;
-                mbar_wait(base + Smem::FULL + 8 * s, (q / OP_SLOTS) & 1u, abort_word);
+                const uint32_t as = q % A_SLOTS, hs = q % H_SLOTS, b = q % ACC_BUFS;
+                mbar_wait(base + Smem::H_FULL + 8 * hs, (q / H_SLOTS) & 1u, abort_word);
+                LM_ACC(tw_h);
                 mbar_wait(base + Smem::ACC_EMPTY + 8 * b, ((q / ACC_BUFS) & 1u) ^ 1u, abort_word);
-                fence_async_proxy();
+                LM_ACC(tw_acc);
+                mbar_wait(base + Smem::A_FULL + 8 * as, (q / A_SLOTS) & 1u, abort_word);
+                LM_ACC(tw_a);
                 tc_fence_after();
-                const uint32_t a_addr = base + Smem::OPS + s * OP_BYTES;
-                const uint32_t h_addr = a_addr + A_BYTES;
+                const uint32_t h_addr = base + Smem::HID + hs * H_BYTES;
 #pragma unroll
-                for (uint32_t half = 0; half < 2; ++half) {
-#pragma unroll
-                    for (uint32_t k4 = 0; k4 < 4; ++k4) {
-                        mma_bf16(tmem + b * ACC_COLS + half * TOK,
-                                 operand_desc(a_addr + half * (A_BYTES / 2) + k4 * 32u),
-                                 operand_desc(h_addr + k4 * 32u), k4);
-                    }
+                for (uint32_t k4 = 0; k4 < 4; ++k4) {
+                    mma_bf16_ts(tmem + b * ACC_COLS + half * TOK,
+                                tmem + A_COL0 + as * A_COLS + half * (A_COLS / 2) + k4 * 8u,
+                                operand_desc(h_addr + k4 * 32u), k4);
                 }
-                mma_commit(base + Smem::EMPTY + 8 * s);
-                mma_commit(base + Smem::ACC_FULL + 8 * b);
+                LM_ACC(t_issue);
+                mma_commit(base + Smem::DONE + 8 * (q % DONE_SLOTS));
+                LM_ACC(t_commit);
             }
+#ifdef LILY_DEBUG
+            if (blockIdx.x == 0 && half == 0) {
+                printf("mma: groups %u wait_h %lld wait_acc %lld wait_a %lld issue %lld commit %lld (clocks per group)\n",
+                       total_groups, tw_h / total_groups, tw_acc / total_groups, tw_a / total_groups,
+                       t_issue / total_groups, t_commit / total_groups);
+            }
+#endif
         }
         __syncwarp();
-    } else if (warp == WARP_HIDDEN) {
-        // ---- the hidden slice of each group, straight into the swizzled layout
-        for (uint32_t q = 0; q <= total_groups; ++q) {
-            if (q < total_groups) {
-                const uint32_t s = q % OP_SLOTS;
-                mbar_wait(base + Smem::EMPTY + 8 * s, ((q / OP_SLOTS) & 1u) ^ 1u, abort_word);
-                const uint32_t g = q % groups;
-                const uint32_t h_addr = base + Smem::OPS + s * OP_BYTES + A_BYTES;
+    } else if (warp == WARP_LOAD) {
+        // ---- one thread asks the copy engine for every stage of weights and
+        // every group's slice of the hidden states, as far ahead as slots are free
+        if (lane == 0) {
+            const uint32_t stages_per_tile = groups / RAW_GROUPS;
+            const uint32_t n_stages = my_tiles * stages_per_tile;
+            long long tw_re = 0, tw_he = 0;
+            LM_T0();
+            for (uint32_t i = 0; i < n_stages; ++i) {
+                const uint32_t st = i % RAW_STAGES;
+                const uint32_t tile = blockIdx.x + (i / stages_per_tile) * gridDim.x;
+                const uint32_t kb = (i % stages_per_tile) * (GROUP_K * RAW_GROUPS);
+                mbar_wait(base + Smem::RAW_EMPTY + 8 * st, ((i / RAW_STAGES) & 1u) ^ 1u, abort_word);
+                LM_ACC(tw_re);
+                if (!(VARIANT & 16)) {
+                    mbar_expect_tx(base + Smem::RAW_FULL + 8 * st, RAW_STAGE_BYTES);
+                    tma_load_2d(base + Smem::RAW + st * RAW_STAGE_BYTES, &a.w_map, base + Smem::RAW_FULL + 8 * st,
+                                (int32_t)kb, (int32_t)(tile * TILE_ROWS));
+                } else {
+                    mbar_arrive(base + Smem::RAW_FULL + 8 * st);
+                }
 #pragma unroll
-                for (uint32_t j = 0; j < 16; ++j) {
-                    const uint32_t chunk = lane + 32u * j;
-                    const uint32_t m = chunk >> 3, c = chunk & 7u;
-                    const bool live = m < a.tokens;
-                    const __nv_bfloat16 *src =
-                        a.hidden + (live ? (uint64_t)m * a.ldh + (uint64_t)g * GROUP_K + c * 8u : 0u);
-                    cp_async16(h_addr + (m >> 3) * 1024u + (m & 7u) * 128u + ((c ^ (m & 7u)) << 4), src,
-                               live ? 16u : 0u);
+                for (uint32_t gg = 0; gg < RAW_GROUPS; ++gg) {
+                    const uint32_t q = i * RAW_GROUPS + gg;
+                    const uint32_t hs = q % H_SLOTS;
+                    if (q >= (uint32_t)H_SLOTS) {  // the slot's previous group has been multiplied
+                        mbar_wait(base + Smem::DONE + 8 * hs, ((q / H_SLOTS) & 1u) ^ 1u, abort_word);
+                    }
+                    LM_ACC(tw_he);
+                    if (!(VARIANT & 8)) {
+                        mbar_expect_tx(base + Smem::H_FULL + 8 * hs, H_BYTES);
+                        tma_load_2d(base + Smem::HID + hs * H_BYTES, &a.h_map, base + Smem::H_FULL + 8 * hs,
+                                    (int32_t)(kb + gg * GROUP_K), 0);
+                    } else {
+                        mbar_arrive(base + Smem::H_FULL + 8 * hs);
+                    }
                 }
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            if (q >= 1) {
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-                fence_async_proxy();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(base + Smem::FULL + 8 * ((q - 1) % OP_SLOTS));
-                }
+#ifdef LILY_DEBUG
+            if (blockIdx.x == 0 && total_groups) {
+                printf("load: wait_raw_empty %lld wait_h_empty %lld\n", tw_re / total_groups,
+                       tw_he / total_groups);
             }
+#endif
         }
+        __syncwarp();
     } else if (warp < WARP_EPI0) {
-        // ---- int8 bytes in, bf16 operand tiles out
+        // ---- int8 bytes in; one thread per tile row widens them into tensor memory
         const uint32_t ct = tid - 32u * WARP_CONV0;
+        const uint32_t quad = warp & 3u;                    // the TMEM lanes this warp may write
+        const uint32_t half = (warp - WARP_CONV0) >> 2;     // which 128 rows of the tile
+        const uint32_t trow = half * 128u + quad * 32u + lane;
+        const uint32_t t_lane = (quad * 32u) << 16;
         const uint32_t stages_per_tile = groups / RAW_GROUPS;
         const uint32_t n_stages = my_tiles * stages_per_tile;
-        auto issue_raw = [&](uint32_t i) {
-            if (i < n_stages) {
-                const uint32_t tile = blockIdx.x + (i / stages_per_tile) * gridDim.x;
-                const uint32_t row0 = tile * TILE_ROWS;
-                const uint32_t kb = (i % stages_per_tile) * (GROUP_K * RAW_GROUPS);
-                const uint32_t dst0 = base + Smem::RAW + (i % RAW_STAGES) * RAW_STAGE_BYTES;
-#pragma unroll
-                for (uint32_t j = 0; j < 16; ++j) {
-                    const uint32_t chunk = ct + CONV_THREADS * j;
-                    const uint32_t r = chunk >> 3, col = chunk & 7u;
-                    const uint32_t grow = min(row0 + r, a.rows - 1u);
-                    const int8_t *src = a.w + (uint64_t)grow * a.ldw + kb + col * 16u;
-                    // Odd rows swap their two 64-byte halves: the reads below stay free of
-                    // bank conflicts.
-                    cp_async16(dst0 + r * 128u + ((col ^ ((r & 1u) << 2)) << 4), src, 16u);
-                }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        issue_raw(0);
-        issue_raw(1);
+        long long tw_raw = 0, tw_ae = 0, t_conv = 0, t_st = 0;
+        LM_T0();
         for (uint32_t i = 0; i < n_stages; ++i) {
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
+            const uint32_t st = i % RAW_STAGES;
+            mbar_wait(base + Smem::RAW_FULL + 8 * st, (i / RAW_STAGES) & 1u, abort_word);
+            LM_ACC(tw_raw);
             __syncwarp();
-            asm volatile("bar.sync 1, %0;" ::"n"(CONV_THREADS) : "memory");
-            issue_raw(i + 2);
-            const uint32_t raw0 = base + Smem::RAW + (i % RAW_STAGES) * RAW_STAGE_BYTES;
+            const uint32_t raw_row = base + Smem::RAW + st * RAW_STAGE_BYTES + trow * 128u;
 #pragma unroll 1
             for (uint32_t gg = 0; gg < RAW_GROUPS; ++gg) {
                 const uint32_t q = i * RAW_GROUPS + gg;
-                const uint32_t s = q % OP_SLOTS;
-                mbar_wait(base + Smem::EMPTY + 8 * s, ((q / OP_SLOTS) & 1u) ^ 1u, abort_word);
-                const uint32_t a_addr = base + Smem::OPS + s * OP_BYTES;
-                const uint32_t j4 = ct & 3u;
+                const uint32_t as = q % A_SLOTS;
+                // Widen first (it needs no slot), then wait for the slot: the
+                // conversion overlaps the multiplies still reading the slot.
+                uint32_t o[2][16];
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t r = (ct >> 2) + 32u * j;
-                    const uint32_t pcol = (gg * 4u + j4) ^ ((r & 1u) << 2);
-                    uint32_t x0, x1, x2, x3;
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
-                                 : "r"(raw0 + r * 128u + (pcol << 4)));
-                    uint32_t o[8];
-                    widen4(x0, o[0], o[1]);
-                    widen4(x1, o[2], o[3]);
-                    widen4(x2, o[4], o[5]);
-                    widen4(x3, o[6], o[7]);
-                    const uint32_t line = a_addr + (r >> 3) * 1024u + (r & 7u) * 128u;
-                    // The swizzle already separates an even row from the odd row below it.
-                    const uint32_t ca = 2u * j4, cb = 2u * j4 + 1u;
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(line + ((ca ^ (r & 7u)) << 4)),
-                                 "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                 : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(line + ((cb ^ (r & 7u)) << 4)),
-                                 "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
-                                 : "memory");
+                for (uint32_t part = 0; part < 2; ++part) {
+                    if (!(VARIANT & 2)) {
+#pragma unroll
+                        for (uint32_t c = 0; c < 2; ++c) {
+                            uint32_t x0, x1, x2, x3;
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
+                                         : "r"(raw_row + (((gg * 4u + part * 2u + c) ^ (trow & 7u)) << 4)));
+                            widen4(x0, o[part][8 * c + 0], o[part][8 * c + 1]);
+                            widen4(x1, o[part][8 * c + 2], o[part][8 * c + 3]);
+                            widen4(x2, o[part][8 * c + 4], o[part][8 * c + 5]);
+                            widen4(x3, o[part][8 * c + 6], o[part][8 * c + 7]);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t c = 0; c < 16; ++c) {
+                            o[part][c] = 0x3F803F80u;
+                        }
+                    }
                 }
-                fence_async_proxy();
-                mbar_arrive(base + Smem::FULL + 8 * s);
+                LM_ACC(t_conv);
+                if (q >= (uint32_t)A_SLOTS) {  // group q - 2, the slot's last user, has been multiplied
+                    mbar_wait(base + Smem::DONE + 8 * ((q - A_SLOTS) % DONE_SLOTS),
+                              ((q - A_SLOTS) / DONE_SLOTS) & 1u, abort_word);
+                }
+                LM_ACC(tw_ae);
+                __syncwarp();
+                tc_fence_after();
+                const uint32_t a_addr = tmem + t_lane + A_COL0 + as * A_COLS + half * (A_COLS / 2);
+                tmem_st16(a_addr, o[0]);
+                tmem_st16(a_addr + 16u, o[1]);
+                tmem_st_wait();
+                tc_fence_before();
+                // One arrival per warp: arrivals on one barrier are serialised.
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(base + Smem::A_FULL + 8 * as);
+                }
+                LM_ACC(t_st);
+            }
+            // The stage's bytes are in registers or tensor memory: the slot may be refilled.
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(base + Smem::RAW_EMPTY + 8 * st);
             }
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+#ifdef LILY_DEBUG
+        if (blockIdx.x == 0 && ct == 0 && total_groups) {
+            printf("conv: wait_raw %lld wait_a_empty %lld convert %lld st+arrive %lld\n",
+                   tw_raw / total_groups, tw_ae / total_groups, t_conv / total_groups, t_st / total_groups);
+        }
+#endif
     } else {
         // ---- scale each group's sums and add them up; write the tile
         const uint32_t e = warp - WARP_EPI0;
         const uint32_t quad = warp & 3u;   // the TMEM lanes this warp may read
-        const uint32_t half = e >> 2;      // which 128 rows of the tile
+        const uint32_t half = (e >> 2) & 1u;  // which 128 rows of the tile
+        const uint32_t tok0 = (e >> 3) * (TOK / 2);  // which 32 tokens of the row
         const uint32_t t_lane = (quad * 32u) << 16;
         uint32_t q = 0;
+        long long tw_af = 0, t_math = 0, t_store = 0;
+        LM_T0();
         for (uint32_t ti = 0; ti < my_tiles; ++ti) {
             const uint32_t tile = blockIdx.x + ti * gridDim.x;
             const uint32_t row = tile * TILE_ROWS + half * 128u + quad * 32u + lane;
             const uint32_t rowc = min(row, a.rows - 1u);
             const uint4 *srow = reinterpret_cast<const uint4 *>(a.scales + (uint64_t)rowc * groups);
-            float acc[TOK];
+            float acc[TOK / 2];
 #pragma unroll
-            for (int m = 0; m < TOK; ++m) {
+            for (int m = 0; m < TOK / 2; ++m) {
                 acc[m] = 0.0f;
             }
+            uint4 sc_next = __ldg(srow);
             for (uint32_t g8 = 0; g8 < groups; g8 += 8) {
-                const uint4 sc = __ldg(srow + (g8 >> 3));
+                const uint4 sc = sc_next;
+                if (g8 + 8u < groups) {
+                    sc_next = __ldg(srow + (g8 >> 3) + 1u);
+                }
                 const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
                 for (uint32_t gi = 0; gi < 8; ++gi, ++q) {
                     const uint32_t b = q % ACC_BUFS;
                     const float s = __uint_as_float((gi & 1u) ? (sw[gi >> 1] & 0xFFFF0000u) : (sw[gi >> 1] << 16));
-                    mbar_wait(base + Smem::ACC_FULL + 8 * b, (q / ACC_BUFS) & 1u, abort_word);
+                    mbar_wait(base + Smem::DONE + 8 * (q % DONE_SLOTS), (q / DONE_SLOTS) & 1u, abort_word);
+                    LM_ACC(tw_af);
                     __syncwarp();
                     tc_fence_after();
-                    const uint32_t taddr = tmem + t_lane + b * ACC_COLS + half * TOK;
-                    uint32_t v[32];
-                    tmem_ld32(taddr, v);
-                    tmem_ld_wait();
+                    const uint32_t taddr = tmem + t_lane + b * ACC_COLS + half * TOK + tok0;
+                    if (!(VARIANT & 1)) {
 #pragma unroll
-                    for (int m = 0; m < 32; ++m) {
-                        acc[m] = __fadd_rn(acc[m], __fmul_rn(s, __uint_as_float(v[m])));
-                    }
-                    tmem_ld32(taddr + 32u, v);
-                    tmem_ld_wait();
+                        for (int c = 0; c < TOK / 32; ++c) {
+                            uint32_t v[16];
+                            tmem_ld16(taddr + 16u * c, v);
+                            tmem_ld_wait();
 #pragma unroll
-                    for (int m = 0; m < 32; ++m) {
-                        acc[32 + m] = __fadd_rn(acc[32 + m], __fmul_rn(s, __uint_as_float(v[m])));
+                            for (int m = 0; m < 16; ++m) {
+                                acc[16 * c + m] = fmaf(s, __uint_as_float(v[m]), acc[16 * c + m]);
+                            }
+                        }
+                    } else {
+                        acc[gi] += s + __uint_as_float(taddr);
                     }
                     tc_fence_before();
-                    mbar_arrive(base + Smem::ACC_EMPTY + 8 * b);
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(base + Smem::ACC_EMPTY + 8 * b);
+                    }
+                    LM_ACC(t_math);
                 }
             }
             if (row < a.rows) {
 #pragma unroll
-                for (int m = 0; m < TOK; ++m) {
-                    if ((uint32_t)m < a.tokens) {
-                        a.out[(uint64_t)m * a.ldo + row] = acc[m];
+                for (int m = 0; m < TOK / 2; ++m) {
+                    if (tok0 + (uint32_t)m < a.tokens) {
+                        a.out[(uint64_t)(tok0 + m) * a.ldo + row] = acc[m];
                     }
                 }
             }
+            LM_ACC(t_store);
         }
+#ifdef LILY_DEBUG
+        if (blockIdx.x == 0 && e == 0 && lane == 0 && total_groups) {
+            printf("epi: wait_acc_full %lld math %lld store %lld\n", tw_af / total_groups,
+                   t_math / total_groups, t_store / total_groups);
+        }
+#endif
     }
 
     tc_fence_before();
