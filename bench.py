@@ -188,6 +188,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--b4-steps", type=int, default=300)
+    ap.add_argument("--lmhead-steps", type=int, default=30,
+                    help="steps of the vocab-sharded LM head + sampling leg (0 = skip)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -312,6 +314,11 @@ def main():
     if rank == 0 and args.b4_steps > 0:
         b4 = b4_latency(torch, lily, w, dev, stream, args.b4_steps)
 
+    # ---- vocab-sharded 8-bit LM head + sampling (every rank takes part) -----
+    lm = None
+    if args.lmhead_steps > 0:
+        lm = lmhead_sharded(torch, dist, lily, dev, stream, world, rank, args.lmhead_steps)
+
     # ---- roofline ----------------------------------------------------------
     alg_bytes = ROWS * (vocab * 2 + HISTORY * 4)
     kernel_ms = statistics.mean(per_launch_ms)
@@ -355,12 +362,91 @@ def main():
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": args.steps, "clocks": clock_info, "latency_b4": b4,
+            "lmhead_sharded": lm,
             "us_per_step": ms_per_step * 1e3,
         }
         print(json.dumps(line), flush=True)
     scratch.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
+    """The vocab-sharded configuration: hidden bf16 [64, 4096] against an int8
+    head [262144, 4096] with bf16 scales per 64 columns, the vocabulary cut
+    into `world` shards (strong scaling: the head is fixed, a rank holds
+    1/world of it). A step is, on every rank: the head over the rank's rows and
+    its 520-byte candidate records, one all-gather of the records, the merged
+    draw (top-k 40, top-p 0.95, T 0.7). Weights are seeded random int8 made on
+    the device; a rank whose shard is smaller than the L2 rotates two copies."""
+    import lily_b200.shard as sh
+
+    tokens, hidden, vocab = 64, 4096, 262_144
+    per = vocab // world
+    g = torch.Generator(device=dev)
+    g.manual_seed(5005 + rank)
+    copies = 1 if per * hidden > 600e6 else 2
+    ws = [torch.randint(-127, 128, (per, hidden), dtype=torch.int8, device=dev, generator=g)
+          for _ in range(copies)]
+    sc = (torch.rand((per, hidden // 64), device=dev, generator=g) * 0.018 + 0.002).to(torch.bfloat16)
+    gh = torch.Generator(device=dev)
+    gh.manual_seed(5005)  # the same hidden states on every rank
+    h = torch.randn((tokens, hidden), device=dev, generator=gh).to(torch.bfloat16)
+    params = [lily.SamplingParams(temperature=0.7, top_k=40, top_p=0.95, seed=5005 + t)
+              for t in range(tokens)]
+    u = torch.tensor([lily.uniform_for(5005 + t, 0) for t in range(tokens)], dtype=torch.float32,
+                     device=dev)
+    scratch = lily.SamplerScratch(per, max_rows=tokens, lmhead=True, device=dev.index)
+    rec = torch.empty((tokens, sh.RECORD_BYTES), dtype=torch.uint8, device=dev)
+    out = torch.zeros(tokens, dtype=torch.int32, device=dev)
+    logits = torch.empty((tokens, per), dtype=torch.float32, device=dev)
+
+    def step(i):
+        sh.sharded_lmhead_draw(scratch, ws[i % copies], sc, h, params, out, first_id=rank * per,
+                               uniforms=u, records=rec, want_sums=True, stream=stream)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        for i in range(3):
+            fn(i)
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(n):
+            fn(i)
+        e1.record(stream)
+        sync()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / n
+
+    step_ms = timed(step, steps)
+    head_ms = timed(lambda i: scratch.lmhead_logits(ws[i % copies], sc, h, logits, stream=stream), steps)
+    assert scratch.status(stream) == lily.OK
+    agree = True
+    if world > 1:
+        every = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(every, out)
+        agree = all(bool(torch.equal(every[0], e)) for e in every)
+    scratch.close()
+    head_bytes = per * hidden + per * (hidden // 64) * 2 + tokens * hidden * 2
+    peak, peak_kind = peaks()
+    gbs = head_bytes / (head_ms * 1e-3) / 1e9
+    return {"workload": "hidden bf16 [64,4096] x int8 head [262144,4096], bf16 scales per 64 columns, "
+                        f"{world} vocabulary shard(s); top-k 40, top-p 0.95, T 0.7",
+            "n_gpus": world, "scaling": "strong", "us_per_step": step_ms * 1e3,
+            "rows_per_s": tokens / (step_ms * 1e-3), "steps": steps,
+            "head_kernel_us": head_ms * 1e3, "head_bytes_per_gpu": head_bytes,
+            "head_gbs_per_gpu": gbs, "head_frac_of_hbm": gbs / peak, "peak_kind": peak_kind,
+            "allgather_bytes_per_rank": tokens * sh.RECORD_BYTES, "ranks_agree": agree,
+            "l2": "one 1.07 GB shard" if copies == 1 else "two weight copies rotated"}
 
 
 def b4_latency(torch, lily, w, dev, stream, steps):

@@ -892,12 +892,22 @@ int32_t shard_candidates(lily_sampler *h, cudaStream_t stream, const lily_sample
     a.n_slices = choose_slices(h, g.rows);
     st = launch(h, stream, a, g.rows, g.logits_dtype);
     if (st == LILY_OK && want_sums) {
+        // The candidate launch has left the slice counters and the tickets (all
+        // zero again) free: the sums use them for their pieces.
+        uint32_t pieces = (2u * (uint32_t)h->sm_count + g.rows - 1u) / g.rows;
+        const uint32_t by_len = (h->vocab + 8191u) / 8192u;
+        pieces = pieces > by_len ? by_len : pieces;
+        pieces = pieces < 1u ? 1u : (pieces > lily::MAX_SLICES ? lily::MAX_SLICES : pieces);
+        const dim3 grid(pieces, g.rows, 1);
+        float *scratch = reinterpret_cast<float *>(h->part_n);
         if (g.logits_dtype == LILY_F32) {
-            lily::shard_sums_kernel<float><<<g.rows, 1024, 0, stream>>>(
-                static_cast<const float *>(g.logits), g.logits_ld, h->vocab, d_params, a.cand_out);
+            lily::shard_sums_kernel<float><<<grid, 1024, 0, stream>>>(
+                static_cast<const float *>(g.logits), g.logits_ld, h->vocab, d_params, a.cand_out, scratch,
+                h->tickets);
         } else {
-            lily::shard_sums_kernel<__nv_bfloat16><<<g.rows, 1024, 0, stream>>>(
-                static_cast<const __nv_bfloat16 *>(g.logits), g.logits_ld, h->vocab, d_params, a.cand_out);
+            lily::shard_sums_kernel<__nv_bfloat16><<<grid, 1024, 0, stream>>>(
+                static_cast<const __nv_bfloat16 *>(g.logits), g.logits_ld, h->vocab, d_params, a.cand_out,
+                scratch, h->tickets);
         }
         CU(h, cudaGetLastError());
     }

@@ -2062,21 +2062,27 @@ __global__ void __launch_bounds__(NT, 2) merge_rows_kernel(const __grid_constant
 }
 
 // Sum over a shard row of exp(adjusted - the shard's maximum), for records
-// made without penalties or lists: adjusted = l / T (l for a greedy row). One
-// block per row; the tree of adds is fixed, so the sum is reproducible.
+// made without penalties or lists: adjusted = l / T (l for a greedy row). A
+// row is cut into gridDim.x pieces; every add happens in a fixed order (a
+// thread's strided elements, the shuffle tree, the warps, the pieces), so the
+// sum is reproducible. The last block of a row to finish adds the pieces up.
 template <typename T>
 __global__ void __launch_bounds__(1024) shard_sums_kernel(const T *logits, uint64_t ld, uint32_t vocab,
                                                            const lily_sampling_params_t *params,
-                                                           ShardRecord *records) {
+                                                           ShardRecord *records, float *pieces,
+                                                           uint32_t *tickets) {
     __shared__ float warp_part[32];
-    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    __shared__ uint32_t is_last;
+    const uint32_t row = blockIdx.y, piece = blockIdx.x, tid = threadIdx.x;
     const lily_sampling_params_t P = params[row];
     const bool greedy = P.temperature <= 0.0f || P.top_k == 1u;
     const float temp = greedy ? 1.0f : P.temperature;
     const float top = records[row].max_adj;
     const T *src = logits + (uint64_t)row * ld;
+    const uint32_t len = (vocab + gridDim.x - 1u) / gridDim.x;
+    const uint32_t lo = piece * len, hi = min(vocab, lo + len);
     float s = 0.0f;
-    for (uint32_t i = tid; i < vocab; i += 1024u) {
+    for (uint32_t i = lo + tid; i < hi; i += 1024u) {
         const float adj = __fdiv_rn(widen(src[i]), temp);
         if (adj == adj) {
             s += expf(adj - top);
@@ -2095,8 +2101,20 @@ __global__ void __launch_bounds__(1024) shard_sums_kernel(const T *logits, uint6
             s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
         }
         if (tid == 0) {
-            records[row].sum_exp = s;
+            pieces[row * MAX_SLICES + piece] = s;
+            __threadfence();
+            is_last = atomicAdd(tickets + row, 1u) == gridDim.x - 1u;
         }
+    }
+    __syncthreads();
+    if (is_last && tid == 0) {
+        __threadfence();
+        float total = 0.0f;
+        for (uint32_t p = 0; p < gridDim.x; ++p) {
+            total += __ldcg(pieces + row * MAX_SLICES + p);
+        }
+        records[row].sum_exp = total;
+        tickets[row] = 0;
     }
 }
 
