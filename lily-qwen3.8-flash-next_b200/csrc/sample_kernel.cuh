@@ -1510,17 +1510,123 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     if (a.debug_stop == 1u) return;
 #endif
 
-    // ---- C0. the first round: a threshold from a fine histogram
+    // ---- C0'. small k, penalties that only lower: two passes over the slice
+    // Pass 1 keeps each thread's largest logit (one packed max per round).
+    // The adjusted values of those 512 logits are values of 512 different
+    // ids, so their k-th largest cannot exceed the k-th largest adjusted
+    // value of the slice: an exact, tight threshold before any logit is
+    // looked at closely. Pass 2 (after the lists, below) streams the slice
+    // again, from L2 this time, against that fixed threshold.
+    bool lean = c.k <= 128u && (!c.use_pen || c.monotone) && nrounds > 0u;
+    if (lean) {
+        constexpr uint32_t NONE = 0xFFFFFFFFu;
+        float best = neg_inf();
+        uint32_t best_r = NONE;
+        bool saw_nan = false;
+        {
+            const uint32_t ring_me = (uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES;
+            const char *src = my_src + (size_t)(STAGES - 1) * (ROUND * sizeof(T));  // round r + STAGES - 1
+            for (uint32_t r = 0; r < nfull; ++r) {
+                if (VEC) {
+                    if (r + STAGES - 1 < nfull) {
+                        const uint32_t dst = ring_me + ((r + STAGES - 1) % STAGES) * (NT * FRAG_BYTES);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src)
+                                     : "memory");
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16u),
+                                     "l"(src + 16)
+                                     : "memory");
+                        cp_async_commit();
+                    } else {
+                        issue(r + STAGES - 1);
+                    }
+                    src += ROUND * sizeof(T);
+                }
+                Frag cur;
+                fetch(r, cur);
+                const float m = frag_max<T>(cur);
+                saw_nan = saw_nan || m != m;
+                if (best_r == NONE || m > best) {
+                    best = m;
+                    best_r = r;
+                }
+            }
+            if (nrounds > nfull) {
+                const uint32_t r = nfull;
+                issue(r + STAGES - 1);
+                Frag cur;
+                fetch(r, cur);
+                const uint32_t base = c.lo + r * ROUND + tid * GROUP;
+                const uint32_t nvalid = base < c.hi ? min(GROUP, c.hi - base) : 0u;
+#pragma unroll
+                for (int e = 0; e < (int)GROUP; ++e) {
+                    if ((uint32_t)e < nvalid) {
+                        const float l = frag_get<T>(cur, e);
+                        saw_nan = saw_nan || l != l;
+                        if (best_r == NONE || l > best) {
+                            best = l;
+                            best_r = r;
+                        }
+                    }
+                }
+            }
+            cp_async_wait<0>();
+        }
+        // A NaN anywhere, or fewer than k threads with a logit: the general path.
+        const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE);
+        lean = !__syncthreads_or(saw_nan) && have >= c.k;
+        if (lean) {
+            uint32_t key = 0u, id = NONE;
+            if (best_r != NONE) {
+                // Which logit of that round it was: the round is read once more.
+                Frag again;
+                const uint32_t base = c.lo + best_r * ROUND + tid * GROUP;
+                load_frag_scalar<T>(again, row_ptr, base, c.hi);
+                const uint32_t nvalid = min(GROUP, c.hi - base);
+                uint32_t at = 0;
+                float l = best;
+#pragma unroll
+                for (int e = (int)GROUP - 1; e >= 0; --e) {
+                    const float v = frag_get<T>(again, e);
+                    if ((uint32_t)e < nvalid && v == best) {
+                        at = (uint32_t)e;
+                        l = v;
+                    }
+                }
+                id = base + at;
+                key = adjusted_key(sm, id, l, c.has_special && is_special(sm, c, id));
+            }
+            sm->key[tid] = key;
+            sm->id[tid] = id;
+            __syncthreads();
+            select_topk(sm, NT, c.k);  // the fillers (key 0) rank last: have >= k
+            if (tid == 0) {
+                // Ties with the k-th value must still pass: one key below it.
+                const uint32_t kth = sm->tau_key;
+                set_exact_threshold(sm, kth > 0u ? kth - 1u : 0u);
+                sm->n = 0;
+                sm->n_adj = 0;
+            }
+            __syncthreads();
+        }
+        // The ring starts over at round 0 for whichever stream follows.
+#pragma unroll
+        for (int st = 0; st < STAGES - 1; ++st) {
+            issue((uint32_t)st);
+        }
+    }
+
+    // ---- C0. (general path) the first round: a threshold from a fine histogram
     // The candidate buffer is still empty: its storage holds an 8192-bin
     // histogram of the raw keys of the round's untouched logits. The bin in
     // which the count from the top reaches k gives the first threshold.
+    Frag first;
+    if (!lean) {
     issue((uint32_t)(STAGES - 1));
     uint32_t *hist0 = sm->key;
     for (uint32_t b = tid; b < H0_BINS; b += NT) {
         hist0[b] = 0;
     }
     __syncthreads();
-    Frag first;
     fetch(0u, first);
     {
         const uint32_t base0 = c.lo + tid * GROUP;
@@ -1588,6 +1694,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         sm->th_base = edge0 >> 16;
         set_raw_edge(sm, edge0);
     }
+    }  // !lean
     LILY_STAMP(PH_ROUND0);
 #ifdef LILY_DEBUG
     if (a.debug_stop == 2u) return;
@@ -1621,7 +1728,84 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     __syncthreads();
     LILY_STAMP(PH_LISTS);
 
-    // ---- C. the stream
+    // ---- C'. pass 2 of the two-pass route: the fixed threshold, no meetings
+    if (lean) {
+        const uint32_t n_lists = min(sm->n, CAP);  // what the lists pushed
+        const float c_fix = sm->c_raw;
+        auto take = [&](const Frag &cur, uint32_t r, uint32_t base, uint32_t valid) {
+            const T *slot = VEC ? reinterpret_cast<const T *>(&ring[((r % STAGES) * NT + tid) * 2u])
+                                : nullptr;
+            uint32_t pass = pass_mask<T>(cur, c_fix) & valid;
+            while (pass != 0u) {
+                const uint32_t e = (uint32_t)__ffs(pass) - 1u;
+                pass &= pass - 1u;
+                const float l = slot != nullptr ? widen(slot[e]) : frag_pick<T>(cur, e);
+                const uint32_t id = base + e;
+                if (c.has_special && is_special(sm, c, id)) {
+                    continue;
+                }
+                push(sm, __float_as_uint(l), id);  // a full buffer raises the overflow flag
+            }
+        };
+        {
+            const uint32_t ring_me = (uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES;
+            const char *src = my_src + (size_t)(STAGES - 1) * (ROUND * sizeof(T));
+            uint32_t base = c.lo + tid * GROUP;
+            for (uint32_t r = 0; r < nfull; ++r) {
+                if (VEC) {
+                    if (r + STAGES - 1 < nfull) {
+                        const uint32_t dst = ring_me + ((r + STAGES - 1) % STAGES) * (NT * FRAG_BYTES);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src)
+                                     : "memory");
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16u),
+                                     "l"(src + 16)
+                                     : "memory");
+                        cp_async_commit();
+                    } else {
+                        issue(r + STAGES - 1);
+                    }
+                    src += ROUND * sizeof(T);
+                }
+                Frag cur;
+                fetch(r, cur);
+                if (!(frag_max<T>(cur) <= c_fix)) {
+                    take(cur, r, base, 0xFFFFFFFFu);
+                }
+                base += ROUND;
+            }
+            if (nrounds > nfull) {
+                const uint32_t r = nfull;
+                issue(r + STAGES - 1);
+                Frag cur;
+                fetch(r, cur);
+                if (base < c.hi) {
+                    const uint32_t nvalid = min(GROUP, c.hi - base);
+                    take(cur, r, base, nvalid >= 32u ? 0xFFFFFFFFu : (1u << nvalid) - 1u);
+                }
+            }
+            cp_async_wait<0>();
+        }
+        if (__syncthreads_or(*reinterpret_cast<volatile uint32_t *>(&sm->overflow))) {
+            // More logits tie with the threshold than the buffer holds: start the
+            // stream over on the general path, which makes room as it goes.
+            if (tid == 0) {
+                sm->n = n_lists;
+                sm->n_adj = n_lists;
+                sm->overflow = 0;
+            }
+            lean = false;
+#pragma unroll
+            for (int st = 0; st < STAGES - 1; ++st) {
+                issue((uint32_t)st);
+            }
+            issue((uint32_t)(STAGES - 1));
+            fetch(0u, first);
+            __syncthreads();
+        }
+    }
+
+    // ---- C. the stream (general path)
+    if (!lean) {
     // Rounds run without block barriers. Every RGROUP rounds the block meets:
     // if a push found the buffer full, the buffer is cut back to the best k
     // and the refused elements of those rounds are offered again (re-read
@@ -1768,6 +1952,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         meet(r);
     }
     cp_async_wait<0>();
+    }  // !lean
     __syncthreads();
 
     LILY_STAMP(PH_STREAM);
