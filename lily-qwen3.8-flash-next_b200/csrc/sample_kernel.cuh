@@ -1202,6 +1202,153 @@ __device__ __noinline__ void compact(SmemFixed *sm) {
     __syncthreads();
 }
 
+// ---- The two lean passes of the small-k route, out of line: each gets a
+// register allocation of its own instead of sharing the big kernel's.
+
+constexpr uint32_t ROUND_BYTES = NT * FRAG_BYTES;  // one round of logits, either type
+
+struct Pass1 {
+    float best;        // the thread's largest logit over its full rounds
+    uint32_t best_r;   // the round it came from (0xFFFFFFFF: no full round)
+    uint32_t saw_nan;
+};
+
+__device__ __forceinline__ void lean_copy_round(uint32_t dst, const char *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16u), "l"(src + 16) : "memory");
+}
+
+__device__ __forceinline__ void lean_read_slot(uint32_t at, Frag &f) {
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(f.v[0].x), "=r"(f.v[0].y), "=r"(f.v[0].z), "=r"(f.v[0].w)
+                 : "r"(at));
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(f.v[1].x), "=r"(f.v[1].y), "=r"(f.v[1].z), "=r"(f.v[1].w)
+                 : "r"(at + 16u));
+}
+
+// Pass 1 over the full rounds of a 16-byte aligned row: four rounds in
+// flight (stages 0, 1 at slot_a, 2, 3 at slot_b; rounds 0..2 are already on
+// their way), the thread's running maximum, and (fused4 != 0) four history
+// ids per thread and round marked in the seen bitmap of [lo, lo + width).
+// The maximum of every `rpb` consecutive rounds is also left, rounded up to a
+// bf16, in the thread's 16-byte table at `tab` (8 entries): pass 2 reads only
+// the rounds whose entry beats the threshold.
+template <typename T>
+__device__ __noinline__ Pass1 lean_pass1(uint32_t slot_a, uint32_t slot_b, const char *src0, uint32_t nfull,
+                                         const uint4 *h4, uint32_t fused4, uint32_t *seen, uint32_t lo,
+                                         uint32_t width, uint32_t tab, uint32_t rpb) {
+    constexpr uint32_t NONE = 0xFFFFFFFFu;
+    const uint32_t tid = threadIdx.x;
+    Pass1 out;
+    out.best = neg_inf();
+    out.best_r = NONE;
+    out.saw_nan = 0u;
+    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(tab), "r"(0xFF80FF80u) : "memory");
+    float bucket_max = neg_inf();
+    uint32_t in_bucket = 0, tab_at = tab;
+    const uint4 no_ids = make_uint4(NONE, NONE, NONE, NONE);
+    uint4 hq = tid < fused4 ? __ldg(h4 + tid) : no_ids;
+    const char *src = src0 + 3u * ROUND_BYTES;  // the round three ahead
+    uint32_t hnext = NT + tid;
+    for (uint32_t r = 0; r < nfull; r += 4u) {
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; ++j) {
+            const uint32_t rr = r + j;
+            if (rr < nfull) {
+                if (rr + 3u < nfull) {
+                    const uint32_t st = (j + 3u) & 3u;
+                    lean_copy_round((st < 2u ? slot_a : slot_b) + (st & 1u) * ROUND_BYTES, src);
+                }
+                cp_async_commit();
+                src += ROUND_BYTES;
+                cp_async_wait<3>();
+                Frag cur;
+                lean_read_slot((j < 2u ? slot_a : slot_b) + (j & 1u) * ROUND_BYTES, cur);
+                if (fused4 != 0u) {
+                    const uint4 h = hq;
+                    hq = hnext < fused4 ? __ldg(h4 + hnext) : no_ids;
+                    hnext += NT;
+                    const uint32_t ids[4] = {h.x, h.y, h.z, h.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t off = ids[i] - lo;
+                        if (off < width) {
+                            atomicOr(&seen[off >> 5], 1u << (off & 31u));
+                        }
+                    }
+                }
+                const float m = frag_max<T>(cur);
+                out.saw_nan |= m != m ? 1u : 0u;
+                if (out.best_r == NONE || m > out.best) {
+                    out.best = m;
+                    out.best_r = rr;
+                }
+                bucket_max = fmaxf(bucket_max, m);
+                if (++in_bucket == rpb || rr + 1u == nfull) {
+                    // Rounded up: a positive value with low bits set goes one bf16 up,
+                    // a negative one is truncated towards zero.
+                    const uint32_t bits = __float_as_uint(bucket_max);
+                    const uint32_t up = (bits >> 16) + (((bits & 0xFFFFu) != 0u && !(bits >> 31)) ? 1u : 0u);
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(tab_at), "h"((unsigned short)up) : "memory");
+                    tab_at += 2u;
+                    in_bucket = 0;
+                    bucket_max = neg_inf();
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    return out;
+}
+
+// The logits of one thread's fragment that beat the fixed threshold go to the
+// candidate buffer as raw bits (ids on the bias / ban lists went in up front).
+template <typename T>
+__device__ __noinline__ void lean_take(SmemFixed *sm, const Frag &cur, uint32_t base, uint32_t valid,
+                                       float c_fix) {
+    const RowCtx &c = sm->ctx;
+    uint32_t pass = pass_mask<T>(cur, c_fix) & valid;
+    while (pass != 0u) {
+        const uint32_t e = (uint32_t)__ffs(pass) - 1u;
+        pass &= pass - 1u;
+        const uint32_t id = base + e;
+        if (c.has_special && is_special(sm, c, id)) {
+            continue;
+        }
+        push(sm, __float_as_uint(frag_pick<T>(cur, e)), id);  // a full buffer raises the overflow flag
+    }
+}
+
+// Pass 2 over the full rounds of a 16-byte aligned row: only the rounds whose
+// table entry (pass 1) beats c_fix are read again, from L2 or DRAM, a few
+// dozen 32-byte fragments per row.
+template <typename T>
+__device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_t nfull, uint32_t base0,
+                                        float c_fix, uint32_t tab, uint32_t rpb) {
+    Frag table;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(table.v[0].x), "=r"(table.v[0].y), "=r"(table.v[0].z), "=r"(table.v[0].w)
+                 : "r"(tab));
+    table.v[1] = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
+    uint32_t buckets = pass_mask<__nv_bfloat16>(table, c_fix) & 0xFFu;
+    const uint4 *src = reinterpret_cast<const uint4 *>(src0);
+    constexpr uint32_t STRIDE = ROUND_BYTES / 16u;
+    while (buckets != 0u) {
+        const uint32_t b = (uint32_t)__ffs(buckets) - 1u;
+        buckets &= buckets - 1u;
+        const uint32_t end = min((b + 1u) * rpb, nfull);
+        for (uint32_t rr = b * rpb; rr < end; ++rr) {
+            Frag cur;
+            cur.v[0] = __ldcg(src + rr * STRIDE);
+            cur.v[1] = __ldcg(src + rr * STRIDE + 1);
+            if (!(frag_max<T>(cur) <= c_fix)) {
+                lean_take<T>(sm, cur, base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+            }
+        }
+    }
+}
+
 // Phase stamps for the optional per-block timing trace.
 enum { PH_START = 0, PH_BITMAPS, PH_LISTS, PH_STREAM, PH_LOCAL_SELECT, PH_MERGE, PH_SORT, PH_END,
        PH_ROUND0, PH_SELECT0, PH_THRESH0, PH_R1, PH_R4, PH_R8, PH_R16, PH_R32 };
@@ -1374,9 +1521,61 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     for (int st = 0; st < STAGES - 1; ++st) {
         issue((uint32_t)st);
     }
+    // Small k with penalties that only lower a logit takes two passes over
+    // the slice (see C0' below). Its first pass is the one that reads DRAM:
+    // it runs four rounds deep, the two extra stages in the still unused
+    // candidate buffer (key[] and id[] are one round each).
+    const bool lean_cand = c.k <= 128u && (!c.use_pen || c.monotone) && nrounds > 0u;
+    constexpr int P1_STAGES = 4;
+    static_assert(STAGES == 2 && CAP * 4u == NT * FRAG_BYTES, "pass 1 stages 2 and 3 are key[] and id[]");
+    const uint32_t p1_slot[P1_STAGES] = {
+        (uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES,
+        (uint32_t)__cvta_generic_to_shared(ring) + (NT + tid) * FRAG_BYTES,
+        (uint32_t)__cvta_generic_to_shared(sm->key) + tid * FRAG_BYTES,
+        (uint32_t)__cvta_generic_to_shared(sm->id) + tid * FRAG_BYTES};
+    // Each thread's 16-byte table of per-bucket maxima (pass 1 -> pass 2) sits
+    // in tkey[] / tid[], idle until the selection at the very end.
+    static_assert(2u * KCAP * 4u >= NT * 16u, "tkey and tid hold one 16-byte table per thread");
+    const uint32_t lean_tab = (uint32_t)__cvta_generic_to_shared(sm->tkey) + tid * 16u;
+    const uint32_t lean_rpb = (nfull + 7u) / 8u;  // rounds per table entry
+    auto p1_issue = [&](uint32_t r) {  // full rounds only; always one commit
+        if (r < nfull) {
+            const char *src = my_src + (size_t)r * (ROUND * sizeof(T));
+            const uint32_t dst = p1_slot[r % P1_STAGES];
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16u), "l"(src + 16)
+                         : "memory");
+        }
+        cp_async_commit();
+    };
+    if (VEC && lean_cand) {
+#pragma unroll
+        for (int st = STAGES - 1; st < P1_STAGES - 1; ++st) {
+            p1_issue((uint32_t)st);
+        }
+    }
 
     // ---- A. bitmaps
     const uint32_t slice_words = (c.hi - c.lo + 31u) >> 5;
+    // One unsigned compare covers both ends of the slice. Real histories
+    // repeat a few ids very often: the atomic is skipped when the bit is
+    // already up.
+    auto mark = [&](uint32_t id) {
+        const uint32_t off = id - c.lo;
+        if (off < c.hi - c.lo) {
+            const uint32_t bit = 1u << (off & 31u);
+            uint32_t *word = &seen[off >> 5];
+            if (!(*reinterpret_cast<volatile uint32_t *>(word) & bit)) {
+                atomicOr(word, bit);
+            }
+        }
+    };
+    // The first part of a plain history list is marked inside pass 1, one
+    // 16-byte load per thread and round, hidden behind the logits' latency.
+    const bool hist_vec = (reinterpret_cast<uintptr_t>(hist) & 15u) == 0u;
+    const uint32_t fused4 = (VEC && lean_cand && hist_vec && !c.need_counts && hist_len > 0u)
+                                ? min(hist_len / 4u, nfull * (uint32_t)NT)
+                                : 0u;
     if (tid == 0) {
         sm->ctx = c;
         sm->n = 0;
@@ -1415,19 +1614,6 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     if (hist_len + extra_len > 0u) {
         const uint32_t lo = c.lo;
         const uint32_t width = c.hi - c.lo;
-        // One unsigned compare covers both ends of the slice. Real histories
-        // repeat a few ids very often: the atomic is skipped when the bit is
-        // already up.
-        auto mark = [&](uint32_t id) {
-            const uint32_t off = id - lo;
-            if (off < width) {
-                const uint32_t bit = 1u << (off & 31u);
-                uint32_t *word = &seen[off >> 5];
-                if (!(*reinterpret_cast<volatile uint32_t *>(word) & bit)) {
-                    atomicOr(word, bit);
-                }
-            }
-        };
         // With the frequency penalty the multiplicities go to the row's
         // count table as well: one global atomic per distinct id of the warp.
         auto mark_count = [&](uint32_t id) {
@@ -1447,11 +1633,10 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             }
         };
         // The bulk of the list in 16-byte loads, four in flight per thread.
-        const bool hvec = (reinterpret_cast<uintptr_t>(hist) & 15u) == 0u;
-        const uint32_t n4 = hvec ? hist_len / 4u : 0u;
+        const uint32_t n4 = hist_vec ? hist_len / 4u : 0u;
         const uint4 *h4 = reinterpret_cast<const uint4 *>(hist);
         constexpr int HB = 4;
-        for (uint32_t i0 = 0; i0 < n4; i0 += NT * HB) {
+        for (uint32_t i0 = fused4; i0 < n4; i0 += NT * HB) {
             uint4 q[HB];
 #pragma unroll
             for (int j = 0; j < HB; ++j) {
@@ -1517,45 +1702,37 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // value of the slice: an exact, tight threshold before any logit is
     // looked at closely. Pass 2 (after the lists, below) streams the slice
     // again, from L2 this time, against that fixed threshold.
-    bool lean = c.k <= 128u && (!c.use_pen || c.monotone) && nrounds > 0u;
+    bool lean = lean_cand;
     if (lean) {
         constexpr uint32_t NONE = 0xFFFFFFFFu;
         float best = neg_inf();
         uint32_t best_r = NONE;
         bool saw_nan = false;
         {
-            const uint32_t ring_me = (uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES;
-            const char *src = my_src + (size_t)(STAGES - 1) * (ROUND * sizeof(T));  // round r + STAGES - 1
-            for (uint32_t r = 0; r < nfull; ++r) {
-                if (VEC) {
-                    if (r + STAGES - 1 < nfull) {
-                        const uint32_t dst = ring_me + ((r + STAGES - 1) % STAGES) * (NT * FRAG_BYTES);
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src)
-                                     : "memory");
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16u),
-                                     "l"(src + 16)
-                                     : "memory");
-                        cp_async_commit();
-                    } else {
-                        issue(r + STAGES - 1);
+            if (VEC) {
+                const Pass1 p1 = lean_pass1<T>(p1_slot[0], p1_slot[2], my_src, nfull,
+                                               reinterpret_cast<const uint4 *>(hist), fused4, seen, c.lo,
+                                               c.hi - c.lo, lean_tab, lean_rpb);
+                best = p1.best;
+                best_r = p1.best_r;
+                saw_nan = p1.saw_nan != 0u;
+            } else {
+                for (uint32_t r = 0; r < nfull; ++r) {
+                    Frag cur;
+                    load_frag_scalar<T>(cur, row_ptr, c.lo + r * ROUND + tid * GROUP, c.hi);
+                    const float m = frag_max<T>(cur);
+                    saw_nan = saw_nan || m != m;
+                    if (best_r == NONE || m > best) {
+                        best = m;
+                        best_r = r;
                     }
-                    src += ROUND * sizeof(T);
-                }
-                Frag cur;
-                fetch(r, cur);
-                const float m = frag_max<T>(cur);
-                saw_nan = saw_nan || m != m;
-                if (best_r == NONE || m > best) {
-                    best = m;
-                    best_r = r;
                 }
             }
             if (nrounds > nfull) {
                 const uint32_t r = nfull;
-                issue(r + STAGES - 1);
                 Frag cur;
-                fetch(r, cur);
                 const uint32_t base = c.lo + r * ROUND + tid * GROUP;
+                load_frag_scalar<T>(cur, row_ptr, base, c.hi);
                 const uint32_t nvalid = base < c.hi ? min(GROUP, c.hi - base) : 0u;
 #pragma unroll
                 for (int e = 0; e < (int)GROUP; ++e) {
@@ -1571,6 +1748,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             }
             cp_async_wait<0>();
         }
+#ifdef LILY_DEBUG
+        if (a.debug_stop == 6u) return;
+#endif
         // A NaN anywhere, or fewer than k threads with a logit: the general path.
         const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE);
         lean = !__syncthreads_or(saw_nan) && have >= c.k;
@@ -1595,16 +1775,19 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 id = base + at;
                 key = adjusted_key(sm, id, l, c.has_special && is_special(sm, c, id));
             }
-            sm->key[tid] = key;
-            sm->id[tid] = id;
-            __syncthreads();
-            select_topk(sm, NT, c.k);  // the fillers (key 0) rank last: have >= k
+            // The largest v (low 8 bits clear) that at least k of the 512 keys
+            // reach, bit by bit from the top: a block-wide count per bit.
+            uint32_t kth = 0u;
+#pragma unroll 1
+            for (int bit = 31; bit >= 8; --bit) {
+                const uint32_t cand = kth | (1u << bit);
+                if ((uint32_t)__syncthreads_count(key >= cand) >= c.k) {
+                    kth = cand;
+                }
+            }
             if (tid == 0) {
                 // Ties with the k-th value must still pass: one key below it.
-                const uint32_t kth = sm->tau_key;
                 set_exact_threshold(sm, kth > 0u ? kth - 1u : 0u);
-                sm->n = 0;
-                sm->n_adj = 0;
             }
             __syncthreads();
         }
@@ -1732,56 +1915,26 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     if (lean) {
         const uint32_t n_lists = min(sm->n, CAP);  // what the lists pushed
         const float c_fix = sm->c_raw;
-        auto take = [&](const Frag &cur, uint32_t r, uint32_t base, uint32_t valid) {
-            const T *slot = VEC ? reinterpret_cast<const T *>(&ring[((r % STAGES) * NT + tid) * 2u])
-                                : nullptr;
-            uint32_t pass = pass_mask<T>(cur, c_fix) & valid;
-            while (pass != 0u) {
-                const uint32_t e = (uint32_t)__ffs(pass) - 1u;
-                pass &= pass - 1u;
-                const float l = slot != nullptr ? widen(slot[e]) : frag_pick<T>(cur, e);
-                const uint32_t id = base + e;
-                if (c.has_special && is_special(sm, c, id)) {
-                    continue;
-                }
-                push(sm, __float_as_uint(l), id);  // a full buffer raises the overflow flag
-            }
-        };
         {
-            const uint32_t ring_me = (uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES;
-            const char *src = my_src + (size_t)(STAGES - 1) * (ROUND * sizeof(T));
             uint32_t base = c.lo + tid * GROUP;
-            for (uint32_t r = 0; r < nfull; ++r) {
-                if (VEC) {
-                    if (r + STAGES - 1 < nfull) {
-                        const uint32_t dst = ring_me + ((r + STAGES - 1) % STAGES) * (NT * FRAG_BYTES);
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src)
-                                     : "memory");
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + 16u),
-                                     "l"(src + 16)
-                                     : "memory");
-                        cp_async_commit();
-                    } else {
-                        issue(r + STAGES - 1);
+            if (VEC) {
+                lean_pass2<T>(sm, my_src, nfull, base, c_fix, lean_tab, lean_rpb);
+                base += nfull * ROUND;
+            } else {
+                for (uint32_t r = 0; r < nfull; ++r) {
+                    Frag cur;
+                    load_frag_scalar<T>(cur, row_ptr, base, c.hi);
+                    if (!(frag_max<T>(cur) <= c_fix)) {
+                        lean_take<T>(sm, cur, base, 0xFFFFFFFFu, c_fix);
                     }
-                    src += ROUND * sizeof(T);
+                    base += ROUND;
                 }
-                Frag cur;
-                fetch(r, cur);
-                if (!(frag_max<T>(cur) <= c_fix)) {
-                    take(cur, r, base, 0xFFFFFFFFu);
-                }
-                base += ROUND;
             }
-            if (nrounds > nfull) {
-                const uint32_t r = nfull;
-                issue(r + STAGES - 1);
+            if (nrounds > nfull && base < c.hi) {
                 Frag cur;
-                fetch(r, cur);
-                if (base < c.hi) {
-                    const uint32_t nvalid = min(GROUP, c.hi - base);
-                    take(cur, r, base, nvalid >= 32u ? 0xFFFFFFFFu : (1u << nvalid) - 1u);
-                }
+                load_frag_scalar<T>(cur, row_ptr, base, c.hi);
+                const uint32_t nvalid = min(GROUP, c.hi - base);
+                lean_take<T>(sm, cur, base, nvalid >= 32u ? 0xFFFFFFFFu : (1u << nvalid) - 1u, c_fix);
             }
             cp_async_wait<0>();
         }
