@@ -1337,13 +1337,32 @@ __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_
     while (buckets != 0u) {
         const uint32_t b = (uint32_t)__ffs(buckets) - 1u;
         buckets &= buckets - 1u;
-        const uint32_t end = min((b + 1u) * rpb, nfull);
-        for (uint32_t rr = b * rpb; rr < end; ++rr) {
-            Frag cur;
-            cur.v[0] = __ldcg(src + rr * STRIDE);
-            cur.v[1] = __ldcg(src + rr * STRIDE + 1);
-            if (!(frag_max<T>(cur) <= c_fix)) {
-                lean_take<T>(sm, cur, base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+        const uint32_t r0 = b * rpb;
+        const uint32_t end = min(r0 + rpb, nfull);
+        if (rpb <= 4u) {
+            // All of the bucket's rounds are asked for before the first is looked at.
+            Frag f[4];
+#pragma unroll
+            for (uint32_t j = 0; j < 4u; ++j) {
+                if (r0 + j < end) {
+                    f[j].v[0] = __ldcg(src + (r0 + j) * STRIDE);
+                    f[j].v[1] = __ldcg(src + (r0 + j) * STRIDE + 1);
+                }
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 4u; ++j) {
+                if (r0 + j < end && !(frag_max<T>(f[j]) <= c_fix)) {
+                    lean_take<T>(sm, f[j], base0 + (r0 + j) * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+                }
+            }
+        } else {
+            for (uint32_t rr = r0; rr < end; ++rr) {
+                Frag cur;
+                cur.v[0] = __ldcg(src + rr * STRIDE);
+                cur.v[1] = __ldcg(src + rr * STRIDE + 1);
+                if (!(frag_max<T>(cur) <= c_fix)) {
+                    lean_take<T>(sm, cur, base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+                }
             }
         }
     }
@@ -1751,6 +1770,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 #ifdef LILY_DEBUG
         if (a.debug_stop == 6u) return;
 #endif
+        LILY_STAMP(PH_SELECT0);
         // A NaN anywhere, or fewer than k threads with a logit: the general path.
         const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE);
         lean = !__syncthreads_or(saw_nan) && have >= c.k;
@@ -1760,7 +1780,13 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 // Which logit of that round it was: the round is read once more.
                 Frag again;
                 const uint32_t base = c.lo + best_r * ROUND + tid * GROUP;
-                load_frag_scalar<T>(again, row_ptr, base, c.hi);
+                if (VEC && best_r < nfull) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(my_src + (size_t)best_r * ROUND_BYTES);
+                    again.v[0] = __ldcg(src);
+                    again.v[1] = __ldcg(src + 1);
+                } else {
+                    load_frag_scalar<T>(again, row_ptr, base, c.hi);
+                }
                 const uint32_t nvalid = min(GROUP, c.hi - base);
                 uint32_t at = 0;
                 float l = best;
@@ -1775,11 +1801,11 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 id = base + at;
                 key = adjusted_key(sm, id, l, c.has_special && is_special(sm, c, id));
             }
-            // The largest v (low 8 bits clear) that at least k of the 512 keys
+            // The largest v (low 16 bits clear) that at least k of the 512 keys
             // reach, bit by bit from the top: a block-wide count per bit.
             uint32_t kth = 0u;
 #pragma unroll 1
-            for (int bit = 31; bit >= 8; --bit) {
+            for (int bit = 31; bit >= 16; --bit) {
                 const uint32_t cand = kth | (1u << bit);
                 if ((uint32_t)__syncthreads_count(key >= cand) >= c.k) {
                     kth = cand;
