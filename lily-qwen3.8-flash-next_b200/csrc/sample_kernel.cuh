@@ -1227,26 +1227,40 @@ __device__ __forceinline__ void lean_read_slot(uint32_t at, Frag &f) {
                  : "r"(at + 16u));
 }
 
+__device__ __forceinline__ void lean_write_slot(uint32_t at, const Frag &f) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(f.v[0].x), "r"(f.v[0].y),
+                 "r"(f.v[0].z), "r"(f.v[0].w)
+                 : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at + 16u), "r"(f.v[1].x), "r"(f.v[1].y),
+                 "r"(f.v[1].z), "r"(f.v[1].w)
+                 : "memory");
+}
+
 // Pass 1 over the full rounds of a 16-byte aligned row: four rounds in
 // flight (stages 0, 1 at slot_a, 2, 3 at slot_b; rounds 0..2 are already on
-// their way), the thread's running maximum, and (fused4 != 0) four history
-// ids per thread and round marked in the seen bitmap of [lo, lo + width).
-// The maximum of every `rpb` consecutive rounds is also left, rounded up to a
-// bf16, in the thread's 16-byte table at `tab` (8 entries): pass 2 reads only
-// the rounds whose entry beats the threshold.
+// their way), and (fused4 != 0) four history ids per thread and round marked
+// in the seen bitmap of [lo, lo + width).
+//
+// Per thread it keeps the fragment with the largest logit (left in the
+// thread's stage-1 slot at the end), the round and maximum of the second
+// best fragment and the maximum over all the others (left at `tab`: m2, r2,
+// m3): pass 2 then needs the row again only where the second or a further
+// fragment of a thread also beats the threshold.
 template <typename T>
 __device__ __noinline__ Pass1 lean_pass1(uint32_t slot_a, uint32_t slot_b, const char *src0, uint32_t nfull,
                                          const uint4 *h4, uint32_t fused4, uint32_t *seen, uint32_t lo,
-                                         uint32_t width, uint32_t tab, uint32_t rpb) {
+                                         uint32_t width, uint32_t tab) {
     constexpr uint32_t NONE = 0xFFFFFFFFu;
     const uint32_t tid = threadIdx.x;
     Pass1 out;
     out.best = neg_inf();
     out.best_r = NONE;
     out.saw_nan = 0u;
-    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(tab), "r"(0xFF80FF80u) : "memory");
-    float bucket_max = neg_inf();
-    uint32_t in_bucket = 0, tab_at = tab;
+    float m2 = neg_inf(), m3 = neg_inf();
+    uint32_t r2 = NONE;
+    Frag keep;
+    keep.v[0] = make_uint4(0, 0, 0, 0);
+    keep.v[1] = make_uint4(0, 0, 0, 0);
     const uint4 no_ids = make_uint4(NONE, NONE, NONE, NONE);
     uint4 hq = tid < fused4 ? __ldg(h4 + tid) : no_ids;
     const char *src = src0 + 3u * ROUND_BYTES;  // the round three ahead
@@ -1281,24 +1295,27 @@ __device__ __noinline__ Pass1 lean_pass1(uint32_t slot_a, uint32_t slot_b, const
                 const float m = frag_max<T>(cur);
                 out.saw_nan |= m != m ? 1u : 0u;
                 if (out.best_r == NONE || m > out.best) {
+                    m3 = fmaxf(m3, m2);
+                    m2 = out.best;
+                    r2 = out.best_r;
                     out.best = m;
                     out.best_r = rr;
-                }
-                bucket_max = fmaxf(bucket_max, m);
-                if (++in_bucket == rpb || rr + 1u == nfull) {
-                    // Rounded up: a positive value with low bits set goes one bf16 up,
-                    // a negative one is truncated towards zero.
-                    const uint32_t bits = __float_as_uint(bucket_max);
-                    const uint32_t up = (bits >> 16) + (((bits & 0xFFFFu) != 0u && !(bits >> 31)) ? 1u : 0u);
-                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(tab_at), "h"((unsigned short)up) : "memory");
-                    tab_at += 2u;
-                    in_bucket = 0;
-                    bucket_max = neg_inf();
+                    keep = cur;
+                } else if (r2 == NONE || m > m2) {
+                    m3 = fmaxf(m3, m2);
+                    m2 = m;
+                    r2 = rr;
+                } else {
+                    m3 = fmaxf(m3, m);
                 }
             }
         }
     }
     cp_async_wait<0>();
+    lean_write_slot(slot_a + ROUND_BYTES, keep);
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tab), "r"(__float_as_uint(m2)), "r"(r2),
+                 "r"(__float_as_uint(m3)), "r"(0u)
+                 : "memory");
     return out;
 }
 
@@ -1320,49 +1337,47 @@ __device__ __noinline__ void lean_take(SmemFixed *sm, const Frag &cur, uint32_t 
     }
 }
 
-// Pass 2 over the full rounds of a 16-byte aligned row: only the rounds whose
-// table entry (pass 1) beats c_fix are read again, from L2 or DRAM, a few
-// dozen 32-byte fragments per row.
+// Pass 2 over the full rounds of a 16-byte aligned row, from what pass 1
+// left: the thread's best fragment (round r1, in its stage-1 slot) needs no
+// memory at all; its second best (m2, round r2) is read again only if it
+// beats the threshold too; only if a third fragment could (m3) does the
+// thread walk its rounds once more.
 template <typename T>
 __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_t nfull, uint32_t base0,
-                                        float c_fix, uint32_t tab, uint32_t rpb) {
-    Frag table;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(table.v[0].x), "=r"(table.v[0].y), "=r"(table.v[0].z), "=r"(table.v[0].w)
-                 : "r"(tab));
-    table.v[1] = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
-    uint32_t buckets = pass_mask<__nv_bfloat16>(table, c_fix) & 0xFFu;
+                                        float c_fix, uint32_t slot_keep, uint32_t tab, float m1, uint32_t r1) {
+    constexpr uint32_t NONE = 0xFFFFFFFFu;
+    if (r1 == NONE) {
+        return;
+    }
+    uint32_t m2b, r2, m3b, unused;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(m2b), "=r"(r2), "=r"(m3b), "=r"(unused) : "r"(tab));
+    const float m2 = __uint_as_float(m2b), m3 = __uint_as_float(m3b);
     const uint4 *src = reinterpret_cast<const uint4 *>(src0);
     constexpr uint32_t STRIDE = ROUND_BYTES / 16u;
-    while (buckets != 0u) {
-        const uint32_t b = (uint32_t)__ffs(buckets) - 1u;
-        buckets &= buckets - 1u;
-        const uint32_t r0 = b * rpb;
-        const uint32_t end = min(r0 + rpb, nfull);
-        if (rpb <= 4u) {
-            // All of the bucket's rounds are asked for before the first is looked at.
-            Frag f[4];
-#pragma unroll
-            for (uint32_t j = 0; j < 4u; ++j) {
-                if (r0 + j < end) {
-                    f[j].v[0] = __ldcg(src + (r0 + j) * STRIDE);
-                    f[j].v[1] = __ldcg(src + (r0 + j) * STRIDE + 1);
-                }
+    const bool second = r2 != NONE && !(m2 <= c_fix);
+    Frag f2;
+    if (second) {
+        f2.v[0] = __ldcg(src + r2 * STRIDE);
+        f2.v[1] = __ldcg(src + r2 * STRIDE + 1);
+    }
+    if (!(m1 <= c_fix)) {
+        Frag keep;
+        lean_read_slot(slot_keep, keep);
+        lean_take<T>(sm, keep, base0 + r1 * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+    }
+    if (second) {
+        lean_take<T>(sm, f2, base0 + r2 * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+    }
+    if (!(m3 <= c_fix)) {
+        for (uint32_t rr = 0; rr < nfull; ++rr) {
+            if (rr == r1 || rr == r2) {
+                continue;
             }
-#pragma unroll
-            for (uint32_t j = 0; j < 4u; ++j) {
-                if (r0 + j < end && !(frag_max<T>(f[j]) <= c_fix)) {
-                    lean_take<T>(sm, f[j], base0 + (r0 + j) * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
-                }
-            }
-        } else {
-            for (uint32_t rr = r0; rr < end; ++rr) {
-                Frag cur;
-                cur.v[0] = __ldcg(src + rr * STRIDE);
-                cur.v[1] = __ldcg(src + rr * STRIDE + 1);
-                if (!(frag_max<T>(cur) <= c_fix)) {
-                    lean_take<T>(sm, cur, base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
-                }
+            Frag cur;
+            cur.v[0] = __ldcg(src + rr * STRIDE);
+            cur.v[1] = __ldcg(src + rr * STRIDE + 1);
+            if (!(frag_max<T>(cur) <= c_fix)) {
+                lean_take<T>(sm, cur, base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
             }
         }
     }
@@ -1552,11 +1567,10 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         (uint32_t)__cvta_generic_to_shared(ring) + (NT + tid) * FRAG_BYTES,
         (uint32_t)__cvta_generic_to_shared(sm->key) + tid * FRAG_BYTES,
         (uint32_t)__cvta_generic_to_shared(sm->id) + tid * FRAG_BYTES};
-    // Each thread's 16-byte table of per-bucket maxima (pass 1 -> pass 2) sits
-    // in tkey[] / tid[], idle until the selection at the very end.
-    static_assert(2u * KCAP * 4u >= NT * 16u, "tkey and tid hold one 16-byte table per thread");
+    // Each thread's 16 bytes of pass 1 -> pass 2 state sit in tkey[] / tid[],
+    // idle until the selection at the very end.
+    static_assert(2u * KCAP * 4u >= NT * 16u, "tkey and tid hold 16 bytes per thread");
     const uint32_t lean_tab = (uint32_t)__cvta_generic_to_shared(sm->tkey) + tid * 16u;
-    const uint32_t lean_rpb = (nfull + 7u) / 8u;  // rounds per table entry
     auto p1_issue = [&](uint32_t r) {  // full rounds only; always one commit
         if (r < nfull) {
             const char *src = my_src + (size_t)r * (ROUND * sizeof(T));
@@ -1722,6 +1736,8 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // looked at closely. Pass 2 (after the lists, below) streams the slice
     // again, from L2 this time, against that fixed threshold.
     bool lean = lean_cand;
+    float full_best = neg_inf();           // pass 1's result over the full rounds, for pass 2
+    uint32_t full_best_r = 0xFFFFFFFFu;
     if (lean) {
         constexpr uint32_t NONE = 0xFFFFFFFFu;
         float best = neg_inf();
@@ -1731,10 +1747,12 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             if (VEC) {
                 const Pass1 p1 = lean_pass1<T>(p1_slot[0], p1_slot[2], my_src, nfull,
                                                reinterpret_cast<const uint4 *>(hist), fused4, seen, c.lo,
-                                               c.hi - c.lo, lean_tab, lean_rpb);
+                                               c.hi - c.lo, lean_tab);
                 best = p1.best;
                 best_r = p1.best_r;
                 saw_nan = p1.saw_nan != 0u;
+                full_best = p1.best;
+                full_best_r = p1.best_r;
             } else {
                 for (uint32_t r = 0; r < nfull; ++r) {
                     Frag cur;
@@ -1774,16 +1792,15 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         // A NaN anywhere, or fewer than k threads with a logit: the general path.
         const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE);
         lean = !__syncthreads_or(saw_nan) && have >= c.k;
+        LILY_STAMP(PH_THRESH0);
         if (lean) {
             uint32_t key = 0u, id = NONE;
             if (best_r != NONE) {
-                // Which logit of that round it was: the round is read once more.
+                // Which logit of that round it was: pass 1 kept the fragment.
                 Frag again;
                 const uint32_t base = c.lo + best_r * ROUND + tid * GROUP;
                 if (VEC && best_r < nfull) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(my_src + (size_t)best_r * ROUND_BYTES);
-                    again.v[0] = __ldcg(src);
-                    again.v[1] = __ldcg(src + 1);
+                    lean_read_slot(p1_slot[1], again);
                 } else {
                     load_frag_scalar<T>(again, row_ptr, base, c.hi);
                 }
@@ -1801,6 +1818,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 id = base + at;
                 key = adjusted_key(sm, id, l, c.has_special && is_special(sm, c, id));
             }
+            LILY_STAMP(PH_R1);
             // The largest v (low 16 bits clear) that at least k of the 512 keys
             // reach, bit by bit from the top: a block-wide count per bit.
             uint32_t kth = 0u;
@@ -1811,11 +1829,13 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                     kth = cand;
                 }
             }
+            LILY_STAMP(PH_R4);
             if (tid == 0) {
                 // Ties with the k-th value must still pass: one key below it.
                 set_exact_threshold(sm, kth > 0u ? kth - 1u : 0u);
             }
             __syncthreads();
+            LILY_STAMP(PH_R8);
         }
         // The ring starts over at round 0 for whichever stream follows.
 #pragma unroll
@@ -1944,7 +1964,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         {
             uint32_t base = c.lo + tid * GROUP;
             if (VEC) {
-                lean_pass2<T>(sm, my_src, nfull, base, c_fix, lean_tab, lean_rpb);
+                lean_pass2<T>(sm, my_src, nfull, base, c_fix, p1_slot[1], lean_tab, full_best, full_best_r);
                 base += nfull * ROUND;
             } else {
                 for (uint32_t r = 0; r < nfull; ++r) {
