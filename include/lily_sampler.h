@@ -158,9 +158,13 @@ int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream, uint32_t slot
 /*
  * With LILY_FLAG_PHASE_CLOCKS: copies the SM clock stamps of the last launch
  * to host_out[max_rows][LILY_MAX_SLICES][LILY_PHASES] (int64 each, 0 where a
- * block did not pass) and clears them; synchronises `stream`. Stamps, in
- * order: start, history bitmap built, bias/ban ids done, vocabulary streamed,
- * block's best k selected, slices merged, candidates sorted, draw done.
+ * block did not pass) and clears them; synchronises `stream`. Stamps 0..7,
+ * in order: start, history bitmap built, bias/ban ids done, vocabulary
+ * streamed, block's best k selected, slices merged, candidates sorted, draw
+ * done. Stamps 8..13 lie between "bitmap built" and "bias/ban ids done":
+ * 8 first threshold known; and on the two-pass route (small k) before it
+ * 9 pass 1 over the logits done (thread 0), 10 whole block done with it,
+ * 11 thread maxima adjusted, 12 threshold searched, 13 threshold stored.
  */
 int32_t lily_sampler_read_phase_clocks(lily_sampler_t *h, void *stream, int64_t *host_out);
 

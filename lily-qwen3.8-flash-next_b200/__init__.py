@@ -346,13 +346,26 @@ class SamplerScratch:
         return out
 
     # -- draws
-    def sample_batch(self, logits, params, out_ids, *, uniforms=None, steps=None,
+    def sample_batch(self, logits, params, out_ids, *, stream=None, **kw):
+        """lily_sample_batch: `params` is a list of SamplingParams (host), or with
+        params_on_device a uint8 tensor holding the 40-byte structs."""
+        a, keep = self._sample_args(logits, params, out_ids, **kw)
+        self._check(lib().lily_sample_batch(self._h, _stream_ptr(stream), C.byref(a)))
+
+    def prepare_sample_batch(self, logits, params, out_ids, **kw):
+        """The argument block of a sample_batch call, built once: a decode loop
+        that draws from the same buffers every step passes it to
+        sample_prepared() and pays no per-step marshalling."""
+        return self._sample_args(logits, params, out_ids, **kw)
+
+    def sample_prepared(self, prepared, stream=None):
+        self._check(lib().lily_sample_batch(self._h, _stream_ptr(stream), C.byref(prepared[0])))
+
+    def _sample_args(self, logits, params, out_ids, *, uniforms=None, steps=None,
                      history_ids=None, history_len=None, bias_ids=None, bias_vals=None,
                      bias_len=None, ban_ids=None, ban_len=None, forced_ids=None,
                      count_slots=None, out_status=None, kept_n=None, kept_ids=None,
-                     kept_probs=None, params_on_device=False, stream=None):
-        """lily_sample_batch: `params` is a list of SamplingParams (host), or with
-        params_on_device a uint8 tensor holding the 40-byte structs."""
+                     kept_probs=None, params_on_device=False):
         rows = logits.shape[0] if logits.dim() == 2 else 1
         a = SampleArgs()
         a.struct_size = C.sizeof(SampleArgs)
@@ -394,7 +407,7 @@ class SamplerScratch:
         if kept_n is not None:
             a.kept_n, a.kept_ids, a.kept_probs = _ptr(kept_n), _ptr(kept_ids), _ptr(kept_probs)
             a.kept_ld = _ld(kept_ids)
-        self._check(lib().lily_sample_batch(self._h, _stream_ptr(stream), C.byref(a)))
+        return a, keep
 
     # -- 8-bit LM head and vocabulary shards
     @staticmethod

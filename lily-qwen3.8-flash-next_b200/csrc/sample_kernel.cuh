@@ -1369,15 +1369,23 @@ __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_
         lean_take<T>(sm, f2, base0 + r2 * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
     }
     if (!(m3 <= c_fix)) {
-        for (uint32_t rr = 0; rr < nfull; ++rr) {
-            if (rr == r1 || rr == r2) {
-                continue;
+        // Rare (a third fragment of this thread may matter): all rounds again,
+        // four loads in flight at a time.
+        for (uint32_t r0 = 0; r0 < nfull; r0 += 4u) {
+            Frag f[4];
+#pragma unroll
+            for (uint32_t j = 0; j < 4u; ++j) {
+                if (r0 + j < nfull) {
+                    f[j].v[0] = __ldcg(src + (r0 + j) * STRIDE);
+                    f[j].v[1] = __ldcg(src + (r0 + j) * STRIDE + 1);
+                }
             }
-            Frag cur;
-            cur.v[0] = __ldcg(src + rr * STRIDE);
-            cur.v[1] = __ldcg(src + rr * STRIDE + 1);
-            if (!(frag_max<T>(cur) <= c_fix)) {
-                lean_take<T>(sm, cur, base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+#pragma unroll
+            for (uint32_t j = 0; j < 4u; ++j) {
+                const uint32_t rr = r0 + j;
+                if (rr < nfull && rr != r1 && rr != r2 && !(frag_max<T>(f[j]) <= c_fix)) {
+                    lean_take<T>(sm, f[j], base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+                }
             }
         }
     }
@@ -1385,7 +1393,8 @@ __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_
 
 // Phase stamps for the optional per-block timing trace.
 enum { PH_START = 0, PH_BITMAPS, PH_LISTS, PH_STREAM, PH_LOCAL_SELECT, PH_MERGE, PH_SORT, PH_END,
-       PH_ROUND0, PH_SELECT0, PH_THRESH0, PH_R1, PH_R4, PH_R8, PH_R16, PH_R32 };
+       PH_FIRST_THRESHOLD, PH_PASS1, PH_PASS1_MET, PH_MAXIMA, PH_SEARCH, PH_THRESHOLD_SET, PH_SPARE0,
+       PH_SPARE1 };
 
 #define LILY_STAMP(phase)                                                                  \
     do {                                                                                   \
@@ -1407,6 +1416,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     const uint32_t slice = blockIdx.x;
     const uint32_t out_row = row;
 
+    // The row's history length is asked for now: its latency overlaps that
+    // of the parameters below.
+    const uint32_t hist_len_row = (a.history_ids && a.history_len) ? __ldg(a.history_len + row) : 0u;
     // ---- forced rows and parameters (uniform per block, before any barrier)
     if (a.forced_ids) {
         const int32_t forced = a.forced_ids[row];
@@ -1505,9 +1517,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                                : a.counts_scratch + (uint64_t)row * a.vocab;
     }
     c.counts = counts_rw;
-    const uint32_t hist_len = (c.use_pen && !table_mode && a.history_ids && a.history_len)
-                                  ? a.history_len[row]
-                                  : 0u;
+    const uint32_t hist_len = (c.use_pen && !table_mode) ? hist_len_row : 0u;
     const uint32_t *hist = a.history_ids ? a.history_ids + (uint64_t)row * a.history_ld : nullptr;
     const uint32_t extra_len = (c.use_pen && !table_mode) ? a.extra_len : 0u;
     const T *row_ptr = reinterpret_cast<const T *>(a.logits) + (uint64_t)row * a.logits_ld;
@@ -1788,11 +1798,11 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 #ifdef LILY_DEBUG
         if (a.debug_stop == 6u) return;
 #endif
-        LILY_STAMP(PH_SELECT0);
+        LILY_STAMP(PH_PASS1);
         // A NaN anywhere, or fewer than k threads with a logit: the general path.
         const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE);
         lean = !__syncthreads_or(saw_nan) && have >= c.k;
-        LILY_STAMP(PH_THRESH0);
+        LILY_STAMP(PH_PASS1_MET);
         if (lean) {
             uint32_t key = 0u, id = NONE;
             if (best_r != NONE) {
@@ -1818,7 +1828,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 id = base + at;
                 key = adjusted_key(sm, id, l, c.has_special && is_special(sm, c, id));
             }
-            LILY_STAMP(PH_R1);
+            LILY_STAMP(PH_MAXIMA);
             // The largest v (low 16 bits clear) that at least k of the 512 keys
             // reach, bit by bit from the top: a block-wide count per bit.
             uint32_t kth = 0u;
@@ -1829,13 +1839,13 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                     kth = cand;
                 }
             }
-            LILY_STAMP(PH_R4);
+            LILY_STAMP(PH_SEARCH);
             if (tid == 0) {
                 // Ties with the k-th value must still pass: one key below it.
                 set_exact_threshold(sm, kth > 0u ? kth - 1u : 0u);
             }
             __syncthreads();
-            LILY_STAMP(PH_R8);
+            LILY_STAMP(PH_THRESHOLD_SET);
         }
         // The ring starts over at round 0 for whichever stream follows.
 #pragma unroll
@@ -1924,7 +1934,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         set_raw_edge(sm, edge0);
     }
     }  // !lean
-    LILY_STAMP(PH_ROUND0);
+    LILY_STAMP(PH_FIRST_THRESHOLD);
 #ifdef LILY_DEBUG
     if (a.debug_stop == 2u) return;
 #endif
