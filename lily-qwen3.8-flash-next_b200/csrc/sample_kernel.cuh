@@ -721,29 +721,9 @@ __device__ __noinline__ void finalize(SmemFixed *sm, const KArgs &a, uint32_t ro
         p[i] = exp_f32(__fsub_rn(float_of_key(sm->key[i]), top));
     }
     Team<SMALL>::sync();
-    if (SMALL) {
-        // n <= 64: every lane runs the same sequential sum over values handed
-        // round by shuffles (rank order, one rounding per add), and keeps the
-        // prefixes of its own two slots.
-        const float p0 = me < n ? p[me] : 0.0f;
-        const float p1 = me + 32u < n ? p[me + 32u] : 0.0f;
-        float s = 0.0f, c0 = 0.0f, c1 = 0.0f;
-        for (uint32_t j = 0; j < n; ++j) {
-            const float v = __shfl_sync(0xFFFFFFFFu, j < 32u ? p0 : p1, (int)(j & 31u));
-            s = __fadd_rn(s, v);
-            c0 = j == me ? s : c0;
-            c1 = j == me + 32u ? s : c1;
-        }
-        if (me < n) {
-            cum[me] = c0;
-        }
-        if (me + 32u < n) {
-            cum[me + 32u] = c1;
-        }
-        if (me == 0) {
-            sm->n_keep = n;
-        }
-    } else if (me == 0) {
+    if (me == 0) {
+        // One thread, rank order, one rounding per add (for n <= 64 too: a
+        // chain of dependent adds is shorter than a chain of shuffles).
         const float *__restrict__ pr = p;
         float *__restrict__ cw = cum;
         float s = 0.0f;
@@ -1419,6 +1399,22 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // The row's history length is asked for now: its latency overlaps that
     // of the parameters below.
     const uint32_t hist_len_row = (a.history_ids && a.history_len) ? __ldg(a.history_len + row) : 0u;
+    // With one slice per row, where the logits are does not depend on the
+    // row's parameters: the first three rounds are asked for before the
+    // parameters have arrived (into the stages pass 1 reads them from).
+    const bool early = VEC && a.n_slices == 1u && a.vocab >= 3u * Geo<T>::ROUND;
+    if (early) {
+        const char *src = reinterpret_cast<const char *>(reinterpret_cast<const T *>(a.logits) +
+                                                         (uint64_t)row * a.logits_ld + tid * Geo<T>::GROUP);
+        const uint32_t dst[3] = {(uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES,
+                                 (uint32_t)__cvta_generic_to_shared(ring) + (NT + tid) * FRAG_BYTES,
+                                 (uint32_t)__cvta_generic_to_shared(sm->key) + tid * FRAG_BYTES};
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            lean_copy_round(dst[j], src + (size_t)j * ROUND_BYTES);
+            cp_async_commit();
+        }
+    }
     // ---- forced rows and parameters (uniform per block, before any barrier)
     if (a.forced_ids) {
         const int32_t forced = a.forced_ids[row];
@@ -1431,6 +1427,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 if (a.kept_n) {
                     a.kept_n[out_row] = 0;
                 }
+            }
+            if (early) {
+                cp_async_wait<0>();
             }
             return;
         }
@@ -1465,6 +1464,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                     a.kept_n[out_row] = 0;
                 }
                 atomicOr(a.status_word, 1u << LILY_ROW_PARAMS);
+            }
+            if (early) {
+                cp_async_wait<0>();
             }
             return;
         }
@@ -1561,9 +1563,11 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             load_frag_scalar<T>(f, row_ptr, c.lo + r * ROUND + tid * GROUP, c.hi);
         }
     };
+    if (!early) {
 #pragma unroll
-    for (int st = 0; st < STAGES - 1; ++st) {
-        issue((uint32_t)st);
+        for (int st = 0; st < STAGES - 1; ++st) {
+            issue((uint32_t)st);
+        }
     }
     // Small k with penalties that only lower a logit takes two passes over
     // the slice (see C0' below). Its first pass is the one that reads DRAM:
@@ -1591,7 +1595,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         }
         cp_async_commit();
     };
-    if (VEC && lean_cand) {
+    if (VEC && lean_cand && !early) {
 #pragma unroll
         for (int st = STAGES - 1; st < P1_STAGES - 1; ++st) {
             p1_issue((uint32_t)st);
@@ -1860,6 +1864,12 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // which the count from the top reaches k gives the first threshold.
     Frag first;
     if (!lean) {
+    if (early) {
+        // Round 2 was copied into key[] ahead of time: it must have landed, in
+        // every thread, before the histogram takes that storage.
+        cp_async_wait<0>();
+        __syncthreads();
+    }
     issue((uint32_t)(STAGES - 1));
     uint32_t *hist0 = sm->key;
     for (uint32_t b = tid; b < H0_BINS; b += NT) {
