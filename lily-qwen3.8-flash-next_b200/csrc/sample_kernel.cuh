@@ -2485,12 +2485,30 @@ __global__ void __launch_bounds__(1024) shard_sums_kernel(const T *logits, uint6
     const T *src = logits + (uint64_t)row * ld;
     const uint32_t len = (vocab + gridDim.x - 1u) / gridDim.x;
     const uint32_t lo = piece * len, hi = min(vocab, lo + len);
+    // exp(l / T - top) as exp2((l - top * T) * log2(e) / T): a reported
+    // statistic, not part of the draw, so the fast exponential will do.
+    const float scale = 1.4426950408889634f / temp;
+    const float shift = top * temp;
     float s = 0.0f;
-    for (uint32_t i = lo + tid; i < hi; i += 1024u) {
-        const float adj = __fdiv_rn(widen(src[i]), temp);
-        if (adj == adj) {
-            s += expf(adj - top);
+    const bool vec = sizeof(T) == 4 && ((reinterpret_cast<uintptr_t>(src) | (lo * sizeof(T))) & 15u) == 0u;
+    uint32_t i = lo + tid;
+    if (vec) {
+        const float4 *src4 = reinterpret_cast<const float4 *>(src + lo);
+        const uint32_t n4 = (hi - lo) / 4u;
+        for (uint32_t q = tid; q < n4; q += 1024u) {
+            const float4 v = __ldcg(src4 + q);
+            const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float t = exp2f((x[e] - shift) * scale);
+                s += t == t ? t : 0.0f;
+            }
         }
+        i = lo + n4 * 4u + tid;
+    }
+    for (; i < hi; i += 1024u) {
+        const float t = exp2f((widen(src[i]) - shift) * scale);
+        s += t == t ? t : 0.0f;
     }
     for (int o = 16; o > 0; o >>= 1) {
         s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
