@@ -50,13 +50,13 @@ def peaks():
     return 6650.0, "fallback"
 
 
-def ncu_traffic():
-    """DRAM bytes per launch of the sampling kernel from the committed ncu
-    summary, if one has been recorded."""
+def ncu_traffic(key="sample_rows_kernel_b256_dram_bytes_per_launch"):
+    """DRAM bytes per launch of a kernel from the committed ncu summary, if
+    one has been recorded."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(path):
         with open(path) as f:
-            return json.load(f).get("sample_rows_kernel_b256_dram_bytes_per_launch")
+            return json.load(f).get(key)
     return None
 
 
@@ -449,6 +449,7 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
             "rows_per_s": tokens / (step_ms * 1e-3), "steps": steps,
             "head_kernel_us": head_ms * 1e3, "head_bytes_per_gpu": head_bytes,
             "head_gbs_per_gpu": gbs, "head_frac_of_hbm": gbs / peak, "peak_kind": peak_kind,
+            "head_traffic_1gpu": ncu_traffic("lmhead_int8_kernel_dram_bytes_per_launch"),
             "allgather_bytes_per_rank": tokens * sh.RECORD_BYTES, "ranks_agree": agree,
             "l2": "one 1.07 GB shard" if copies == 1 else "two weight copies rotated"}
 
