@@ -9,6 +9,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "../../include/lily_sampler.h"
 #include "sample_kernel.cuh"
@@ -62,6 +63,12 @@ struct lily_sampler {
     uint32_t *h_status = nullptr;
     uint32_t attr_mask = 0;  // kernel variants whose shared-memory limit is raised
     long long *phase_clocks = nullptr;
+    // The parameters a sharded call staged last: a decode step stages the same
+    // rows for its candidate call and its merge call, and usually again next step.
+    uint64_t slot_serial[RING] = {};
+    int shard_slot = -1;
+    uint64_t shard_serial = 0;
+    std::vector<char> shard_bytes;
     float *lm_logits = nullptr;  // LILY_FLAG_LMHEAD: F32 [64, lm_ld]
     uint64_t lm_ld = 0;
     bool lm_attr = false, merge_attr = false;
@@ -138,6 +145,7 @@ int32_t next_stage(lily_sampler *h, int *slot) {
     const int s = h->ring_pos;
     h->ring_pos = (h->ring_pos + 1) % RING;
     CU(h, cudaEventSynchronize(h->ev[s]));
+    ++h->slot_serial[s];
     *slot = s;
     return LILY_OK;
 }
@@ -844,21 +852,38 @@ int32_t stage_shard_params(lily_sampler *h, cudaStream_t stream, const lily_samp
             return fail(h, LILY_ERR_ARG, "sharded sampling needs 1 <= top_k <= 64");
         }
     }
-    int slot = -1;
-    int32_t st = next_stage(h, &slot);
-    if (st != LILY_OK) {
-        return st;
+    // What would be staged: [rows][has steps][params][steps].
+    const size_t pb = sizeof(lily_sampling_params_t) * g.rows, sb = g.steps ? sizeof(uint32_t) * g.rows : 0;
+    std::vector<char> want(8 + pb + sb);
+    const uint32_t head[2] = {g.rows, g.steps != nullptr ? 1u : 0u};
+    std::memcpy(want.data(), head, 8);
+    std::memcpy(want.data() + 8, g.params, pb);
+    if (sb) {
+        std::memcpy(want.data() + 8 + pb, g.steps, sb);
     }
-    char *hs = h->h_stage[slot];
-    std::memcpy(hs + h->layout.params, g.params, sizeof(lily_sampling_params_t) * g.rows);
+    int slot = h->shard_slot;
+    const bool reuse = slot >= 0 && h->slot_serial[slot] == h->shard_serial && want == h->shard_bytes;
+    if (!reuse) {
+        int32_t st = next_stage(h, &slot);
+        if (st != LILY_OK) {
+            return st;
+        }
+        char *hs = h->h_stage[slot];
+        std::memcpy(hs + h->layout.params, g.params, pb);
+        if (sb) {
+            std::memcpy(hs + h->layout.steps, g.steps, sb);
+        }
+        CU(h, cudaMemcpyAsync(h->d_stage[slot], h->h_stage[slot], h->layout.total, cudaMemcpyHostToDevice,
+                              stream));
+        h->shard_slot = slot;
+        h->shard_serial = h->slot_serial[slot];
+        h->shard_bytes.swap(want);
+    }
+    // (A reused slot is read by one more launch: the caller records the slot's
+    // event after it, so the ring does not overwrite the slot under that launch.)
     *d_params = reinterpret_cast<const lily_sampling_params_t *>(h->d_stage[slot] + h->layout.params);
-    *d_steps = nullptr;
-    if (g.steps != nullptr) {
-        std::memcpy(hs + h->layout.steps, g.steps, sizeof(uint32_t) * g.rows);
-        *d_steps = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.steps);
-    }
-    CU(h, cudaMemcpyAsync(h->d_stage[slot], h->h_stage[slot], h->layout.total, cudaMemcpyHostToDevice,
-                          stream));
+    *d_steps = g.steps != nullptr ? reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.steps)
+                                  : nullptr;
     *slot_out = slot;
     return LILY_OK;
 }

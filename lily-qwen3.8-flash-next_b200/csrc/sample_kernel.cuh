@@ -1222,10 +1222,10 @@ __device__ __forceinline__ void lean_write_slot(uint32_t at, const Frag &f) {
 // in the seen bitmap of [lo, lo + width).
 //
 // Per thread it keeps the fragment with the largest logit (left in the
-// thread's stage-1 slot at the end), the round and maximum of the second
-// best fragment and the maximum over all the others (left at `tab`: m2, r2,
-// m3): pass 2 then needs the row again only where the second or a further
-// fragment of a thread also beats the threshold.
+// thread's stage-1 slot at the end), the rounds and maxima of the second and
+// third best fragments and the maximum over all the others (left at `tab`:
+// m2, m3, m4, r2 | r3 << 16): pass 2 then needs the row again only where a
+// second or further fragment of a thread also beats the threshold.
 template <typename T>
 __device__ __noinline__ Pass1 lean_pass1(uint32_t slot_a, uint32_t slot_b, const char *src0, uint32_t nfull,
                                          const uint4 *h4, uint32_t fused4, uint32_t *seen, uint32_t lo,
@@ -1236,8 +1236,8 @@ __device__ __noinline__ Pass1 lean_pass1(uint32_t slot_a, uint32_t slot_b, const
     out.best = neg_inf();
     out.best_r = NONE;
     out.saw_nan = 0u;
-    float m2 = neg_inf(), m3 = neg_inf();
-    uint32_t r2 = NONE;
+    float m2 = neg_inf(), m3 = neg_inf(), m4 = neg_inf();
+    uint32_t r2 = NONE, r3 = NONE;
     Frag keep;
     keep.v[0] = make_uint4(0, 0, 0, 0);
     keep.v[1] = make_uint4(0, 0, 0, 0);
@@ -1274,27 +1274,38 @@ __device__ __noinline__ Pass1 lean_pass1(uint32_t slot_a, uint32_t slot_b, const
                 }
                 const float m = frag_max<T>(cur);
                 out.saw_nan |= m != m ? 1u : 0u;
+                // The three best fragments by maximum (rounds r1, r2, r3) and the
+                // largest maximum among all the others (m4).
                 if (out.best_r == NONE || m > out.best) {
-                    m3 = fmaxf(m3, m2);
+                    m4 = fmaxf(m4, m3);
+                    m3 = m2;
+                    r3 = r2;
                     m2 = out.best;
                     r2 = out.best_r;
                     out.best = m;
                     out.best_r = rr;
                     keep = cur;
                 } else if (r2 == NONE || m > m2) {
-                    m3 = fmaxf(m3, m2);
+                    m4 = fmaxf(m4, m3);
+                    m3 = m2;
+                    r3 = r2;
                     m2 = m;
                     r2 = rr;
+                } else if (r3 == NONE || m > m3) {
+                    m4 = fmaxf(m4, m3);
+                    m3 = m;
+                    r3 = rr;
                 } else {
-                    m3 = fmaxf(m3, m);
+                    m4 = fmaxf(m4, m);
                 }
             }
         }
     }
     cp_async_wait<0>();
     lean_write_slot(slot_a + ROUND_BYTES, keep);
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tab), "r"(__float_as_uint(m2)), "r"(r2),
-                 "r"(__float_as_uint(m3)), "r"(0u)
+    // Rounds fit 16 bits (a slice has at most 2^24 / 4096 of them); 0xFFFF = none.
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tab), "r"(__float_as_uint(m2)),
+                 "r"(__float_as_uint(m3)), "r"(__float_as_uint(m4)), "r"((r2 & 0xFFFFu) | (r3 << 16))
                  : "memory");
     return out;
 }
@@ -1319,9 +1330,9 @@ __device__ __noinline__ void lean_take(SmemFixed *sm, const Frag &cur, uint32_t 
 
 // Pass 2 over the full rounds of a 16-byte aligned row, from what pass 1
 // left: the thread's best fragment (round r1, in its stage-1 slot) needs no
-// memory at all; its second best (m2, round r2) is read again only if it
-// beats the threshold too; only if a third fragment could (m3) does the
-// thread walk its rounds once more.
+// memory at all; its second and third best (rounds r2, r3) are read again,
+// both at once, only if they beat the threshold too; only if a fourth
+// fragment could (m4) does the thread walk its rounds once more.
 template <typename T>
 __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_t nfull, uint32_t base0,
                                         float c_fix, uint32_t slot_keep, uint32_t tab, float m1, uint32_t r1) {
@@ -1329,16 +1340,23 @@ __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_
     if (r1 == NONE) {
         return;
     }
-    uint32_t m2b, r2, m3b, unused;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(m2b), "=r"(r2), "=r"(m3b), "=r"(unused) : "r"(tab));
-    const float m2 = __uint_as_float(m2b), m3 = __uint_as_float(m3b);
+    uint32_t m2b, m3b, m4b, rr23;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(m2b), "=r"(m3b), "=r"(m4b), "=r"(rr23) : "r"(tab));
+    const float m2 = __uint_as_float(m2b), m3 = __uint_as_float(m3b), m4 = __uint_as_float(m4b);
+    const uint32_t r2 = (rr23 & 0xFFFFu) == 0xFFFFu ? NONE : (rr23 & 0xFFFFu);
+    const uint32_t r3 = (rr23 >> 16) == 0xFFFFu ? NONE : (rr23 >> 16);
     const uint4 *src = reinterpret_cast<const uint4 *>(src0);
     constexpr uint32_t STRIDE = ROUND_BYTES / 16u;
     const bool second = r2 != NONE && !(m2 <= c_fix);
-    Frag f2;
+    const bool third = r3 != NONE && !(m3 <= c_fix);
+    Frag f2, f3;
     if (second) {
         f2.v[0] = __ldcg(src + r2 * STRIDE);
         f2.v[1] = __ldcg(src + r2 * STRIDE + 1);
+    }
+    if (third) {
+        f3.v[0] = __ldcg(src + r3 * STRIDE);
+        f3.v[1] = __ldcg(src + r3 * STRIDE + 1);
     }
     if (!(m1 <= c_fix)) {
         Frag keep;
@@ -1348,9 +1366,12 @@ __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_
     if (second) {
         lean_take<T>(sm, f2, base0 + r2 * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
     }
-    if (!(m3 <= c_fix)) {
-        // Rare (a third fragment of this thread may matter): all rounds again,
-        // four loads in flight at a time.
+    if (third) {
+        lean_take<T>(sm, f3, base0 + r3 * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
+    }
+    if (!(m4 <= c_fix)) {
+        // Very rare (a fourth fragment of this thread may matter): all rounds
+        // again, four loads in flight at a time.
         for (uint32_t r0 = 0; r0 < nfull; r0 += 4u) {
             Frag f[4];
 #pragma unroll
@@ -1363,7 +1384,7 @@ __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_
 #pragma unroll
             for (uint32_t j = 0; j < 4u; ++j) {
                 const uint32_t rr = r0 + j;
-                if (rr < nfull && rr != r1 && rr != r2 && !(frag_max<T>(f[j]) <= c_fix)) {
+                if (rr < nfull && rr != r1 && rr != r2 && rr != r3 && !(frag_max<T>(f[j]) <= c_fix)) {
                     lean_take<T>(sm, f[j], base0 + rr * Geo<T>::ROUND, 0xFFFFFFFFu, c_fix);
                 }
             }
