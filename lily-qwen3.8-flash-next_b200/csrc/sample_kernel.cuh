@@ -1622,6 +1622,19 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             p1_issue((uint32_t)st);
         }
     }
+    // The slice's last, partial round (plain loads: it may end anywhere) is
+    // asked for now and used at the end of pass 1 and again in pass 2: its
+    // latency hides behind everything in between.
+    Frag part;
+    part.v[0] = make_uint4(0, 0, 0, 0);
+    part.v[1] = make_uint4(0, 0, 0, 0);
+    const uint32_t part_base = c.lo + nfull * ROUND + tid * GROUP;
+    const uint32_t part_valid = (lean_cand && nrounds > nfull && part_base < c.hi)
+                                    ? min(GROUP, c.hi - part_base)
+                                    : 0u;
+    if (part_valid != 0u) {
+        load_frag_scalar<T>(part, row_ptr, part_base, c.hi);
+    }
 
     // ---- A. bitmaps
     const uint32_t slice_words = (c.hi - c.lo + 31u) >> 5;
@@ -1800,20 +1813,15 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                     }
                 }
             }
-            if (nrounds > nfull) {
-                const uint32_t r = nfull;
-                Frag cur;
-                const uint32_t base = c.lo + r * ROUND + tid * GROUP;
-                load_frag_scalar<T>(cur, row_ptr, base, c.hi);
-                const uint32_t nvalid = base < c.hi ? min(GROUP, c.hi - base) : 0u;
+            if (part_valid != 0u) {
 #pragma unroll
                 for (int e = 0; e < (int)GROUP; ++e) {
-                    if ((uint32_t)e < nvalid) {
-                        const float l = frag_get<T>(cur, e);
+                    if ((uint32_t)e < part_valid) {
+                        const float l = frag_get<T>(part, e);
                         saw_nan = saw_nan || l != l;
                         if (best_r == NONE || l > best) {
                             best = l;
-                            best_r = r;
+                            best_r = nfull;
                         }
                     }
                 }
@@ -1834,7 +1842,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 // Which logit of that round it was: pass 1 kept the fragment.
                 Frag again;
                 const uint32_t base = c.lo + best_r * ROUND + tid * GROUP;
-                if (VEC && best_r < nfull) {
+                if (best_r == nfull) {
+                    again = part;
+                } else if (VEC) {
                     lean_read_slot(p1_slot[1], again);
                 } else {
                     load_frag_scalar<T>(again, row_ptr, base, c.hi);
@@ -2017,11 +2027,8 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                     base += ROUND;
                 }
             }
-            if (nrounds > nfull && base < c.hi) {
-                Frag cur;
-                load_frag_scalar<T>(cur, row_ptr, base, c.hi);
-                const uint32_t nvalid = min(GROUP, c.hi - base);
-                lean_take<T>(sm, cur, base, nvalid >= 32u ? 0xFFFFFFFFu : (1u << nvalid) - 1u, c_fix);
+            if (part_valid != 0u) {
+                lean_take<T>(sm, part, part_base, (1u << part_valid) - 1u, c_fix);
             }
             cp_async_wait<0>();
         }
