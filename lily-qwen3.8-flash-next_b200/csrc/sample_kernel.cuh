@@ -1333,12 +1333,15 @@ __device__ __noinline__ void lean_take(SmemFixed *sm, const Frag &cur, uint32_t 
 // memory at all; its second and third best (rounds r2, r3) are read again,
 // both at once, only if they beat the threshold too; only if a fourth
 // fragment could (m4) does the thread walk its rounds once more.
+// Returns which of the steps the thread took (bit 0: second fragment read,
+// bit 1: third, bit 2: the walk over all rounds), for the phase trace.
 template <typename T>
-__device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_t nfull, uint32_t base0,
-                                        float c_fix, uint32_t slot_keep, uint32_t tab, float m1, uint32_t r1) {
+__device__ __noinline__ uint32_t lean_pass2(SmemFixed *sm, const char *src0, uint32_t nfull, uint32_t base0,
+                                            float c_fix, uint32_t slot_keep, uint32_t tab, float m1,
+                                            uint32_t r1) {
     constexpr uint32_t NONE = 0xFFFFFFFFu;
     if (r1 == NONE) {
-        return;
+        return 0u;
     }
     uint32_t m2b, m3b, m4b, rr23;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(m2b), "=r"(m3b), "=r"(m4b), "=r"(rr23) : "r"(tab));
@@ -1390,6 +1393,7 @@ __device__ __noinline__ void lean_pass2(SmemFixed *sm, const char *src0, uint32_
             }
         }
     }
+    return (second ? 1u : 0u) | (third ? 2u : 0u) | (!(m4 <= c_fix) ? 4u : 0u);
 }
 
 // Phase stamps for the optional per-block timing trace.
@@ -1882,10 +1886,12 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             __syncthreads();
             LILY_STAMP(PH_THRESHOLD_SET);
         }
-        // The ring starts over at round 0 for whichever stream follows.
+        if (!lean) {
+            // The general path follows: its ring starts over at round 0.
 #pragma unroll
-        for (int st = 0; st < STAGES - 1; ++st) {
-            issue((uint32_t)st);
+            for (int st = 0; st < STAGES - 1; ++st) {
+                issue((uint32_t)st);
+            }
         }
     }
 
@@ -2015,8 +2021,20 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         {
             uint32_t base = c.lo + tid * GROUP;
             if (VEC) {
-                lean_pass2<T>(sm, my_src, nfull, base, c_fix, p1_slot[1], lean_tab, full_best, full_best_r);
+                const uint32_t took =
+                    lean_pass2<T>(sm, my_src, nfull, base, c_fix, p1_slot[1], lean_tab, full_best, full_best_r);
                 base += nfull * ROUND;
+                if (a.phase_clocks != nullptr) {
+                    // The trace's two spare words: threads that read a second or third
+                    // fragment again, threads that walked all their rounds.
+                    const int again = __syncthreads_count((took & 3u) != 0u);
+                    const int walked = __syncthreads_count((took & 4u) != 0u);
+                    if (tid == 0) {
+                        long long *w = a.phase_clocks + ((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES;
+                        w[PH_SPARE0] = again;
+                        w[PH_SPARE1] = walked;
+                    }
+                }
             } else {
                 for (uint32_t r = 0; r < nfull; ++r) {
                     Frag cur;
