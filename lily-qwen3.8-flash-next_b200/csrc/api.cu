@@ -201,7 +201,7 @@ uint32_t choose_slices(const lily_sampler *h, uint32_t rows) {
     if (s > lily::MAX_SLICES) {
         s = lily::MAX_SLICES;
     }
-    // Slices shorter than 4096 logits buy nothing.
+    // Short slices cost more in merging than they save.
     const uint32_t by_len = (h->vocab + lily::MIN_SLICE - 1u) / lily::MIN_SLICE;
     if (s > by_len) {
         s = by_len;

@@ -48,7 +48,7 @@ constexpr int STAGES = 2;               // rounds in flight in the cp.async ring
 constexpr uint32_t RING_BYTES = STAGES * NT * FRAG_BYTES;
 constexpr uint32_t SP_SMEM = 256;       // bias + ban entries staged in shared memory
 constexpr uint32_t MAX_SLICES = LILY_MAX_SLICES;
-constexpr uint32_t MIN_SLICE = 4096;    // slices shorter than this buy nothing
+constexpr uint32_t MIN_SLICE = 32768;   // shorter slices cost more in merging than they save (measured)
 constexpr uint32_t H0_SHIFT = 19;       // first-round histogram: raw key >> 19, 8192 bins
 constexpr uint32_t H0_BINS = 1u << (32 - H0_SHIFT);
 constexpr uint32_t TH_BINS = 1024;      // tightening histogram: raw key >> 16 above a base
@@ -1598,7 +1598,12 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // the slice (see C0' below). Its first pass is the one that reads DRAM:
     // it runs four rounds deep, the two extra stages in the still unused
     // candidate buffer (key[] and id[] are one round each).
-    const bool lean_cand = c.k <= 128u && (!c.use_pen || c.monotone) && nrounds > 0u;
+    // Up to k = 128 the threshold comes from one maximum per thread; beyond
+    // that ("wide", up to the cap of 1024) from each thread's three best
+    // fragments, which needs aligned rows and three full rounds per thread.
+    const bool lean_wide = c.k > 128u;
+    const bool lean_cand = (!c.use_pen || c.monotone) && nrounds > 0u &&
+                           (!lean_wide || (VEC && nfull >= 3u && c.k <= 3u * NT));
     constexpr int P1_STAGES = 4;
     static_assert(STAGES == 2 && CAP * 4u == NT * FRAG_BYTES, "pass 1 stages 2 and 3 are key[] and id[]");
     const uint32_t p1_slot[P1_STAGES] = {
@@ -1837,7 +1842,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 #endif
         LILY_STAMP(PH_PASS1);
         // A NaN anywhere, or fewer than k threads with a logit: the general path.
-        const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE);
+        const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE) * (lean_wide ? 3u : 1u);
         lean = !__syncthreads_or(saw_nan) && have >= c.k;
         LILY_STAMP(PH_PASS1_MET);
         if (lean) {
@@ -1867,15 +1872,81 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 id = base + at;
                 key = adjusted_key(sm, id, l, c.has_special && is_special(sm, c, id));
             }
+            // Wide: the largest logits of the thread's second and third best
+            // fragments as well (other fragments, so other ids: still a lower
+            // bound). Their rounds are read once more to find the ids.
+            uint32_t key2 = 0u, key3 = 0u;
+            if (lean_wide) {
+                uint32_t m2b, m3b, m4b, rr23;
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(m2b), "=r"(m3b), "=r"(m4b), "=r"(rr23)
+                             : "r"(lean_tab));
+                const uint32_t rr[2] = {rr23 & 0xFFFFu, rr23 >> 16};
+                const float mm[2] = {__uint_as_float(m2b), __uint_as_float(m3b)};
+                Frag f[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(my_src + (size_t)rr[j] * ROUND_BYTES);
+                    f[j].v[0] = __ldcg(src);
+                    f[j].v[1] = __ldcg(src + 1);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t at = 0;
+                    float l = mm[j];
+#pragma unroll
+                    for (int e = (int)GROUP - 1; e >= 0; --e) {
+                        const float v = frag_get<T>(f[j], e);
+                        if (v == mm[j]) {
+                            at = (uint32_t)e;
+                            l = v;
+                        }
+                    }
+                    const uint32_t id2 = c.lo + rr[j] * ROUND + tid * GROUP + at;
+                    const uint32_t kk = adjusted_key(sm, id2, l, c.has_special && is_special(sm, c, id2));
+                    if (j == 0) {
+                        key2 = kk;
+                    } else {
+                        key3 = kk;
+                    }
+                }
+            }
             LILY_STAMP(PH_MAXIMA);
-            // The largest v (low 16 bits clear) that at least k of the 512 keys
+            // The largest v (low 16 bits clear) that at least k of the keys
             // reach, bit by bit from the top: a block-wide count per bit.
             uint32_t kth = 0u;
+            if (!lean_wide) {
 #pragma unroll 1
-            for (int bit = 31; bit >= 16; --bit) {
-                const uint32_t cand = kth | (1u << bit);
-                if ((uint32_t)__syncthreads_count(key >= cand) >= c.k) {
-                    kth = cand;
+                for (int bit = 31; bit >= 16; --bit) {
+                    const uint32_t cand = kth | (1u << bit);
+                    if ((uint32_t)__syncthreads_count(key >= cand) >= c.k) {
+                        kth = cand;
+                    }
+                }
+            } else {
+                // Three keys per thread: warp sums into three rotating counters,
+                // one barrier per bit.
+                uint32_t *ctr = &sm->sel_digit;  // sel_digit, sel_before, sel_count
+                if (tid < 3u) {
+                    ctr[tid] = 0u;
+                }
+                __syncthreads();
+#pragma unroll 1
+                for (int bit = 31, it = 0; bit >= 16; --bit, ++it) {
+                    const uint32_t cand = kth | (1u << bit);
+                    const uint32_t mine = (key >= cand ? 1u : 0u) + (key2 >= cand ? 1u : 0u) +
+                                          (key3 >= cand ? 1u : 0u);
+                    const uint32_t warp_sum = __reduce_add_sync(0xFFFFFFFFu, mine);
+                    if ((tid & 31u) == 0u && warp_sum != 0u) {
+                        atomicAdd(&ctr[it % 3], warp_sum);
+                    }
+                    __syncthreads();
+                    if (*reinterpret_cast<volatile uint32_t *>(&ctr[it % 3]) >= c.k) {
+                        kth = cand;
+                    }
+                    if (tid == 0) {
+                        ctr[(it + 2) % 3] = 0u;  // next used two barriers from now
+                    }
                 }
             }
             LILY_STAMP(PH_SEARCH);
