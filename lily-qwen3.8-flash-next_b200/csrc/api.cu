@@ -151,10 +151,11 @@ int32_t next_stage(lily_sampler *h, int *slot) {
 }
 
 size_t smem_bytes(uint32_t vocab, uint32_t n_slices) {
-    // The largest slice a row can get is the one of a row cut into
-    // min(n_slices, CAP / KCAP) pieces.
-    const uint32_t want = n_slices < lily::CAP / lily::KCAP ? n_slices : lily::CAP / lily::KCAP;
-    const uint32_t slice_len = (((vocab + want - 1u) / want) + 255u) & ~255u;
+    // The largest slice a row can get is the whole row: a row that keeps many
+    // candidates and takes the two-pass route is not cut, whatever n_slices is
+    // (the kernel decides per row; the seen bitmap must fit either way).
+    (void)n_slices;
+    const uint32_t slice_len = (vocab + 255u) & ~255u;
     const size_t words = (slice_len + 31u) / 32u + 8u;
     return sizeof(lily::SmemFixed) + lily::RING_BYTES + words * sizeof(uint32_t);
 }

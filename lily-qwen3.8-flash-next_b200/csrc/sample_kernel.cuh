@@ -1527,7 +1527,11 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     c.need_counts = c.use_pen && P.frequency_penalty != 0.0f;
     // A row is cut into at most CAP / k slices so that the merge of the
     // slices' best k fits the candidate buffer; blocks past that leave.
-    const uint32_t want = min(a.n_slices, CAP / c.k);
+    // (A row that keeps many candidates is not cut at all when it can take
+    // the two-pass route: merging slices of a thousand candidates each costs
+    // more than one block streaming the whole row.)
+    const bool one_block = c.k > 128u && (!c.use_pen || c.monotone) && a.cand_out == nullptr;
+    const uint32_t want = one_block ? 1u : min(a.n_slices, CAP / c.k);
     const uint32_t slice_len = (((a.vocab + want - 1u) / want) + 255u) & ~255u;
     const uint32_t n_slices = (a.vocab + slice_len - 1u) / slice_len;
     if (slice >= n_slices) {
