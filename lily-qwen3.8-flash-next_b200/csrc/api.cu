@@ -11,6 +11,7 @@
 #include <string>
 #include <vector>
 
+#include "../../include/lily_batch.h"
 #include "../../include/lily_sampler.h"
 #include "sample_kernel.cuh"
 #include "lmhead_kernel.cuh"
@@ -521,6 +522,35 @@ int32_t lily_sampler_copy_counts(lily_sampler_t *dst, uint32_t dst_slot, const l
                             src->seen_table + (size_t)src_slot * src->seen_words,
                             (size_t)dst->seen_words * 4, cudaMemcpyDefault, stream));
     return LILY_OK;
+}
+
+// include/lily_batch.h: CountsSlot::Engine is the engine handle's slot 0,
+// CountsSlot::Batch(i) slot i of the batch handle.
+int32_t lily_move_counts(lily_sampler_t *engine, lily_sampler_t *batch, void *stream_,
+                         uint32_t from, uint32_t to) {
+    if (from == to) {
+        return LILY_OK;
+    }
+    int32_t st = check_handle(engine);
+    if (st != LILY_OK) {
+        return st;
+    }
+    st = check_handle(batch);
+    if (st != LILY_OK) {
+        return st;
+    }
+    for (uint32_t slot : {from, to}) {
+        if (slot != LILY_COUNTS_ENGINE && slot >= batch->max_rows) {
+            std::string msg = "batch slot " + std::to_string(slot) + " of " +
+                              std::to_string(batch->max_rows);
+            fail(engine, LILY_ERR_ARG, msg.c_str());
+            return fail(batch, LILY_ERR_ARG, msg.c_str());
+        }
+    }
+    lily_sampler_t *src = from == LILY_COUNTS_ENGINE ? engine : batch;
+    lily_sampler_t *dst = to == LILY_COUNTS_ENGINE ? engine : batch;
+    return lily_sampler_copy_counts(dst, to == LILY_COUNTS_ENGINE ? 0u : to, src,
+                                    from == LILY_COUNTS_ENGINE ? 0u : from, stream_);
 }
 
 int32_t lily_sampler_read_counts(lily_sampler_t *h, void *stream_, uint32_t slot,
