@@ -341,6 +341,15 @@ int32_t lily_spec_accept(lily_sampler_t *h, void *stream, const uint32_t *draws,
  * hidden bf16 [tokens, hidden_ld], all sums in binary32 (group sums on the
  * tensor cores, exact products, then scaled and added in group order).
  * tokens <= 64, hidden a multiple of 512, every pointer 16-byte aligned.
+ *
+ * With `biases_bf16` set the head is in MLX affine 8-bit storage and
+ *
+ *   logits[t, n] = sum_g ( scale[n, g] * sum_c (q[n, c] - 128) * hidden[t, c]
+ *                          + (128 * scale[n, g] + bias[n, g]) * sum_c hidden[t, c] )
+ *
+ * which is sum_c (scale * q + bias) * hidden up to binary32 rounding (the
+ * reference's own test allows 2e-2 + 2e-2 |x| against a dequantise-then-
+ * multiply sum, tests/unit/kernels/quant.rs:418-434).
  */
 typedef struct lily_lmhead {
     uint32_t struct_size;        /* sizeof(lily_lmhead_t) */
@@ -349,6 +358,14 @@ typedef struct lily_lmhead {
     uint32_t group;              /* columns per scale: 64 */
     const int8_t *weights;       /* device [rows, hidden] */
     const void *scales_bf16;     /* device [rows, hidden / group] */
+    const void *biases_bf16;     /* NULL: the symmetric format above. Else the
+                                    reference's own 8-bit storage, MLX affine
+                                    (src/weights.rs:21-36): `weights` holds
+                                    UNSIGNED bytes q (QuantWeights::codes, U32
+                                    [rows, hidden / 4], low byte first, is the
+                                    same memory), w = scale * q + bias, and
+                                    this is device bf16 [rows, hidden / group];
+                                    hidden <= 16384 */
 } lily_lmhead_t;
 
 /* out_logits: device F32 [tokens, out_ld >= rows]. Needs no handle state

@@ -101,7 +101,8 @@ class LmHead(C.Structure):
     """lily_lmhead_t: an 8-bit head (or one vocabulary shard of it) on the device."""
 
     _fields_ = [("struct_size", C.c_uint32), ("rows", C.c_uint32), ("hidden", C.c_uint32),
-                ("group", C.c_uint32), ("weights", C.c_void_p), ("scales_bf16", C.c_void_p)]
+                ("group", C.c_uint32), ("weights", C.c_void_p), ("scales_bf16", C.c_void_p),
+                ("biases_bf16", C.c_void_p)]
 
 
 SHARD_CANDIDATES = 64
@@ -411,13 +412,14 @@ class SamplerScratch:
 
     # -- 8-bit LM head and vocabulary shards
     @staticmethod
-    def _head(weights, scales, group: int = 64) -> LmHead:
+    def _head(weights, scales, biases=None, group: int = 64) -> LmHead:
         hd = LmHead()
         hd.struct_size = C.sizeof(LmHead)
         hd.rows, hd.hidden = int(weights.shape[0]), int(weights.shape[1])
         hd.group = group
         hd.weights = _ptr(weights)
         hd.scales_bf16 = _ptr(scales)
+        hd.biases_bf16 = _ptr(biases) if biases is not None else None
         return hd
 
     def _shard_args(self, rows, params, steps, keep):
@@ -433,10 +435,12 @@ class SamplerScratch:
             a.steps = C.cast(sarr, C.c_void_p)
         return a
 
-    def lmhead_logits(self, weights, scales, hidden, out_logits, stream=None):
+    def lmhead_logits(self, weights, scales, hidden, out_logits, stream=None, biases=None):
         """lily_lmhead_logits: int8 `weights` [rows, hidden], bf16 `scales`
-        [rows, hidden/64], bf16 `hidden` [tokens, hidden] -> F32 out [tokens, >= rows]."""
-        hd = self._head(weights, scales)
+        [rows, hidden/64], bf16 `hidden` [tokens, hidden] -> F32 out [tokens, >= rows].
+        With bf16 `biases` [rows, hidden/64] the head is in MLX affine 8-bit
+        storage: `weights` are unsigned bytes, w = scale * q + bias."""
+        hd = self._head(weights, scales, biases)
         self._check(lib().lily_lmhead_logits(self._h, _stream_ptr(stream), C.byref(hd), _ptr(hidden),
                                              _ld(hidden), int(hidden.shape[0]), _ptr(out_logits),
                                              _ld(out_logits)))
@@ -452,13 +456,13 @@ class SamplerScratch:
                                                 int(want_sums), _ptr(records)))
 
     def lmhead_shard_candidates(self, weights, scales, hidden, params, records, first_id: int = 0,
-                                want_sums: bool = False, stream=None):
+                                want_sums: bool = False, stream=None, biases=None):
         """lily_lmhead_shard_candidates: head projection into the handle's own
         logits, then this shard's records (needs lmhead=True at creation)."""
         rows = int(hidden.shape[0])
         keep = []
         a = self._shard_args(rows, params, None, keep)
-        hd = self._head(weights, scales)
+        hd = self._head(weights, scales, biases)
         self._check(lib().lily_lmhead_shard_candidates(self._h, _stream_ptr(stream), C.byref(hd),
                                                        _ptr(hidden), _ld(hidden), C.byref(a),
                                                        first_id, int(want_sums), _ptr(records)))

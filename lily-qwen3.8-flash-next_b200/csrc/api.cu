@@ -41,6 +41,8 @@ StageLayout stage_layout(uint32_t max_rows) {
 
 }  // namespace
 
+constexpr uint32_t LM_HSUM_GROUPS = 256;  // affine heads: hidden <= 16384
+
 struct lily_sampler {
     int device = 0;
     uint32_t vocab = 0, max_rows = 0, max_history = 0, max_list = 0, flags = 0;
@@ -72,7 +74,8 @@ struct lily_sampler {
     std::vector<char> shard_bytes;
     float *lm_logits = nullptr;  // LILY_FLAG_LMHEAD: F32 [64, lm_ld]
     uint64_t lm_ld = 0;
-    bool lm_attr = false, merge_attr = false;
+    float *lm_hsum = nullptr;    // affine heads: sums of hidden values, F32 [LM_HSUM_GROUPS, 64]
+    bool lm_attr = false, lm_attr_affine = false, merge_attr = false;
 };
 
 namespace {
@@ -356,6 +359,9 @@ int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
     if ((e = cudaMallocHost(&h->h_status, 4)) != cudaSuccess) {
         return bail(e, "status word (host)");
     }
+    if ((e = cudaMalloc(&h->lm_hsum, (size_t)LM_HSUM_GROUPS * lily_head::TOK * sizeof(float))) != cudaSuccess) {
+        return bail(e, "LM head group sums");
+    }
     if (flags & LILY_FLAG_COUNTS_TABLE) {
         const size_t cb = (size_t)max_rows * vocab * 4, sb = (size_t)max_rows * h->seen_words * 4;
         if ((e = cudaMalloc(&h->counts_table, cb)) != cudaSuccess ||
@@ -408,6 +414,7 @@ void lily_sampler_destroy(lily_sampler_t *h) {
     cudaFree(h->seen_table);
     cudaFree(h->phase_clocks);
     cudaFree(h->lm_logits);
+    cudaFree(h->lm_hsum);
     if (h->h_status) {
         cudaFreeHost(h->h_status);
     }
@@ -791,27 +798,35 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
         return fail(h, LILY_ERR_ARG, "out_ld < rows or hidden_ld < hidden");
     }
     if (reinterpret_cast<uintptr_t>(head->weights) % 16u || reinterpret_cast<uintptr_t>(head->scales_bf16) % 16u ||
-        reinterpret_cast<uintptr_t>(hidden) % 16u || (hidden_ld * 2u) % 16u) {
-        return fail(h, LILY_ERR_ARG, "weights, scales and hidden rows must be 16-byte aligned");
+        reinterpret_cast<uintptr_t>(head->biases_bf16) % 16u || reinterpret_cast<uintptr_t>(hidden) % 16u ||
+        (hidden_ld * 2u) % 16u) {
+        return fail(h, LILY_ERR_ARG, "weights, scales, biases and hidden rows must be 16-byte aligned");
     }
-    auto kernel = lily_head::lmhead_int8_kernel<0>;
+    const bool affine = head->biases_bf16 != nullptr;
+    if (affine && head->hidden / lily_head::GROUP_K > LM_HSUM_GROUPS) {
+        return fail(h, LILY_ERR_CAPACITY, "an affine head takes a hidden size of at most 16384");
+    }
+    auto kernel = affine ? lily_head::lmhead_int8_kernel<lily_head::VARIANT_AFFINE>
+                         : lily_head::lmhead_int8_kernel<0>;
+    bool &attr_set = affine ? h->lm_attr_affine : h->lm_attr;
 #ifdef LILY_DEBUG
     if (const char *v = std::getenv("LILY_LMHEAD_VARIANT")) {
-        const int variant = std::atoi(v);
-        kernel = variant == 1    ? lily_head::lmhead_int8_kernel<1>
+        const int variant = affine ? -1 : std::atoi(v);
+        kernel = variant < 0     ? kernel
+                 : variant == 1    ? lily_head::lmhead_int8_kernel<1>
                  : variant == 2  ? lily_head::lmhead_int8_kernel<2>
                  : variant == 3  ? lily_head::lmhead_int8_kernel<3>
                  : variant == 11 ? lily_head::lmhead_int8_kernel<11>
                  : variant == 19 ? lily_head::lmhead_int8_kernel<19>
                  : variant == 27 ? lily_head::lmhead_int8_kernel<27>
                                  : lily_head::lmhead_int8_kernel<0>;
-        h->lm_attr = false;
+        attr_set = false;
     }
 #endif
-    if (!h->lm_attr) {
+    if (!attr_set) {
         CU(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)lily_head::Smem::BYTES));
-        h->lm_attr = true;
+        attr_set = true;
     }
     EncodeTiledFn encode = tensor_map_encoder();
     if (encode == nullptr) {
@@ -844,6 +859,13 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
         }
     }
     a.scales = static_cast<const __nv_bfloat16 *>(head->scales_bf16);
+    a.biases = static_cast<const __nv_bfloat16 *>(head->biases_bf16);
+    a.hsum = h->lm_hsum;
+    if (affine) {
+        lily_head::hidden_group_sums_kernel<<<head->hidden / lily_head::GROUP_K, lily_head::TOK, 0, stream>>>(
+            static_cast<const __nv_bfloat16 *>(hidden), hidden_ld, tokens, h->lm_hsum);
+        CU(h, cudaGetLastError());
+    }
     a.tokens = tokens;
     a.k = head->hidden;
     a.rows = head->rows;

@@ -6,6 +6,13 @@
 // called from src/qwen4exp/model.rs:2999-3006); the reference's format is
 // affine 4/8-bit, this one is the symmetric int8 layout of the vocab-sharded
 // configuration, so parity here is by tolerance against a binary32 CPU sum.
+// The same kernel (VARIANT bit 5) takes the reference's own 8-bit storage, MLX
+// affine (src/weights.rs:21-36; gemv_q8, src/kernels/metal/quant.metal:
+// 124-160): w = scale * q + bias with q an unsigned byte. The converters widen
+// q - 128 (again exact in bf16, and for the same three instructions), and the
+// epilogue adds (128 * scale + bias) * (sum of the group's 64 hidden values),
+// the group sums of the hidden states coming from a small kernel that runs
+// first.
 //
 // sm_100a only. The weights are the only large operand (1 byte per
 // multiply-add), so the kernel is a stream of them through the tensor cores,
@@ -110,6 +117,8 @@ struct Args {
     CUtensorMap w_map;
     CUtensorMap h_map;
     const __nv_bfloat16 *scales;  // [rows, hidden / 64]
+    const __nv_bfloat16 *biases;  // affine storage only: [rows, hidden / 64]
+    const float *hsum;            // affine storage only: [hidden / 64][64 tokens] sums of hidden values
     uint32_t tokens;            // <= 64
     uint32_t k;                 // hidden size, a multiple of 512
     uint32_t rows;              // vocabulary rows of this shard
@@ -255,11 +264,15 @@ __device__ __forceinline__ void tc_fence_after() {
 // (0x4300 | b) & 0xFF80 is 128 or 256: their difference is the signed byte.
 // (A variant that trades the two masks for two bf16 fused multiply-adds and a
 // minimum was measured slower.)
+template <bool UNSIGNED>
 __device__ __forceinline__ void widen4(uint32_t x, uint32_t &lo, uint32_t &hi) {
     const uint32_t t01 = __byte_perm(x, 0x43434343u, 0x5140);
     const uint32_t t23 = __byte_perm(x, 0x43434343u, 0x5342);
-    const uint32_t a01 = t01 & 0xFF7FFF7Fu, b01 = t01 & 0xFF80FF80u;
-    const uint32_t a23 = t23 & 0xFF7FFF7Fu, b23 = t23 & 0xFF80FF80u;
+    // An unsigned byte q widens to q - 128: the same subtraction with the
+    // byte's top bit flipped in the subtrahend.
+    constexpr uint32_t FLIP = UNSIGNED ? 0x00800080u : 0u;
+    const uint32_t a01 = t01 & 0xFF7FFF7Fu, b01 = (t01 ^ FLIP) & 0xFF80FF80u;
+    const uint32_t a23 = t23 & 0xFF7FFF7Fu, b23 = (t23 ^ FLIP) & 0xFF80FF80u;
     asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(a01), "r"(b01));
     asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(a23), "r"(b23));
 }
@@ -274,9 +287,12 @@ __device__ __forceinline__ void widen4(uint32_t x, uint32_t &lo, uint32_t &hi) {
 
 // VARIANT is 0 in the product; debug builds instantiate others that leave
 // out the epilogue's math (bit 0), the conversion (bit 1), the hidden-state
-// copies (bit 3) or the weight copies (bit 4) to time the rest.
+// copies (bit 3) or the weight copies (bit 4) to time the rest. Bit 5 selects
+// the affine storage (unsigned bytes, a bias per group).
+constexpr int VARIANT_AFFINE = 32;
 template <int VARIANT>
 __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_constant__ Args a) {
+    constexpr bool AFFINE = (VARIANT & VARIANT_AFFINE) != 0;
     extern __shared__ uint8_t smem_unaligned[];
     const uint32_t base = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_unaligned + (base - smem_u32(smem_unaligned));
@@ -439,10 +455,10 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                             asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                          : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
                                          : "r"(raw_row + (((gg * 4u + part * 2u + c) ^ (trow & 7u)) << 4)));
-                            widen4(x0, o[part][8 * c + 0], o[part][8 * c + 1]);
-                            widen4(x1, o[part][8 * c + 2], o[part][8 * c + 3]);
-                            widen4(x2, o[part][8 * c + 4], o[part][8 * c + 5]);
-                            widen4(x3, o[part][8 * c + 6], o[part][8 * c + 7]);
+                            widen4<AFFINE>(x0, o[part][8 * c + 0], o[part][8 * c + 1]);
+                            widen4<AFFINE>(x1, o[part][8 * c + 2], o[part][8 * c + 3]);
+                            widen4<AFFINE>(x2, o[part][8 * c + 4], o[part][8 * c + 5]);
+                            widen4<AFFINE>(x3, o[part][8 * c + 6], o[part][8 * c + 7]);
                         }
                     } else {
 #pragma unroll
@@ -498,22 +514,38 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             const uint32_t row = tile * TILE_ROWS + half * 128u + quad * 32u + lane;
             const uint32_t rowc = min(row, a.rows - 1u);
             const uint4 *srow = reinterpret_cast<const uint4 *>(a.scales + (uint64_t)rowc * groups);
+            const uint4 *brow = AFFINE ? reinterpret_cast<const uint4 *>(a.biases + (uint64_t)rowc * groups) : nullptr;
             float acc[TOK / 2];
 #pragma unroll
             for (int m = 0; m < TOK / 2; ++m) {
                 acc[m] = 0.0f;
             }
             uint4 sc_next = __ldg(srow);
+            uint4 bi_next = make_uint4(0u, 0u, 0u, 0u);
+            if (AFFINE) {
+                bi_next = __ldg(brow);
+            }
             for (uint32_t g8 = 0; g8 < groups; g8 += 8) {
                 const uint4 sc = sc_next;
+                const uint4 bi = bi_next;
                 if (g8 + 8u < groups) {
                     sc_next = __ldg(srow + (g8 >> 3) + 1u);
+                    if (AFFINE) {
+                        bi_next = __ldg(brow + (g8 >> 3) + 1u);
+                    }
                 }
                 const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
+                const uint32_t bw[4] = {bi.x, bi.y, bi.z, bi.w};
 #pragma unroll
                 for (uint32_t gi = 0; gi < 8; ++gi, ++q) {
                     const uint32_t b = q % ACC_BUFS;
                     const float s = __uint_as_float((gi & 1u) ? (sw[gi >> 1] & 0xFFFF0000u) : (sw[gi >> 1] << 16));
+                    // Affine: the multiplier summed (q - 128) * h, so the group adds
+                    // scale * that + (128 * scale + bias) * (sum of h).
+                    const float shift = AFFINE ? fmaf(128.0f, s, __uint_as_float((gi & 1u) ? (bw[gi >> 1] & 0xFFFF0000u)
+                                                                                             : (bw[gi >> 1] << 16)))
+                                               : 0.0f;
+                    const float4 *hs = reinterpret_cast<const float4 *>(a.hsum + (uint64_t)(g8 + gi) * TOK + tok0);
                     mbar_wait(base + Smem::DONE + 8 * (q % DONE_SLOTS), (q / DONE_SLOTS) & 1u, abort_word);
                     LM_ACC(tw_af);
                     __syncwarp();
@@ -524,10 +556,26 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                         for (int c = 0; c < TOK / 32; ++c) {
                             uint32_t v[16];
                             tmem_ld16(taddr + 16u * c, v);
+                            float4 hv[4];
+                            if (AFFINE) {
+#pragma unroll
+                                for (int m = 0; m < 4; ++m) {
+                                    hv[m] = __ldg(hs + 4 * c + m);
+                                }
+                            }
                             tmem_ld_wait();
 #pragma unroll
                             for (int m = 0; m < 16; ++m) {
                                 acc[16 * c + m] = fmaf(s, __uint_as_float(v[m]), acc[16 * c + m]);
+                            }
+                            if (AFFINE) {
+#pragma unroll
+                                for (int m = 0; m < 4; ++m) {
+                                    acc[16 * c + 4 * m + 0] = fmaf(shift, hv[m].x, acc[16 * c + 4 * m + 0]);
+                                    acc[16 * c + 4 * m + 1] = fmaf(shift, hv[m].y, acc[16 * c + 4 * m + 1]);
+                                    acc[16 * c + 4 * m + 2] = fmaf(shift, hv[m].z, acc[16 * c + 4 * m + 2]);
+                                    acc[16 * c + 4 * m + 3] = fmaf(shift, hv[m].w, acc[16 * c + 4 * m + 3]);
+                                }
                             }
                         }
                     } else {
@@ -569,6 +617,29 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
     if (tid == 0 && *abort_word) {
         atomicOr(a.status_word, 1u << STATUS_TIMEOUT_BIT);
     }
+}
+
+// Affine storage: sums of each token's hidden values over every group of 64
+// columns, binary32 in index order, as [hidden / 64][64 tokens] (tokens past
+// the last: 0). One block per group, one thread per token.
+__global__ void __launch_bounds__(TOK) hidden_group_sums_kernel(const __nv_bfloat16 *hidden, uint64_t ld,
+                                                                uint32_t tokens, float *out) {
+    const uint32_t g = blockIdx.x, t = threadIdx.x;
+    float sum = 0.0f;
+    if (t < tokens) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(hidden + (uint64_t)t * ld + (uint64_t)g * GROUP_K);
+#pragma unroll
+        for (int i = 0; i < GROUP_K / 8; ++i) {
+            const uint4 v = __ldg(src + i);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                sum += __uint_as_float(w[j] << 16);
+                sum += __uint_as_float(w[j] & 0xFFFF0000u);
+            }
+        }
+    }
+    out[(uint64_t)g * TOK + t] = sum;
 }
 
 }  // namespace lily_head

@@ -261,3 +261,47 @@ def lmhead_int8(hidden_bf16, w, scales_bf16, group: int, n_begin: int, n_end: in
                          scales_bf16.ctypes.data_as(C.POINTER(C.c_uint16)), group, n_begin,
                          n_end, _ptr(out, _f32p), out.shape[1])
     return out
+
+
+def dequant_affine(codes, scales, biases, rows: int, cols: int, group: int, bits: int) -> np.ndarray:
+    """tests/support/cpu_ref.rs:402-430: MLX affine codes -> f32 [rows, cols]."""
+    codes = np.ascontiguousarray(codes, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    biases = np.ascontiguousarray(biases, dtype=np.float32)
+    assert codes.size == rows * cols * bits // 32 and scales.size == biases.size == rows * cols // group
+    out = np.zeros((rows, cols), dtype=np.float32)
+    f = lib().lo_dequant_affine
+    f.argtypes = [_u32p, _f32p, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _f32p]
+    f.restype = None
+    f(_ptr(codes, _u32p), _ptr(scales, _f32p), _ptr(biases, _f32p), rows, cols, group, bits,
+      _ptr(out, _f32p))
+    return out
+
+
+def gemm_nt(a, b) -> np.ndarray:
+    """tests/support/cpu_ref.rs:50-62: a [m, k] times b [n, k] transposed, fp32 in index order."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    m, k = a.shape
+    n = b.shape[0]
+    assert b.shape[1] == k
+    out = np.zeros((m, n), dtype=np.float32)
+    f = lib().lo_gemm_nt
+    f.argtypes = [_f32p, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, _f32p]
+    f.restype = None
+    f(_ptr(a, _f32p), _ptr(b, _f32p), m, k, n, _ptr(out, _f32p))
+    return out
+
+
+def lmhead_affine(hidden_bf16, codes, scales_bf16, biases_bf16, group: int, bits: int) -> np.ndarray:
+    """The head in MLX affine storage as the reference's tests state it
+    (tests/unit/kernels/quant.rs:418-434): bf16 hidden states times the
+    dequantised weights. codes uint32 [rows, hidden * bits / 32], scales and
+    biases bf16 bits [rows, hidden / group]. Returns f32 [tokens, rows]."""
+    hidden_bf16 = np.ascontiguousarray(hidden_bf16, dtype=np.uint16)
+    codes = np.ascontiguousarray(codes, dtype=np.uint32)
+    rows = codes.shape[0]
+    hidden = hidden_bf16.shape[1]
+    widen = lambda bits16: (np.ascontiguousarray(bits16, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+    w = dequant_affine(codes, widen(scales_bf16), widen(biases_bf16), rows, hidden, group, bits)
+    return gemm_nt(widen(hidden_bf16), w)

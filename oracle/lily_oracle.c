@@ -584,3 +584,39 @@ void lo_lmhead_int8(const uint16_t *hidden_bf16, uint32_t tokens, uint32_t hidde
         }
     }
 }
+
+/* ---------------------------------------------- MLX affine 4/8-bit head -- */
+
+/* tests/support/cpu_ref.rs:402-430 dequant_affine: element c of row r is bits
+ * bits*(c % per_word) of codes[r][c / per_word], low element first;
+ * w = scale * q + bias, two roundings. */
+void lo_dequant_affine(const uint32_t *codes, const float *scales, const float *biases,
+                       uint32_t rows, uint32_t cols, uint32_t group, uint32_t bits, float *out) {
+    const uint32_t per_word = 32u / bits;
+    const uint32_t mask = (1u << bits) - 1u;
+    const uint32_t words = cols / per_word, groups = cols / group;
+    for (uint32_t r = 0; r < rows; ++r) {
+        for (uint32_t c = 0; c < cols; ++c) {
+            const uint32_t word = codes[(uint64_t)r * words + c / per_word];
+            const uint32_t q = (word >> (bits * (c % per_word))) & mask;
+            const uint64_t g = (uint64_t)r * groups + c / group;
+            const float scaled = scales[g] * (float)q;
+            out[(uint64_t)r * cols + c] = scaled + biases[g];
+        }
+    }
+}
+
+/* tests/support/cpu_ref.rs:50-62 gemm_nt: c[m, n] = sum_i a[m, i] * b[n, i],
+ * one fp32 accumulator in index order. */
+void lo_gemm_nt(const float *a, const float *b, uint32_t m, uint32_t k, uint32_t n, float *c) {
+    for (uint32_t row = 0; row < m; ++row) {
+        for (uint32_t col = 0; col < n; ++col) {
+            float sum = 0.0f;
+            for (uint32_t i = 0; i < k; ++i) {
+                const float prod = a[(uint64_t)row * k + i] * b[(uint64_t)col * k + i];
+                sum = sum + prod;
+            }
+            c[(uint64_t)row * n + col] = sum;
+        }
+    }
+}

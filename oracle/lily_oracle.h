@@ -149,6 +149,16 @@ void lo_lmhead_int8(const uint16_t *hidden_bf16, uint32_t tokens, uint32_t hidde
                     const int8_t *w, const uint16_t *scales_bf16, uint32_t group,
                     uint32_t n_begin, uint32_t n_end, float *logits, uint64_t ld);
 
+/*
+ * The head in the reference's own storage (MLX affine, src/weights.rs:21-36):
+ * the dequantisation the reference's tests pin bit for bit against MLX
+ * (tests/unit/kernels/quant.rs:39-63) and the fp32 product they compare
+ * gemv_quant with (tests/unit/kernels/quant.rs:418-434).
+ */
+void lo_dequant_affine(const uint32_t *codes, const float *scales, const float *biases,
+                       uint32_t rows, uint32_t cols, uint32_t group, uint32_t bits, float *out);
+void lo_gemm_nt(const float *a, const float *b, uint32_t m, uint32_t k, uint32_t n, float *c);
+
 #ifdef __cplusplus
 }
 #endif

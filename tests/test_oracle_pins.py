@@ -226,3 +226,28 @@ def test_lmhead_matches_float64():
     wd = cfg.weight.astype(np.float64).reshape(64, 4, 64) * s[:, :, None]
     want = h @ wd.reshape(64, 256).T
     assert np.allclose(got, want, rtol=1e-5, atol=1e-4)
+
+
+def test_dequant_affine_matches_the_reference_golden_bit_for_bit():
+    # tests/unit/kernels/quant.rs:39-63 on tests/goldens/quant_fixture.json
+    # (4- and 8-bit cases; re-emitted by tests/golden/make_quant_fixture.py).
+    import json
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "quant_fixture.json")
+    with open(path) as f:
+        cases = json.load(f)["cases"]
+    assert {c["bits"] for c in cases} == {4, 8}
+    for c in cases:
+        f32 = lambda bits: np.array(bits, dtype=np.uint32).view(np.float32)
+        got = oracle.dequant_affine(c["codes"], f32(c["scales_f32_bits"]), f32(c["biases_f32_bits"]),
+                                    c["rows"], c["cols"], c["group_size"], c["bits"])
+        want = np.array(c["expected_f32_bits"], dtype=np.uint32)
+        assert np.array_equal(got.reshape(-1).view(np.uint32), want), c["name"]
+
+
+def test_gemm_nt_sums_in_index_order():
+    # tests/support/cpu_ref.rs:50-62: one fp32 accumulator, index order.
+    a = np.array([[1e8, 1.0, -1e8, 1.0]], dtype=np.float32)
+    b = np.ones((1, 4), dtype=np.float32)
+    assert oracle.gemm_nt(a, b)[0, 0] == np.float32(1.0)  # (1e8 + 1) - 1e8 = 0, + 1
