@@ -365,7 +365,7 @@ typedef struct lily_lmhead {
                                     [rows, hidden / 4], low byte first, is the
                                     same memory), w = scale * q + bias, and
                                     this is device bf16 [rows, hidden / group];
-                                    hidden <= 16384 */
+                                    hidden <= 8192 */
 } lily_lmhead_t;
 
 /* out_logits: device F32 [tokens, out_ld >= rows]. Needs no handle state

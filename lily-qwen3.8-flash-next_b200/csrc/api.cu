@@ -41,8 +41,6 @@ StageLayout stage_layout(uint32_t max_rows) {
 
 }  // namespace
 
-constexpr uint32_t LM_HSUM_GROUPS = 256;  // affine heads: hidden <= 16384
-
 struct lily_sampler {
     int device = 0;
     uint32_t vocab = 0, max_rows = 0, max_history = 0, max_list = 0, flags = 0;
@@ -74,8 +72,8 @@ struct lily_sampler {
     std::vector<char> shard_bytes;
     float *lm_logits = nullptr;  // LILY_FLAG_LMHEAD: F32 [64, lm_ld]
     uint64_t lm_ld = 0;
-    float *lm_hsum = nullptr;    // affine heads: sums of hidden values, F32 [LM_HSUM_GROUPS, 64]
-    bool lm_attr = false, lm_attr_affine = false, merge_attr = false;
+    float *lm_hsum = nullptr;    // affine heads: sums of hidden values, F32 [BIAS_MAX_GROUPS, 64]
+    bool lm_attr = false, lm_attr_affine = false, lm_attr_bias = false, merge_attr = false;
 };
 
 namespace {
@@ -359,7 +357,8 @@ int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
     if ((e = cudaMallocHost(&h->h_status, 4)) != cudaSuccess) {
         return bail(e, "status word (host)");
     }
-    if ((e = cudaMalloc(&h->lm_hsum, (size_t)LM_HSUM_GROUPS * lily_head::TOK * sizeof(float))) != cudaSuccess) {
+    if ((e = cudaMalloc(&h->lm_hsum, (size_t)lily_head::BIAS_MAX_GROUPS * lily_head::TOK * sizeof(float))) !=
+        cudaSuccess) {
         return bail(e, "LM head group sums");
     }
     if (flags & LILY_FLAG_COUNTS_TABLE) {
@@ -803,8 +802,8 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
         return fail(h, LILY_ERR_ARG, "weights, scales, biases and hidden rows must be 16-byte aligned");
     }
     const bool affine = head->biases_bf16 != nullptr;
-    if (affine && head->hidden / lily_head::GROUP_K > LM_HSUM_GROUPS) {
-        return fail(h, LILY_ERR_CAPACITY, "an affine head takes a hidden size of at most 16384");
+    if (affine && head->hidden / lily_head::GROUP_K > lily_head::BIAS_MAX_GROUPS) {
+        return fail(h, LILY_ERR_CAPACITY, "an affine head takes a hidden size of at most 8192");
     }
     auto kernel = affine ? lily_head::lmhead_int8_kernel<lily_head::VARIANT_AFFINE>
                          : lily_head::lmhead_int8_kernel<0>;
@@ -859,11 +858,21 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
         }
     }
     a.scales = static_cast<const __nv_bfloat16 *>(head->scales_bf16);
-    a.biases = static_cast<const __nv_bfloat16 *>(head->biases_bf16);
-    a.hsum = h->lm_hsum;
     if (affine) {
-        lily_head::hidden_group_sums_kernel<<<head->hidden / lily_head::GROUP_K, lily_head::TOK, 0, stream>>>(
+        const uint32_t head_groups = head->hidden / lily_head::GROUP_K;
+        lily_head::hidden_group_sums_kernel<<<head_groups, lily_head::TOK, 0, stream>>>(
             static_cast<const __nv_bfloat16 *>(hidden), hidden_ld, tokens, h->lm_hsum);
+        if (!h->lm_attr_bias) {
+            CU(h, cudaFuncSetAttribute(lily_head::affine_bias_term_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)lily_head::bias_smem_bytes(lily_head::BIAS_MAX_GROUPS)));
+            h->lm_attr_bias = true;
+        }
+        lily_head::affine_bias_term_kernel<<<(head->rows + lily_head::BIAS_ROWS - 1) / lily_head::BIAS_ROWS,
+                                             lily_head::BIAS_THREADS, lily_head::bias_smem_bytes(head_groups),
+                                             stream>>>(
+            h->lm_hsum, tokens, static_cast<const __nv_bfloat16 *>(head->scales_bf16),
+            static_cast<const __nv_bfloat16 *>(head->biases_bf16), head_groups, head->rows, out, out_ld);
         CU(h, cudaGetLastError());
     }
     a.tokens = tokens;

@@ -9,10 +9,10 @@
 // The same kernel (VARIANT bit 5) takes the reference's own 8-bit storage, MLX
 // affine (src/weights.rs:21-36; gemv_q8, src/kernels/metal/quant.metal:
 // 124-160): w = scale * q + bias with q an unsigned byte. The converters widen
-// q - 128 (again exact in bf16, and for the same three instructions), and the
-// epilogue adds (128 * scale + bias) * (sum of the group's 64 hidden values),
-// the group sums of the hidden states coming from a small kernel that runs
-// first.
+// q - 128 (again exact in bf16, and for the same three instructions); the
+// term that leaves out, (128 * scale + bias) * (sum of the group's 64 hidden
+// values) summed over the groups, is written to the output by a small kernel
+// that runs first (affine_bias_term_kernel); the epilogue's sums start from it.
 //
 // sm_100a only. The weights are the only large operand (1 byte per
 // multiply-add), so the kernel is a stream of them through the tensor cores,
@@ -117,8 +117,6 @@ struct Args {
     CUtensorMap w_map;
     CUtensorMap h_map;
     const __nv_bfloat16 *scales;  // [rows, hidden / 64]
-    const __nv_bfloat16 *biases;  // affine storage only: [rows, hidden / 64]
-    const float *hsum;            // affine storage only: [hidden / 64][64 tokens] sums of hidden values
     uint32_t tokens;            // <= 64
     uint32_t k;                 // hidden size, a multiple of 512
     uint32_t rows;              // vocabulary rows of this shard
@@ -275,6 +273,23 @@ __device__ __forceinline__ void widen4(uint32_t x, uint32_t &lo, uint32_t &hi) {
     const uint32_t a23 = t23 & 0xFF7FFF7Fu, b23 = (t23 ^ FLIP) & 0xFF80FF80u;
     asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(a01), "r"(b01));
     asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(a23), "r"(b23));
+}
+
+// Two binary32 values in one 64-bit register, and the packed fused
+// multiply-add on them (each half rounds as a scalar fma does).
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void fma2(uint64_t &acc, uint64_t a, uint64_t b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
 }
 
 #ifdef LILY_DEBUG
@@ -514,38 +529,38 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             const uint32_t row = tile * TILE_ROWS + half * 128u + quad * 32u + lane;
             const uint32_t rowc = min(row, a.rows - 1u);
             const uint4 *srow = reinterpret_cast<const uint4 *>(a.scales + (uint64_t)rowc * groups);
-            const uint4 *brow = AFFINE ? reinterpret_cast<const uint4 *>(a.biases + (uint64_t)rowc * groups) : nullptr;
-            float acc[TOK / 2];
+            uint64_t acc[TOK / 4];  // 32 tokens, two per register
 #pragma unroll
-            for (int m = 0; m < TOK / 2; ++m) {
-                acc[m] = 0.0f;
+            for (int m = 0; m < TOK / 4; ++m) {
+                acc[m] = 0ull;
+            }
+            if (AFFINE && row < a.rows) {
+                // The sums start from the term the bias kernel left in `out`; the
+                // loads complete while the first groups are multiplied.
+#pragma unroll
+                for (int m = 0; m < TOK / 4; ++m) {
+                    uint32_t lo = 0u, hi = 0u;
+                    if (tok0 + 2u * m < a.tokens) {
+                        lo = __float_as_uint(__ldcg(a.out + (uint64_t)(tok0 + 2 * m) * a.ldo + row));
+                    }
+                    if (tok0 + 2u * m + 1u < a.tokens) {
+                        hi = __float_as_uint(__ldcg(a.out + (uint64_t)(tok0 + 2 * m + 1) * a.ldo + row));
+                    }
+                    acc[m] = pack2(lo, hi);
+                }
             }
             uint4 sc_next = __ldg(srow);
-            uint4 bi_next = make_uint4(0u, 0u, 0u, 0u);
-            if (AFFINE) {
-                bi_next = __ldg(brow);
-            }
             for (uint32_t g8 = 0; g8 < groups; g8 += 8) {
                 const uint4 sc = sc_next;
-                const uint4 bi = bi_next;
                 if (g8 + 8u < groups) {
                     sc_next = __ldg(srow + (g8 >> 3) + 1u);
-                    if (AFFINE) {
-                        bi_next = __ldg(brow + (g8 >> 3) + 1u);
-                    }
                 }
                 const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
-                const uint32_t bw[4] = {bi.x, bi.y, bi.z, bi.w};
 #pragma unroll
                 for (uint32_t gi = 0; gi < 8; ++gi, ++q) {
                     const uint32_t b = q % ACC_BUFS;
                     const float s = __uint_as_float((gi & 1u) ? (sw[gi >> 1] & 0xFFFF0000u) : (sw[gi >> 1] << 16));
-                    // Affine: the multiplier summed (q - 128) * h, so the group adds
-                    // scale * that + (128 * scale + bias) * (sum of h).
-                    const float shift = AFFINE ? fmaf(128.0f, s, __uint_as_float((gi & 1u) ? (bw[gi >> 1] & 0xFFFF0000u)
-                                                                                             : (bw[gi >> 1] << 16)))
-                                               : 0.0f;
-                    const float4 *hs = reinterpret_cast<const float4 *>(a.hsum + (uint64_t)(g8 + gi) * TOK + tok0);
+                    const uint64_t s2 = pack2(__float_as_uint(s), __float_as_uint(s));
                     mbar_wait(base + Smem::DONE + 8 * (q % DONE_SLOTS), (q / DONE_SLOTS) & 1u, abort_word);
                     LM_ACC(tw_af);
                     __syncwarp();
@@ -556,30 +571,14 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                         for (int c = 0; c < TOK / 32; ++c) {
                             uint32_t v[16];
                             tmem_ld16(taddr + 16u * c, v);
-                            float4 hv[4];
-                            if (AFFINE) {
-#pragma unroll
-                                for (int m = 0; m < 4; ++m) {
-                                    hv[m] = __ldg(hs + 4 * c + m);
-                                }
-                            }
                             tmem_ld_wait();
 #pragma unroll
-                            for (int m = 0; m < 16; ++m) {
-                                acc[16 * c + m] = fmaf(s, __uint_as_float(v[m]), acc[16 * c + m]);
-                            }
-                            if (AFFINE) {
-#pragma unroll
-                                for (int m = 0; m < 4; ++m) {
-                                    acc[16 * c + 4 * m + 0] = fmaf(shift, hv[m].x, acc[16 * c + 4 * m + 0]);
-                                    acc[16 * c + 4 * m + 1] = fmaf(shift, hv[m].y, acc[16 * c + 4 * m + 1]);
-                                    acc[16 * c + 4 * m + 2] = fmaf(shift, hv[m].z, acc[16 * c + 4 * m + 2]);
-                                    acc[16 * c + 4 * m + 3] = fmaf(shift, hv[m].w, acc[16 * c + 4 * m + 3]);
-                                }
+                            for (int m = 0; m < 8; ++m) {
+                                fma2(acc[8 * c + m], s2, pack2(v[2 * m], v[2 * m + 1]));
                             }
                         }
                     } else {
-                        acc[gi] += s + __uint_as_float(taddr);
+                        acc[gi] += (uint64_t)__float_as_uint(s) + taddr;
                     }
                     tc_fence_before();
                     __syncwarp();
@@ -591,9 +590,14 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             }
             if (row < a.rows) {
 #pragma unroll
-                for (int m = 0; m < TOK / 2; ++m) {
-                    if (tok0 + (uint32_t)m < a.tokens) {
-                        a.out[(uint64_t)(tok0 + m) * a.ldo + row] = acc[m];
+                for (int m = 0; m < TOK / 4; ++m) {
+                    float lo, hi;
+                    unpack2(acc[m], lo, hi);
+                    if (tok0 + 2u * m < a.tokens) {
+                        a.out[(uint64_t)(tok0 + 2 * m) * a.ldo + row] = lo;
+                    }
+                    if (tok0 + 2u * m + 1u < a.tokens) {
+                        a.out[(uint64_t)(tok0 + 2 * m + 1) * a.ldo + row] = hi;
                     }
                 }
             }
@@ -619,9 +623,15 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
     }
 }
 
-// Affine storage: sums of each token's hidden values over every group of 64
-// columns, binary32 in index order, as [hidden / 64][64 tokens] (tokens past
-// the last: 0). One block per group, one thread per token.
+// Affine storage, the term the multiplier does not see: with the converters
+// widening q - 128,
+//   sum_c (scale * q + bias) * h = scale * sum_c (q - 128) * h + (128 * scale + bias) * sum_c h
+// per group, and this kernel writes out[t, n] = sum_g (128 * scale[n, g] +
+// bias[n, g]) * hsum[g, t]; the head kernel then adds its own sums to it.
+// A thread owns 4 vocabulary rows x 16 tokens, their partial results in registers;
+// the group sums of the hidden states (binary32, index order; [group][token],
+// tokens past the last: 0) come from hidden_group_sums_kernel, which runs
+// before it, one block per group and one thread per token.
 __global__ void __launch_bounds__(TOK) hidden_group_sums_kernel(const __nv_bfloat16 *hidden, uint64_t ld,
                                                                 uint32_t tokens, float *out) {
     const uint32_t g = blockIdx.x, t = threadIdx.x;
@@ -640,6 +650,114 @@ __global__ void __launch_bounds__(TOK) hidden_group_sums_kernel(const __nv_bfloa
         }
     }
     out[(uint64_t)g * TOK + t] = sum;
+}
+
+constexpr int BIAS_THREADS = 128;
+constexpr uint32_t BIAS_ROWS = BIAS_THREADS * 4 / 4;  // a warp covers 32 rows x 64 tokens
+constexpr uint32_t BIAS_MAX_GROUPS = 128;             // hidden <= 8192
+
+// Dynamic shared memory: the group sums, then the block's scales and biases,
+// each row padded by 16 bytes so that rows four apart fall into different banks.
+__host__ __device__ constexpr uint32_t bias_row_bytes(uint32_t groups) { return groups * 2u + 16u; }
+__host__ __device__ constexpr uint32_t bias_smem_bytes(uint32_t groups) {
+    return groups * TOK * 4u + 2u * BIAS_ROWS * bias_row_bytes(groups);
+}
+
+__global__ void __launch_bounds__(BIAS_THREADS) affine_bias_term_kernel(
+    const float *group_sums, uint32_t tokens, const __nv_bfloat16 *scales, const __nv_bfloat16 *biases,
+    uint32_t groups, uint32_t rows, float *out, uint64_t ldo) {
+    extern __shared__ __align__(16) uint8_t bias_smem[];
+    float *hsum = reinterpret_cast<float *>(bias_smem);  // [group][token]
+    uint8_t *sc_s = bias_smem + groups * TOK * 4u;
+    const uint32_t row_bytes = bias_row_bytes(groups);
+    uint8_t *bi_s = sc_s + BIAS_ROWS * row_bytes;
+    const uint32_t block_row0 = blockIdx.x * BIAS_ROWS;
+    for (uint32_t i = threadIdx.x; i < groups * TOK / 4u; i += BIAS_THREADS) {
+        reinterpret_cast<float4 *>(hsum)[i] = __ldg(reinterpret_cast<const float4 *>(group_sums) + i);
+    }
+    {
+        const uint32_t per_row = groups / 8u;  // 16-byte pieces of a row
+        for (uint32_t i = threadIdx.x; i < BIAS_ROWS * per_row; i += BIAS_THREADS) {
+            const uint32_t r = i / per_row, piece = i % per_row;
+            const uint32_t rowc = min(block_row0 + r, rows - 1u);
+            const uint4 sv = __ldg(reinterpret_cast<const uint4 *>(scales + (uint64_t)rowc * groups) + piece);
+            const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(biases + (uint64_t)rowc * groups) + piece);
+            *reinterpret_cast<uint4 *>(sc_s + r * row_bytes + piece * 16u) = sv;
+            *reinterpret_cast<uint4 *>(bi_s + r * row_bytes + piece * 16u) = bv;
+        }
+    }
+    __syncthreads();
+    // A thread owns 4 rows x 16 tokens: a group's 16 sums are read once from
+    // shared memory for 64 multiply-adds.
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    // Its rows are 8 apart, so that the eight threads that read scales at
+    // once read consecutive (padded) rows: no bank conflicts, and the stores
+    // of one token fill whole sectors.
+    const uint32_t lrow0 = warp * 32u + (lane >> 2);
+    const uint32_t row0 = block_row0 + lrow0;
+    const uint32_t tok0 = (lane & 3u) * 16u;
+    const uint4 *srow[4], *brow[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        srow[r] = reinterpret_cast<const uint4 *>(sc_s + (lrow0 + 8u * r) * row_bytes);
+        brow[r] = reinterpret_cast<const uint4 *>(bi_s + (lrow0 + 8u * r) * row_bytes);
+    }
+    uint64_t acc[4][8];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            acc[r][m] = 0ull;
+        }
+    }
+    for (uint32_t g8 = 0; g8 < groups; g8 += 8) {
+        uint32_t sw[4][4], bw[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const uint4 sc = srow[r][g8 >> 3];
+            const uint4 bi = brow[r][g8 >> 3];
+            sw[r][0] = sc.x, sw[r][1] = sc.y, sw[r][2] = sc.z, sw[r][3] = sc.w;
+            bw[r][0] = bi.x, bw[r][1] = bi.y, bw[r][2] = bi.z, bw[r][3] = bi.w;
+        }
+#pragma unroll
+        for (uint32_t gi = 0; gi < 8; ++gi) {
+            const ulonglong2 *hs = reinterpret_cast<const ulonglong2 *>(hsum + (g8 + gi) * TOK + tok0);
+            ulonglong2 h2[4];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                h2[m] = hs[m];
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float s = __uint_as_float((gi & 1u) ? (sw[r][gi >> 1] & 0xFFFF0000u) : (sw[r][gi >> 1] << 16));
+                const float b = __uint_as_float((gi & 1u) ? (bw[r][gi >> 1] & 0xFFFF0000u) : (bw[r][gi >> 1] << 16));
+                const float shift = fmaf(128.0f, s, b);
+                const uint64_t shift2 = pack2(__float_as_uint(shift), __float_as_uint(shift));
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    fma2(acc[r][2 * m], shift2, h2[m].x);
+                    fma2(acc[r][2 * m + 1], shift2, h2[m].y);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t row = row0 + 8u * r;
+        if (row < rows) {
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                float lo, hi;
+                unpack2(acc[r][m], lo, hi);
+                if (tok0 + 2u * m < tokens) {
+                    out[(uint64_t)(tok0 + 2 * m) * ldo + row] = lo;
+                }
+                if (tok0 + 2u * m + 1u < tokens) {
+                    out[(uint64_t)(tok0 + 2 * m + 1) * ldo + row] = hi;
+                }
+            }
+        }
+    }
 }
 
 }  // namespace lily_head
