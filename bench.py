@@ -433,6 +433,11 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
 
     step_ms = timed(step, steps)
     head_ms = timed(lambda i: scratch.lmhead_logits(ws[i % copies], sc, h, logits, stream=stream), steps)
+    # The same head read as the reference's MLX affine 8-bit storage (the
+    # bytes as unsigned codes, plus a bias per 64 columns).
+    bi = (-torch.rand((per, hidden // 64), device=dev, generator=g)).to(torch.bfloat16)
+    affine_ms = timed(lambda i: scratch.lmhead_logits(ws[i % copies], sc, h, logits, stream=stream,
+                                                      biases=bi), steps)
     assert scratch.status(stream) == lily.OK
     agree = True
     if world > 1:
@@ -450,6 +455,8 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
             "head_kernel_us": head_ms * 1e3, "head_bytes_per_gpu": head_bytes,
             "head_gbs_per_gpu": gbs, "head_frac_of_hbm": gbs / peak, "peak_kind": peak_kind,
             "head_traffic_1gpu": ncu_traffic("lmhead_int8_kernel_dram_bytes_per_launch"),
+            "affine_head_us": affine_ms * 1e3,
+            "affine_head_frac_of_hbm": (head_bytes + per * (hidden // 64) * 2) / (affine_ms * 1e-3) / 1e9 / peak,
             "allgather_bytes_per_rank": tokens * sh.RECORD_BYTES, "ranks_agree": agree,
             "l2": "one 1.07 GB shard" if copies == 1 else "two weight copies rotated"}
 

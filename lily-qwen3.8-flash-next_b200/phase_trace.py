@@ -1,0 +1,105 @@
+"""Per-block phase times of one sampler launch, from the SM clock stamps the
+kernel leaves with LILY_FLAG_PHASE_CLOCKS (the counterpart of the reference's
+LILY_KERNEL_PROFILE, src/metal.rs:140-198).
+
+    python -m lily_b200.phase_trace b4 [step ...]     # the 4-row server batch
+    python -m lily_b200.phase_trace b256              # the 256-row batch (summary)
+
+Stamps of different blocks come from different SMs' clocks: only differences
+inside one block mean anything. Times assume the 1965 MHz maximum SM clock.
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+MHZ = 1965.0
+NAMES = ["start", "bitmaps", "lists", "pass 2 / stream", "adjust + select", "merge", "sort", "end",
+         "first threshold", "pass 1", "pass 1 met", "maxima", "search", "threshold set",
+         "threads reading again", "threads walking"]
+# The order in which a block of the two-pass route reaches its stamps.
+ORDER = [0, 1, 9, 10, 11, 12, 13, 8, 2, 3, 4, 5, 6, 7]
+
+
+def _device_batch(torch, lily, x):
+    t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a).view(dt)).cuda()
+    kw = dict(uniforms=t(x.uniforms, np.float32))
+    if x.history is not None:
+        kw.update(history_ids=t(x.history, np.int32), history_len=t(x.history_len, np.int32))
+    if x.bias_ids is not None:
+        kw.update(bias_ids=t(x.bias_ids, np.int32), bias_vals=t(x.bias_vals, np.float32),
+                  bias_len=t(x.bias_len, np.int32))
+    if x.ban_ids is not None:
+        kw.update(ban_ids=t(x.ban_ids, np.int32), ban_len=t(x.ban_len, np.int32))
+    if x.forced is not None:
+        kw.update(forced_ids=t(x.forced, np.int32))
+    logits = t(x.logits, np.int16).view(torch.bfloat16) if x.bf16 else t(x.logits, np.float32)
+    return logits, [lily.SamplingParams(**p) for p in x.params], kw
+
+
+def trace(torch, lily, scratch, x, launches: int = 3):
+    """Runs `x` `launches` times; returns the stamps of the last launch,
+    int64 [rows, slices, phases] (0 where a block did not pass)."""
+    logits, params, kw = _device_batch(torch, lily, x)
+    out = torch.zeros(len(params), dtype=torch.int32, device="cuda")
+    clk = None
+    for _ in range(launches):
+        scratch.sample_batch(logits, params, out, **kw)
+        clk = scratch.read_phase_clocks()
+    return clk
+
+
+def segments(stamps):
+    """[(phase name, microseconds since the previous stamp)] of one block."""
+    out, prev = [], float(stamps[0])
+    for i in ORDER[1:]:
+        if stamps[i] != 0:
+            out.append((NAMES[i], (float(stamps[i]) - prev) / MHZ))
+            prev = float(stamps[i])
+    return out
+
+
+def main(argv) -> None:
+    import torch
+
+    import lily_b200 as lily
+    import lily_b200.workloads as w
+
+    which = argv[1] if len(argv) > 1 else "b4"
+    if which == "b4":
+        steps = [int(a) for a in argv[2:]] or [0, 3]
+        scratch = lily.SamplerScratch(w.VOCAB, max_rows=4, max_list=128, phase_clocks=True)
+        for step in steps:
+            x = w.config2_step(step)
+            clk = trace(torch, lily, scratch, x)
+            print(f"step {step}: (T, top_k, top_p) per row",
+                  [(p.get("temperature"), p.get("top_k"), p.get("top_p")) for p in x.params])
+            for r in range(clk.shape[0]):
+                for sl in range(clk.shape[1]):
+                    c = clk[r, sl]
+                    if c[0] == 0:
+                        continue
+                    total = f"{(c[7] - c[0]) / MHZ:6.1f} us" if c[7] != 0 else "   (not the row's last block)"
+                    print(f"  row {r} block {sl}: {total} | " +
+                          " ".join(f"{n} {us:.1f}" for n, us in segments(c)) +
+                          f" | read again {int(c[14])}, walked {int(c[15])}")
+    else:
+        scratch = lily.SamplerScratch(w.VOCAB, max_rows=256, phase_clocks=True)
+        clk = trace(torch, lily, scratch, w.config4_batch(), launches=4)
+        live = clk[clk[:, :, 0] != 0].astype(np.float64)
+        print("blocks", len(live))
+        prev = 0
+        for i in ORDER[1:]:
+            ok = (live[:, i] != 0) & (live[:, prev] != 0)
+            if ok.any():
+                d = (live[ok, i] - live[ok, prev]) / MHZ
+                print(f"  {NAMES[i]:18s} mean {d.mean():6.2f} us  max {d.max():6.2f}")
+                prev = i
+        tot = (live[:, 7] - live[:, 0]) / MHZ
+        print(f"  block total mean {tot.mean():.1f} us, max {tot.max():.1f}")
+    scratch.close()
+
+
+if __name__ == "__main__":
+    main(sys.argv)
