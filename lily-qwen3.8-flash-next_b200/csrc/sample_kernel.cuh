@@ -47,6 +47,7 @@ constexpr uint32_t CAP = 4096;          // candidate buffer entries
 constexpr int STAGES = 2;               // rounds in flight in the cp.async ring
 constexpr uint32_t RING_BYTES = STAGES * NT * FRAG_BYTES;
 constexpr uint32_t SP_SMEM = 256;       // bias + ban entries staged in shared memory
+constexpr uint32_t BLOOM_WORDS = 128;   // 4096-bit filter over the low 12 bits of a bias / ban id
 constexpr uint32_t MAX_SLICES = LILY_MAX_SLICES;
 constexpr uint32_t MIN_SLICE = 32768;   // shorter slices cost more in merging than they save (measured)
 constexpr uint32_t H0_SHIFT = 19;       // first-round histogram: raw key >> 19, 8192 bins
@@ -163,7 +164,7 @@ struct alignas(16) SmemFixed {
     uint32_t tid[KCAP];   // select's histogram / staging; later the prefix sums
     uint32_t thist[TH_BINS];
     uint32_t warp_sums[NT / 32];
-    uint32_t sp_ids[SP_SMEM];
+    alignas(16) uint32_t sp_ids[SP_SMEM + 4];  // padded to a multiple of four with an id no logit has
     float sp_vals[SP_SMEM];
     uint32_t n;      // buffered candidates
     uint32_t n_adj;  // the first n_adj hold adjusted keys, the rest raw logit bits
@@ -185,7 +186,7 @@ struct alignas(16) SmemFixed {
     uint32_t chosen;
     float p_d;
     float q_d;
-    uint32_t bloom[32];
+    uint32_t bloom[BLOOM_WORDS];
 #ifdef LILY_DEBUG
     uint32_t dbg_hits, dbg_hit_warps, dbg_tighten;
 #endif
@@ -237,17 +238,22 @@ __device__ __forceinline__ bool seen_bit(const RowCtx &c, uint32_t id) {
 
 // Whether `id` is on the row's bias or ban list.
 __device__ __forceinline__ bool is_special(const SmemFixed *sm, const RowCtx &c, uint32_t id) {
-    if (!((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u)) {
+    if (!((sm->bloom[(id >> 5) & (BLOOM_WORDS - 1u)] >> (id & 31u)) & 1u)) {
         return false;
     }
     const uint32_t n = c.bias_len + c.ban_len;
-    for (uint32_t j = 0; j < n; ++j) {
-        uint32_t e;
-        if (c.sp_in_smem) {
-            e = sm->sp_ids[j];
-        } else {
-            e = j < c.bias_len ? c.bias_ids[j] : c.ban_ids[j - c.bias_len];
+    if (c.sp_in_smem) {
+        // Four staged ids per load; the padding never matches.
+        const uint4 *v = reinterpret_cast<const uint4 *>(sm->sp_ids);
+        bool hit = false;
+        for (uint32_t j = 0; j < n; j += 4u) {
+            const uint4 e = v[j >> 2];
+            hit = hit || e.x == id || e.y == id || e.z == id || e.w == id;
         }
+        return hit;
+    }
+    for (uint32_t j = 0; j < n; ++j) {
+        const uint32_t e = j < c.bias_len ? c.bias_ids[j] : c.ban_ids[j - c.bias_len];
         if (e == id) {
             return true;
         }
@@ -1313,7 +1319,7 @@ __device__ __noinline__ Pass1 lean_pass1(uint32_t slot_a, uint32_t slot_b, const
 // The logits of one thread's fragment that beat the fixed threshold go to the
 // candidate buffer as raw bits (ids on the bias / ban lists went in up front).
 template <typename T>
-__device__ __noinline__ void lean_take(SmemFixed *sm, const Frag &cur, uint32_t base, uint32_t valid,
+__device__ __forceinline__ void lean_take(SmemFixed *sm, const Frag &cur, uint32_t base, uint32_t valid,
                                        float c_fix) {
     const RowCtx &c = sm->ctx;
     uint32_t pass = pass_mask<T>(cur, c_fix) & valid;
@@ -1685,7 +1691,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         sm->dbg_hits = sm->dbg_hit_warps = sm->dbg_tighten = 0;
 #endif
     }
-    if (tid < 32) {
+    if (tid < BLOOM_WORDS) {
         sm->bloom[tid] = 0;
     }
     for (uint32_t b = tid; b < TH_BINS; b += NT) {
@@ -1776,11 +1782,14 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         const uint32_t n_sp = c.bias_len + c.ban_len;
         for (uint32_t j = tid; j < n_sp; j += NT) {
             const uint32_t id = j < c.bias_len ? c.bias_ids[j] : c.ban_ids[j - c.bias_len];
-            atomicOr(&sm->bloom[(id >> 5) & 31u], 1u << (id & 31u));
+            atomicOr(&sm->bloom[(id >> 5) & (BLOOM_WORDS - 1u)], 1u << (id & 31u));
             if (c.sp_in_smem) {
                 sm->sp_ids[j] = id;
                 sm->sp_vals[j] = j < c.bias_len ? c.bias_vals[j] : 0.0f;
             }
+        }
+        if (c.sp_in_smem && tid < 4u) {
+            sm->sp_ids[n_sp + tid] = 0xFFFFFFFFu;
         }
     }
     __syncthreads();
@@ -2003,7 +2012,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 #pragma unroll
             for (int e = 0; e < (int)GROUP; ++e) {
                 const uint32_t id = base0 + e;
-                touched |= ((sm->bloom[(id >> 5) & 31u] >> (id & 31u)) & 1u) << e;
+                touched |= ((sm->bloom[(id >> 5) & (BLOOM_WORDS - 1u)] >> (id & 31u)) & 1u) << e;
             }
         }
         if (c.k <= 128u) {
