@@ -655,6 +655,83 @@ __device__ __noinline__ void sort_candidates(SmemFixed *sm, uint32_t n) {
     }
 }
 
+// Whole-block sort of slots [0, n), n <= SORT2K, by (key descending, id
+// ascending): a bitonic network over 2048 packed (key, ~id) words, four per
+// thread in registers. Partners fewer than 32 slots apart sit in the same warp
+// and trade by shuffle; only the wider strides go through shared memory (the
+// key and id arrays, overlaid as 64-bit words, one barrier per stage).
+constexpr uint32_t SORT2K = 2048;
+static_assert(SORT2K == 4 * NT && 2 * SORT2K <= 2 * CAP, "four slots per thread; the overlay fits key + id");
+
+__device__ __forceinline__ unsigned long long sort_exchange(unsigned long long v, unsigned long long other,
+                                                            bool keep_first) {
+    return keep_first ? (v > other ? v : other) : (v < other ? v : other);
+}
+
+__device__ __noinline__ void sort_block_2k(SmemFixed *sm, uint32_t n) {
+    const uint32_t t = threadIdx.x;
+    unsigned long long *buf = reinterpret_cast<unsigned long long *>(sm->key);
+    unsigned long long v[4];
+#pragma unroll
+    for (uint32_t r = 0; r < 4u; ++r) {
+        const uint32_t idx = t + NT * r;
+        v[r] = idx < n ? ((unsigned long long)sm->key[idx] << 32) | (uint32_t)~sm->id[idx] : 0ull;
+    }
+    __syncthreads();  // every slot is in a register: the arrays may be overlaid
+    // Stages of one network level whose partners are in the same warp.
+    auto warp_stages = [&](uint32_t size, uint32_t from_stride) {
+        for (uint32_t stride = from_stride; stride > 0u; stride >>= 1) {
+#pragma unroll
+            for (uint32_t r = 0; r < 4u; ++r) {
+                const uint32_t idx = t + NT * r;
+                const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, v[r], stride);
+                const bool forward = (idx & size) == 0u, lower = (idx & stride) == 0u;
+                v[r] = sort_exchange(v[r], other, forward == lower);
+            }
+        }
+    };
+    for (uint32_t size = 2u; size <= 32u; size <<= 1) {
+        warp_stages(size, size >> 1);
+    }
+    for (uint32_t size = 64u; size <= SORT2K; size <<= 1) {
+#pragma unroll
+        for (uint32_t r = 0; r < 4u; ++r) {
+            buf[t + NT * r] = v[r];
+        }
+        __syncthreads();
+        for (uint32_t stride = size >> 1; stride >= 32u; stride >>= 1) {
+#pragma unroll
+            for (uint32_t h = 0; h < 2u; ++h) {
+                const uint32_t pr = t + NT * h;  // one of the 1024 pairs
+                const uint32_t i = ((pr / stride) * stride << 1) + (pr % stride);
+                const uint32_t j = i + stride;
+                const unsigned long long x = buf[i], y = buf[j];
+                const bool forward = (i & size) == 0u;
+                if ((x < y) == forward) {
+                    buf[i] = y;
+                    buf[j] = x;
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (uint32_t r = 0; r < 4u; ++r) {
+            v[r] = buf[t + NT * r];
+        }
+        warp_stages(size, 16u);
+    }
+    __syncthreads();  // the overlay has been read for the last time
+#pragma unroll
+    for (uint32_t r = 0; r < 4u; ++r) {
+        const uint32_t idx = t + NT * r;
+        if (idx < n) {
+            sm->key[idx] = (uint32_t)(v[r] >> 32);
+            sm->id[idx] = ~(uint32_t)v[r];
+        }
+    }
+    __syncthreads();
+}
+
 // First slot of [0, n) whose prefix sum exceeds target, else the last slot
 // (tests/unit/kernels/sample.rs:48-52). Result in sm->chosen.
 template <bool SMALL>
@@ -2340,6 +2417,18 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         rank_sort(sm, n, c.k);
         n = min(n, c.k);
         sorted = true;
+    } else if (n_slices == 1u && n <= SORT2K) {
+        // A row in one block with many candidates: sorting them all costs less
+        // than selecting the best k and sorting those.
+        sort_block_2k(sm, n);
+        n = min(n, c.k);
+        sorted = true;
+        if (tid == 0) {
+            sm->n = n;
+            sm->n_adj = n;
+            sm->tau_key = sm->key[n - 1u];
+        }
+        __syncthreads();
     } else if (n > c.k) {
         select_topk(sm, n, c.k);
         n = c.k;
