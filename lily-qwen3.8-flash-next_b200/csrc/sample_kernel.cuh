@@ -2399,13 +2399,10 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             if (i < total) {
                 id = i < hist_len ? hist[i] : a.extra_ids[i - hist_len];
             }
-            const bool mine = id >= c.lo && id < c.hi;
-            const unsigned live = __ballot_sync(0xFFFFFFFFu, mine);
-            if (mine) {
-                const unsigned peers = __match_any_sync(live, id);
-                if ((tid & 31u) == (uint32_t)(__ffs(peers) - 1)) {
-                    atomicSub(counts_rw + id, (uint32_t)__popc(peers));
-                }
+            // The row's table is this row's alone, and a slice owns its range of
+            // ids: plain stores (a frequent id is simply zeroed many times).
+            if (id >= c.lo && id < c.hi) {
+                counts_rw[id] = 0u;
             }
         }
     }
