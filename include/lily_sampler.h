@@ -55,6 +55,8 @@ enum lily_row_status {
     LILY_ROW_NAN = 1,        /* a NaN among the adjusted logits */
     LILY_ROW_NONFINITE = 2,  /* largest adjusted logit not finite (all banned) */
     LILY_ROW_PARAMS = 3,     /* device-resident params failed validation */
+    LILY_ROW_LIST = 4,       /* history_len / bias_len / ban_len beyond max_history /
+                                max_list or beyond the list's row pitch: row refused */
     LILY_ROW_FORCED = 16     /* informational: the row returned its forced id */
 };
 
@@ -112,7 +114,7 @@ uint32_t lily_residual_step(uint32_t step);
                                      counterpart of LILY_KERNEL_PROFILE,
                                      src/metal.rs:140-198); off by default */
 #define LILY_MAX_SLICES 128u      /* most thread blocks a row is split over */
-#define LILY_PHASES 16u           /* stamps per block, see lily_sampler_read_phase_clocks */
+#define LILY_PHASES 20u           /* stamps per block, see lily_sampler_read_phase_clocks */
 
 /*
  * src/kernels/sample.rs:130-143 SamplerScratch::new, for `max_rows` rows at
@@ -156,7 +158,8 @@ int32_t lily_sampler_read_counts(lily_sampler_t *h, void *stream, uint32_t slot,
 int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream, uint32_t slot, const uint32_t *host_in);
 
 /*
- * With LILY_FLAG_PHASE_CLOCKS: copies the SM clock stamps of the last launch
+ * With LILY_FLAG_PHASE_CLOCKS: copies the time stamps of the last launch
+ * (nanoseconds of the GPU's global timer: one time base for all blocks)
  * to host_out[max_rows][LILY_MAX_SLICES][LILY_PHASES] (int64 each, 0 where a
  * block did not pass) and clears them; synchronises `stream`. Stamps 0..7,
  * in order: start, history bitmap built, bias/ban ids done, vocabulary
@@ -165,6 +168,9 @@ int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream, uint32_t slot
  * 8 first threshold known; and on the two-pass route (small k) before it
  * 9 pass 1 over the logits done (thread 0), 10 whole block done with it,
  * 11 thread maxima adjusted, 12 threshold searched, 13 threshold stored.
+ * 14, 15: on the route that takes its threshold while the row streams,
+ * thread 0 has the threshold / has collected what its earlier rounds hold
+ * above it; 16 is the block's first instruction.
  */
 int32_t lily_sampler_read_phase_clocks(lily_sampler_t *h, void *stream, int64_t *host_out);
 
@@ -253,7 +259,13 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream, const lily_sample_arg
  * (cudaGetSymbolAddress) and raises the kernel's shared-memory limit; make it
  * before any stream capture. All calls share the one array: it keeps the last
  * call's contents (the entry point clears the words that must start at zero),
- * and two calls that overlap on the GPU, on any streams, race on it.
+ * and two calls that overlap on the GPU, on any streams, race on it. On the
+ * host the entry point may be called from several threads (the one-time
+ * set-up is behind a mutex); keeping their launches from overlapping on the
+ * GPU stays the caller's job. A row that fails on the device (a NaN, no
+ * finite logit, an over-long list) is reported through `out_status` only:
+ * there is no handle whose status word could be read back, so pass
+ * `out_status` when such rows are possible.
  * `vocab` is the row length; errors are written to err[0..err_cap).
  */
 #define LILY_NOALLOC_MAX_ROWS 8u

@@ -24,12 +24,12 @@ F32, BF16 = 0, 1
 SPEC_REJECTION, SPEC_GREEDY_MATCH = 0, 1
 FLAG_COUNTS_TABLE = 1
 FLAG_PHASE_CLOCKS = 2
-MAX_SLICES, PHASES = 128, 16
+MAX_SLICES, PHASES = 128, 20
 
 OK = 0
 ERR_ARG, ERR_PARAMS, ERR_CAPACITY, ERR_FAULT, ERR_VOCAB = -1, -2, -3, -4, -5
 ERR_CUDA, ERR_DEVICE_ROW = 1, 2
-ROW_OK, ROW_NAN, ROW_NONFINITE, ROW_PARAMS, ROW_FORCED = 0, 1, 2, 3, 16
+ROW_OK, ROW_NAN, ROW_NONFINITE, ROW_PARAMS, ROW_LIST, ROW_FORCED = 0, 1, 2, 3, 4, 16
 
 
 class LilyError(RuntimeError):

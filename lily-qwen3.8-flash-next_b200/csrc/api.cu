@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -172,9 +173,20 @@ int32_t launch_one(lily_sampler *h, cudaStream_t stream, const lily::KArgs &a, u
                                    h->max_smem));
         h->attr_mask |= bit;
     }
-    dim3 grid(a.n_slices, rows, 1);
-    kernel<<<grid, lily::NT, smem, stream>>>(a);
-    CU(h, cudaGetLastError());
+    // Programmatic stream serialisation: the grid may be set up and its blocks may
+    // start while the stream's previous kernel drains; the kernel waits
+    // (griddepcontrol.wait) before it reads or writes any global memory.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.n_slices, rows, 1);
+    cfg.blockDim = dim3(lily::NT, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CU(h, cudaLaunchKernelEx(&cfg, kernel, a));
     return LILY_OK;
 }
 
@@ -219,6 +231,8 @@ void base_args(const lily_sampler *h, lily::KArgs *a) {
     a->seen_table = h->seen_table;
     a->seen_words = h->seen_words;
     a->counts_scratch = h->counts_scratch;
+    a->max_history = h->max_history;
+    a->max_list = h->max_list;
     a->part = h->part;
     a->part_n = h->part_n;
     a->tickets = h->tickets;
@@ -228,15 +242,6 @@ void base_args(const lily_sampler *h, lily::KArgs *a) {
     const char *stop = std::getenv("LILY_DEBUG_STOP");
     a->debug_stop = stop ? (uint32_t)std::atoi(stop) : 0u;
 #endif
-}
-
-int32_t ensure_counts_scratch(lily_sampler *h) {
-    if (h->counts_scratch == nullptr) {
-        const size_t bytes = (size_t)h->max_rows * h->vocab * sizeof(uint32_t);
-        CU(h, cudaMalloc(&h->counts_scratch, bytes));
-        CU(h, cudaMemset(h->counts_scratch, 0, bytes));
-    }
-    return LILY_OK;
 }
 
 int32_t check_handle(lily_sampler *h) {
@@ -360,6 +365,16 @@ int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
     if ((e = cudaMalloc(&h->lm_hsum, (size_t)lily_head::BIAS_MAX_GROUPS * lily_head::TOK * sizeof(float))) !=
         cudaSuccess) {
         return bail(e, "LM head group sums");
+    }
+    if (max_history > 0u) {
+        // A row with a frequency penalty over a history LIST counts the list's ids
+        // into this table and clears it again before the launch ends: all zero
+        // between launches. Made here, never inside a draw.
+        const size_t bytes = (size_t)max_rows * vocab * sizeof(uint32_t);
+        if ((e = cudaMalloc(&h->counts_scratch, bytes)) != cudaSuccess ||
+            (e = cudaMemset(h->counts_scratch, 0, bytes)) != cudaSuccess) {
+            return bail(e, "count table of the history lists");
+        }
     }
     if (flags & LILY_FLAG_COUNTS_TABLE) {
         const size_t cb = (size_t)max_rows * vocab * 4, sb = (size_t)max_rows * h->seen_words * 4;
@@ -643,7 +658,6 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
 
     lily::KArgs a;
     base_args(h, &a);
-    bool need_scratch = false;
     const lily_sampling_params_t *d_params = g.params;
     const uint32_t *d_steps = g.steps;
     const uint32_t *d_slots = nullptr;
@@ -661,8 +675,6 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
                 std::snprintf(buf, sizeof buf, "row %u: invalid sampling parameters", r);
                 return fail(h, LILY_ERR_PARAMS, buf);
             }
-            need_scratch = need_scratch || (uses_penalties(g.params[r]) &&
-                                            g.params[r].frequency_penalty != 0.0f);
         }
         char *hs = h->h_stage[slot];
         std::memcpy(hs + h->layout.params, g.params, sizeof(lily_sampling_params_t) * g.rows);
@@ -672,8 +684,6 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
             std::memcpy(hs + h->layout.steps, g.steps, sizeof(uint32_t) * g.rows);
             d_steps = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.steps);
         }
-    } else {
-        need_scratch = true;
     }
     if (g.count_slots != nullptr) {
         for (uint32_t r = 0; r < g.rows; ++r) {
@@ -683,14 +693,6 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
         }
         std::memcpy(h->h_stage[slot] + h->layout.slots, g.count_slots, sizeof(uint32_t) * g.rows);
         d_slots = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.slots);
-        need_scratch = false;
-    }
-    if (need_scratch && g.history_ids != nullptr) {
-        st = ensure_counts_scratch(h);
-        if (st != LILY_OK) {
-            return st;
-        }
-        a.counts_scratch = h->counts_scratch;
     }
     if (slot >= 0) {
         CU(h, cudaMemcpyAsync(h->d_stage[slot], h->h_stage[slot], h->layout.total,
@@ -1191,14 +1193,6 @@ int32_t lily_spec_verify(lily_sampler_t *h, void *stream_, const lily_spec_args_
 
     lily::KArgs a;
     base_args(h, &a);
-    const bool list_counts = pen && p.frequency_penalty != 0.0f && g.count_slot == nullptr;
-    if (list_counts) {
-        st = ensure_counts_scratch(h);
-        if (st != LILY_OK) {
-            return st;
-        }
-        a.counts_scratch = h->counts_scratch;
-    }
     a.logits = g.target_logits;
     a.logits_ld = g.logits_ld;
     a.rows = g.m;
@@ -1309,6 +1303,7 @@ struct NoAllocDevice {
     uint32_t attr_mask = 0;
 };
 NoAllocDevice g_noalloc_devices[64];
+std::mutex g_noalloc_mutex;  // guards the per-device set-up above (host threads may race to the first call)
 
 int32_t noalloc_fail(int32_t code, const char *msg, char *err, uint32_t err_cap) {
     if (err != nullptr && err_cap > 0u) {
@@ -1322,13 +1317,16 @@ cudaError_t noalloc_launch_one(NoAllocDevice *d, cudaStream_t stream, const lily
                                uint32_t rows, size_t smem) {
     auto kernel = lily::sample_rows_kernel<T, VEC>;
     const uint32_t bit = 1u << ((sizeof(T) == 4 ? 0 : 2) + (VEC ? 1 : 0));
-    if (!(d->attr_mask & bit)) {
-        const cudaError_t e = cudaFuncSetAttribute(
-            kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d->max_smem);
-        if (e != cudaSuccess) {
-            return e;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!(d->attr_mask & bit)) {
+            const cudaError_t e = cudaFuncSetAttribute(
+                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d->max_smem);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            d->attr_mask |= bit;
         }
-        d->attr_mask |= bit;
     }
     dim3 grid(a.n_slices, rows, 1);
     kernel<<<grid, lily::NT, smem, stream>>>(a);
@@ -1390,24 +1388,27 @@ int32_t lily_sample_batch_noalloc(void *stream_, uint32_t vocab, const lily_samp
         return noalloc_fail(LILY_ERR_CUDA, "no current CUDA device", err, err_cap);
     }
     NoAllocDevice *d = &g_noalloc_devices[device];
-    if (!d->ready) {
-        // Set-up, once per device, with that device current: the array's
-        // address ON THIS DEVICE. (Passing the host-side name to the kernel
-        // instead would hand it a host address.)
-        void *p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (e != cudaSuccess || p == nullptr) {
-            return noalloc_fail(LILY_ERR_CUDA, "cudaGetSymbolAddress failed for the static scratch",
-                                err, err_cap);
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!d->ready) {
+            // Set-up, once per device, with that device current: the array's
+            // address ON THIS DEVICE. (Passing the host-side name to the kernel
+            // instead would hand it a host address.)
+            void *p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || p == nullptr) {
+                return noalloc_fail(LILY_ERR_CUDA, "cudaGetSymbolAddress failed for the static scratch",
+                                    err, err_cap);
+            }
+            if (cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, device) !=
+                    cudaSuccess ||
+                cudaDeviceGetAttribute(&d->max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) !=
+                    cudaSuccess) {
+                return noalloc_fail(LILY_ERR_CUDA, "device attributes unavailable", err, err_cap);
+            }
+            d->scratch = static_cast<NoAllocScratch *>(p);
+            d->ready = true;
         }
-        if (cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, device) !=
-                cudaSuccess ||
-            cudaDeviceGetAttribute(&d->max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) !=
-                cudaSuccess) {
-            return noalloc_fail(LILY_ERR_CUDA, "device attributes unavailable", err, err_cap);
-        }
-        d->scratch = static_cast<NoAllocScratch *>(p);
-        d->ready = true;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     NoAllocScratch *sc = d->scratch;
@@ -1425,6 +1426,8 @@ int32_t lily_sample_batch_noalloc(void *stream_, uint32_t vocab, const lily_samp
     lily::KArgs a;
     std::memset(&a, 0, sizeof(a));
     a.vocab = vocab;
+    a.max_history = 1u << 16;
+    a.max_list = 512u;
     a.part = &sc->part[0][0];
     a.part_n = &sc->part_n[0][0];
     a.tickets = sc->tickets;

@@ -54,6 +54,7 @@ constexpr uint32_t H0_SHIFT = 19;       // first-round histogram: raw key >> 19,
 constexpr uint32_t H0_BINS = 1u << (32 - H0_SHIFT);
 constexpr uint32_t TH_BINS = 1024;      // tightening histogram: raw key >> 16 above a base
 constexpr uint32_t RANKSORT_MAX = 384;  // candidate counts up to this are rank-sorted
+constexpr uint32_t LCAP = 1024;         // candidates of a row that streams with the full ring (see lean_stream)
 
 // Per logit type: 16 bf16 or 8 f32 per thread per round.
 template <typename T>
@@ -102,6 +103,8 @@ struct KArgs {
     const uint32_t *extra_ids;  // ids appended to every row's history (earlier draws of a step)
     uint32_t extra_len;
     uint32_t force_greedy;      // ignore params: exact argmax rows
+    uint32_t max_history;       // history_len[row] above this (or above history_ld) refuses the row
+    uint32_t max_list;          // likewise bias_len[row] and ban_len[row]
     const uint32_t *bias_ids;
     const float *bias_vals;
     const uint32_t *bias_len;
@@ -157,6 +160,16 @@ struct RowCtx {
     bool sp_in_smem;
 };
 
+// What lean_stream needs beyond its register arguments; read when the
+// threshold is taken or a fragment has to be read again, not in the rounds.
+struct StreamShared {
+    uint32_t nfull;       // full rounds (rounds 0..2 are already on their way)
+    uint32_t has_part;    // whether a partial round follows them
+    uint32_t r_check;     // the round after which the threshold is taken
+    uint32_t k;
+    uint32_t lo, hi;      // the slice's ids
+};
+
 struct alignas(16) SmemFixed {
     uint32_t key[CAP];    // candidates: adjusted keys below n_adj, raw logit bits above;
     uint32_t id[CAP];     //   during the first round key+id hold the 8192-bin histogram
@@ -187,6 +200,17 @@ struct alignas(16) SmemFixed {
     float p_d;
     float q_d;
     uint32_t bloom[BLOOM_WORDS];
+    // Where pushes go: key / id (CAP entries), or lkey / lid (LCAP) while the
+    // cp.async ring borrows key and id as its third and fourth stage.
+    uint32_t *ckey;
+    uint32_t *cid;
+    uint32_t ccap;
+    float u_draw;         // the row's uniform, fetched (or derived) when the block starts
+    uint32_t lean_abort;  // lean_stream: a thread saw a NaN before the threshold was taken
+    alignas(8) unsigned long long mbar[2];  // lean_stream: history marked; thread maxima written
+    uint32_t lkey[LCAP];
+    uint32_t lid[LCAP];
+    StreamShared stream;
 #ifdef LILY_DEBUG
     uint32_t dbg_hits, dbg_hit_warps, dbg_tighten;
 #endif
@@ -197,6 +221,13 @@ static_assert(2 * CAP >= H0_BINS, "the first-round histogram aliases the candida
 static_assert(CAP >= KCAP + NT, "a selection must leave room for one push per thread");
 
 __device__ __forceinline__ float neg_inf() { return __uint_as_float(0xFF800000u); }
+
+// Nanoseconds of the GPU's global timer: one time base for every block of a launch.
+__device__ __forceinline__ long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return (long long)t;
+}
 
 // Warp-aggregated append to the candidate buffer. A full buffer refuses the
 // entry and raises the overflow flag; the caller remembers the element and
@@ -211,9 +242,9 @@ __device__ __forceinline__ bool push(SmemFixed *sm, uint32_t key, uint32_t id) {
     }
     base = __shfl_sync(act, base, leader);
     const uint32_t slot = base + __popc(act & ((1u << lane) - 1u));
-    if (slot < CAP) {
-        sm->key[slot] = key;
-        sm->id[slot] = id;
+    if (slot < sm->ccap) {
+        sm->ckey[slot] = key;
+        sm->cid[slot] = id;
         return true;
     }
     sm->overflow = 1;
@@ -323,9 +354,10 @@ __device__ __noinline__ void adjust_pending(SmemFixed *sm) {
 // front in chunks so that no entry is overwritten before it is read.
 __device__ __noinline__ void filter_adjust(SmemFixed *sm) {
     const uint32_t tid = threadIdx.x;
-    const uint32_t n = min(sm->n, CAP);
+    const uint32_t n = min(sm->n, sm->ccap);
     const uint32_t from = sm->n_adj;
     const uint32_t kstar = sm->kstar;
+    const uint32_t *src_key = sm->ckey, *src_id = sm->cid;
     if (tid == 0) {
         sm->cnt = 0;
     }
@@ -335,8 +367,8 @@ __device__ __noinline__ void filter_adjust(SmemFixed *sm) {
         bool alive = false;
         uint32_t key = 0, id = 0;
         if (i < n) {
-            id = sm->id[i];
-            key = sm->key[i];
+            id = src_id[i];
+            key = src_key[i];
             if (i >= from) {
                 key = adjusted_key(sm, id, __uint_as_float(key), false);
             }
@@ -367,6 +399,9 @@ __device__ __noinline__ void filter_adjust(SmemFixed *sm) {
 #endif
         sm->n = sm->cnt;
         sm->n_adj = sm->cnt;
+        sm->ckey = sm->key;  // from here on the candidates live in key / id
+        sm->cid = sm->id;
+        sm->ccap = CAP;
     }
     __syncthreads();
 }
@@ -931,6 +966,123 @@ __device__ __noinline__ void finalize(SmemFixed *sm, const KArgs &a, uint32_t ro
     }
 }
 
+// finalize for at most 64 sorted candidates and a plain (not speculative)
+// draw, one warp, everything in registers: lane i holds candidates i and
+// i + 32. The prefix sums are the sequential rank-order sums of the
+// reference (tests/unit/kernels/sample.rs:37-46): every lane runs the same
+// chain of adds over values handed round by shuffles, which do not sit on the
+// chain.
+__device__ __noinline__ void finalize_warp(SmemFixed *sm, const KArgs &a, uint32_t row, uint32_t n,
+                                           uint64_t seed) {
+    const RowCtx &c = sm->ctx;
+    const uint32_t lane = threadIdx.x & 31u;
+    constexpr unsigned FULL = 0xFFFFFFFFu;
+    const uint32_t k0 = lane < n ? sm->key[lane] : 0u, k1 = lane + 32u < n ? sm->key[lane + 32u] : 0u;
+    const uint32_t i0 = lane < n ? sm->id[lane] : 0xFFFFFFFFu, i1 = lane + 32u < n ? sm->id[lane + 32u] : 0xFFFFFFFFu;
+    const float top = float_of_key(__shfl_sync(FULL, k0, 0));
+    uint32_t err = sm->err;
+    if (!c.argmax_mode && err == 0 && (top == neg_inf() || top == -neg_inf())) {
+        err = LILY_ROW_NONFINITE;
+    }
+    if (err != 0) {
+        if (lane == 0) {
+            a.out_ids[row] = 0xFFFFFFFFu;
+            if (a.out_status) {
+                a.out_status[row] = err;
+            }
+            if (a.kept_n) {
+                a.kept_n[row] = 0;
+            }
+            atomicOr(a.status_word, 1u << (err & 31u));
+        }
+        return;
+    }
+    if (c.argmax_mode) {
+        if (lane == 0) {
+            a.out_ids[row] = i0;
+            if (a.out_status) {
+                a.out_status[row] = LILY_ROW_OK;
+            }
+            if (a.kept_n) {
+                a.kept_n[row] = 1;
+                a.kept_ids[(uint64_t)row * a.kept_ld] = i0;
+                a.kept_probs[(uint64_t)row * a.kept_ld] = 1.0f;
+            }
+        }
+        return;
+    }
+    const float u = sm->u_draw;
+    const float p0 = lane < n ? exp_f32(__fsub_rn(float_of_key(k0), top)) : 0.0f;
+    const float p1 = lane + 32u < n ? exp_f32(__fsub_rn(float_of_key(k1), top)) : 0.0f;
+    float s = 0.0f, c0 = 0.0f, c1 = 0.0f;
+    const uint32_t n_lo = min(n, 32u);
+    for (uint32_t i = 0; i < n_lo; ++i) {
+        s = __fadd_rn(s, __shfl_sync(FULL, p0, (int)i));
+        c0 = lane == i ? s : c0;
+    }
+    for (uint32_t i = 32u; i < n; ++i) {
+        s = __fadd_rn(s, __shfl_sync(FULL, p1, (int)(i - 32u)));
+        c1 = lane == i - 32u ? s : c1;
+    }
+    // Keep rank i >= 1 while the mass before it is below top_p of the total and
+    // its weight reaches min_p; the first rank that fails ends the kept set.
+    const float limit = __fmul_rn(c.top_p, s);
+    const float up0 = __shfl_up_sync(FULL, c0, 1);
+    const float up1 = __shfl_up_sync(FULL, c1, 1);
+    const float last0 = __shfl_sync(FULL, c0, 31);
+    const float before0 = up0, before1 = lane == 0u ? last0 : up1;
+    uint32_t stop = n;
+    if (lane + 32u < n && !(before1 < limit && p1 >= c.min_p)) {
+        stop = lane + 32u;
+    }
+    if (lane >= 1u && lane < n && !(before0 < limit && p0 >= c.min_p)) {
+        stop = lane;
+    }
+    const uint32_t n_keep = __reduce_min_sync(FULL, stop);
+    const uint32_t last = n_keep - 1u;
+    const float mass = last < 32u ? __shfl_sync(FULL, c0, (int)last) : __shfl_sync(FULL, c1, (int)(last - 32u));
+    if (a.kept_n) {
+        if (lane < n_keep) {
+            a.kept_ids[(uint64_t)row * a.kept_ld + lane] = i0;
+            a.kept_probs[(uint64_t)row * a.kept_ld + lane] = __fdiv_rn(p0, mass);
+        }
+        if (lane + 32u < n_keep) {
+            a.kept_ids[(uint64_t)row * a.kept_ld + lane + 32u] = i1;
+            a.kept_probs[(uint64_t)row * a.kept_ld + lane + 32u] = __fdiv_rn(p1, mass);
+        }
+        if (lane == 0) {
+            a.kept_n[row] = n_keep;
+        }
+    }
+    // First kept rank whose prefix sum exceeds the target, else the last one
+    // (tests/unit/kernels/sample.rs:48-52).
+    const float target = __fmul_rn(u, mass);
+    uint32_t hit = last;
+    if (lane + 32u < n_keep && target < c1) {
+        hit = lane + 32u;
+    }
+    if (lane < n_keep && target < c0) {
+        hit = lane;
+    }
+    const uint32_t chosen = __reduce_min_sync(FULL, hit);
+    const uint32_t chosen_id = chosen < 32u ? __shfl_sync(FULL, i0, (int)chosen) : __shfl_sync(FULL, i1, (int)(chosen - 32u));
+    if (lane == 0) {
+        a.out_ids[row] = chosen_id;
+        if (a.out_status) {
+            a.out_status[row] = LILY_ROW_OK;
+        }
+        if (c.use_pen && a.count_slots) {
+            // src/kernels/metal/sample.metal:509-511: the draw is counted.
+            const uint32_t slot = a.count_slots[row];
+            if (chosen_id < a.vocab) {
+                atomicAdd(a.counts_table + (uint64_t)slot * a.vocab + chosen_id, 1u);
+                atomicOr(a.seen_table + (uint64_t)slot * a.seen_words + (chosen_id >> 5),
+                         1u << (chosen_id & 31u));
+            }
+        }
+    }
+}
+
 
 // Raises the raw threshold to `c` (pass iff l > c) and the adjusted-key
 // threshold to `kstar` (survivors have key >= kstar). Any single thread;
@@ -1479,18 +1631,410 @@ __device__ __noinline__ uint32_t lean_pass2(SmemFixed *sm, const char *src0, uin
     return (second ? 1u : 0u) | (third ? 2u : 0u) | (!(m4 <= c_fix) ? 4u : 0u);
 }
 
+
 // Phase stamps for the optional per-block timing trace.
 enum { PH_START = 0, PH_BITMAPS, PH_LISTS, PH_STREAM, PH_LOCAL_SELECT, PH_MERGE, PH_SORT, PH_END,
        PH_FIRST_THRESHOLD, PH_PASS1, PH_PASS1_MET, PH_MAXIMA, PH_SEARCH, PH_THRESHOLD_SET, PH_SPARE0,
-       PH_SPARE1 };
+       PH_SPARE1, PH_ENTRY };
+
 
 #define LILY_STAMP(phase)                                                                  \
     do {                                                                                   \
         if (a.phase_clocks != nullptr && threadIdx.x == 0) {                               \
             a.phase_clocks[((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES + (phase)] = \
-                clock64();                                                                 \
+                global_ns();                                                               \
         }                                                                                  \
     } while (0)
+
+// ---- One pass with the threshold taken on the way (rows that keep few
+// candidates, aligned logits, no bias / ban list).
+//
+// The row streams through the four-stage ring exactly once. Up to round
+// `r_check` a thread only tracks maxima, as lean_pass1 does. At `r_check`
+// every thread adjusts its largest logit so far and leaves the key in shared
+// memory; warp 0 alone takes the k-th largest of those 512 keys (keys of 512
+// different ids: a lower bound of the row's k-th largest adjusted value),
+// turns it into the raw-space bound and publishes it, while the other warps
+// keep streaming. A thread that sees the bound collects what its rounds so
+// far hold above it (its best fragment is still in registers; a second or
+// third fragment is read again) and from then on tests every new fragment
+// against the bound directly. Nobody waits at a block barrier inside the
+// stream, so DRAM stays busy, and when the last round has landed the
+// candidates are already in the buffer.
+//
+// History ids are marked in the seen bitmap inside the first rounds (two
+// 16-byte loads per thread and round); an mbarrier tells the threads that take
+// the threshold that every mark is in place.
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count) {
+    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(at), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
+    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}" ::"r"(at) : "memory");
+}
+
+// Waits for the barrier's first phase, at most about a millisecond; false if
+// it gave up (a bug elsewhere: the caller leaves the two-pass route).
+__device__ __forceinline__ bool mbar_wait_first(unsigned long long *bar) {
+    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(at)
+            : "memory");
+        if (done) {
+            return true;
+        }
+    }
+    return false;
+}
+
+// The threshold of lean_stream. Every warp sorts its 32 thread keys and
+// leaves its best POOL_PER_WARP in a pool of 128: keys of 128 different ids,
+// whose k-th largest (k <= 128) is a lower bound of the row's k-th largest
+// adjusted value, and equals the k-th largest of all 512 keys unless one warp
+// holds more than eight of the best k.
+constexpr uint32_t POOL_PER_WARP = 8;
+constexpr uint32_t POOL = POOL_PER_WARP * (NT / 32);
+static_assert(POOL == 128, "four pool keys per lane");
+
+__device__ __forceinline__ uint32_t warp_sort_desc(uint32_t v) {
+    const uint32_t lane = threadIdx.x & 31u;
+#pragma unroll
+    for (uint32_t size = 2u; size <= 32u; size <<= 1) {
+#pragma unroll
+        for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
+            const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, v, stride);
+            const bool first = ((lane & size) == 0u) == ((lane & stride) == 0u);
+            v = first ? max(v, other) : min(v, other);
+        }
+    }
+    return v;  // lane 0 holds the largest
+}
+
+// Any full warp: the largest v with its low 16 bits clear that at least k of
+// the pool's keys reach, bit by bit from the top.
+__device__ __forceinline__ uint32_t pool_kth(const uint32_t *pool, uint32_t k) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t v0 = pool[lane], v1 = pool[lane + 32u], v2 = pool[lane + 64u], v3 = pool[lane + 96u];
+    uint32_t kth = 0u;
+#pragma unroll 1
+    for (int bit = 31; bit >= 16; --bit) {
+        const uint32_t cand = kth | (1u << bit);
+        const uint32_t cnt = (v0 >= cand ? 1u : 0u) + (v1 >= cand ? 1u : 0u) + (v2 >= cand ? 1u : 0u) +
+                             (v3 >= cand ? 1u : 0u);
+        if (__reduce_add_sync(0xFFFFFFFFu, cnt) >= k) {
+            kth = cand;
+        }
+    }
+    return kth;
+}
+
+// Whether the barrier's first phase is over (does not wait).
+__device__ __forceinline__ bool mbar_test_first(unsigned long long *bar) {
+    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done)
+                 : "r"(at)
+                 : "memory");
+    return done != 0u;
+}
+
+// Elements of a fragment from `nvalid` on become -inf (the row's last,
+// partial round: cp.async filled them with zeros).
+template <typename T>
+__device__ __forceinline__ void frag_mask_tail(Frag &f, uint32_t nvalid) {
+    uint32_t *w = reinterpret_cast<uint32_t *>(&f);
+    if (sizeof(T) == 4) {
+#pragma unroll
+        for (uint32_t e = 0; e < 8u; ++e) {
+            if (e >= nvalid) {
+                w[e] = 0xFF800000u;
+            }
+        }
+    } else {
+#pragma unroll
+        for (uint32_t e = 0; e < 8u; ++e) {
+            const uint32_t lo = 2u * e < nvalid ? (w[e] & 0xFFFFu) : 0xFF80u;
+            const uint32_t hi = 2u * e + 1u < nvalid ? (w[e] & 0xFFFF0000u) : 0xFF800000u;
+            w[e] = lo | hi;
+        }
+    }
+}
+
+template <typename T>
+__device__ __noinline__ uint32_t lean_stream(SmemFixed *sm, const StreamShared *gs, uint32_t slot_a,
+                                             uint32_t slot_b, const char *src0, const uint4 *h4, uint32_t n4,
+                                             uint32_t seen_at, long long *stamps) {
+    constexpr uint32_t NONE = 0xFFFFFFFFu;
+    constexpr uint32_t GROUP = Geo<T>::GROUP, ROUND = Geo<T>::ROUND;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t nfull = gs->nfull;
+    const uint32_t nproc = nfull + gs->has_part;
+    const uint32_t r_check = gs->r_check;
+    const uint32_t mark_rounds = (n4 + 2u * NT - 1u) / (2u * NT);  // <= r_check < nfull
+
+    float best = neg_inf(), m2 = neg_inf(), m3 = neg_inf(), m4 = neg_inf();
+    uint32_t best_r = NONE, r2 = NONE, r3 = NONE;
+    Frag keep;
+    keep.v[0] = make_uint4(0, 0, 0, 0);
+    keep.v[1] = make_uint4(0, 0, 0, 0);
+    uint32_t saw_nan = 0u;
+
+    // The thread's logits in the partial round (0 if it has none).
+    auto part_valid = [&]() -> uint32_t {
+        const uint32_t at = gs->lo + nfull * ROUND + tid * GROUP;
+        return (gs->has_part && at < gs->hi) ? min(GROUP, gs->hi - at) : 0u;
+    };
+    const char *src = src0 + 3u * ROUND_BYTES;  // the round three ahead of the one being read
+    // Starts the copy of round rr + 3 (into the stage round rr - 1 has left) and
+    // waits for round rr.
+    auto advance = [&](uint32_t rr) {
+        if (rr + 3u < nproc) {
+            const uint32_t st = (rr + 3u) & 3u;
+            const uint32_t dst = ((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES;
+            if (rr + 3u < nfull) {
+                lean_copy_round(dst, src);
+            } else {
+                const uint32_t bytes = part_valid() * (uint32_t)sizeof(T);
+                const uint32_t b0 = min(bytes, 16u), b1 = bytes > 16u ? bytes - 16u : 0u;
+                // (A source of zero bytes is never read; it still has to be an address.)
+                const char *base = src - (size_t)(rr + 3u) * ROUND_BYTES;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst),
+                             "l"(b0 ? src : base), "r"(b0)
+                             : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst + 16u),
+                             "l"(b1 ? src + 16 : base), "r"(b1)
+                             : "memory");
+            }
+        }
+        cp_async_commit();
+        src += ROUND_BYTES;
+        cp_async_wait<3>();
+    };
+    auto read_round = [&](uint32_t rr, Frag &cur) -> bool {
+        const uint32_t st = rr & 3u;
+        lean_read_slot(((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES, cur);
+        if (rr == nfull) {
+            const uint32_t pv = part_valid();
+            frag_mask_tail<T>(cur, pv);
+            return pv != 0u;
+        }
+        return true;
+    };
+    auto track = [&](const Frag &cur, uint32_t rr) {
+        const float m = frag_max<T>(cur);
+        saw_nan |= m != m ? 1u : 0u;
+        // The three best fragments by maximum (rounds best_r, r2, r3) and the
+        // largest maximum among all the others (m4).
+        if (best_r == NONE || m > best) {
+            m4 = fmaxf(m4, m3);
+            m3 = m2;
+            r3 = r2;
+            m2 = best;
+            r2 = best_r;
+            best = m;
+            best_r = rr;
+            keep = cur;
+        } else if (r2 == NONE || m > m2) {
+            m4 = fmaxf(m4, m3);
+            m3 = m2;
+            r3 = r2;
+            m2 = m;
+            r2 = rr;
+        } else if (r3 == NONE || m > m3) {
+            m4 = fmaxf(m4, m3);
+            m3 = m;
+            r3 = rr;
+        } else {
+            m4 = fmaxf(m4, m);
+        }
+    };
+
+    uint32_t rr = 0;
+    // ---- rounds that also mark history ids (two 16-byte loads ahead)
+    if (mark_rounds != 0u) {
+        const uint4 no_ids = make_uint4(NONE, NONE, NONE, NONE);
+        const uint32_t lo = gs->lo, width = gs->hi - gs->lo;
+        uint32_t hnext = tid;
+        uint4 hq0 = hnext < n4 ? __ldg(h4 + hnext) : no_ids;
+        uint4 hq1 = hnext + NT < n4 ? __ldg(h4 + hnext + NT) : no_ids;
+        hnext += 2u * NT;
+        for (; rr < mark_rounds; ++rr) {
+            advance(rr);
+            {
+                const uint32_t ids[8] = {hq0.x, hq0.y, hq0.z, hq0.w, hq1.x, hq1.y, hq1.z, hq1.w};
+                hq0 = hnext < n4 ? __ldg(h4 + hnext) : no_ids;
+                hq1 = hnext + NT < n4 ? __ldg(h4 + hnext + NT) : no_ids;
+                hnext += 2u * NT;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t off = ids[i] - lo;
+                    if (off < width) {
+                        asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(seen_at + (off >> 5) * 4u),
+                                     "r"(1u << (off & 31u))
+                                     : "memory");
+                    }
+                }
+            }
+            Frag cur;
+            read_round(rr, cur);  // (a full round: mark_rounds < nfull)
+            track(cur, rr);
+        }
+    }
+    mbar_arrive(&sm->mbar[0]);  // this thread's history marks are in place
+    // ---- rounds up to the one after which the threshold is taken
+    for (; rr <= r_check; ++rr) {
+        advance(rr);
+        Frag cur;
+        read_round(rr, cur);
+        track(cur, rr);
+    }
+    {
+        // The threshold, this warp's share: every thread adjusts its largest logit
+        // so far; the warp's best eight keys go to the pool.
+        bool ok = mbar_wait_first(&sm->mbar[0]);
+        uint32_t key = 0u;
+        if (!ok || saw_nan != 0u || best_r == NONE) {
+            sm->lean_abort = 1u;
+        } else {
+            uint32_t at = 0;
+#pragma unroll
+            for (int e = (int)GROUP - 1; e >= 0; --e) {
+                if (frag_get<T>(keep, e) == best) {
+                    at = (uint32_t)e;
+                }
+            }
+            key = adjusted_key(sm, gs->lo + best_r * ROUND + tid * GROUP + at, best, false);
+        }
+        __syncwarp();
+        key = warp_sort_desc(key);
+        uint32_t *pool = sm->thist;  // POOL words
+        if ((tid & 31u) < POOL_PER_WARP) {
+            pool[(tid >> 5) * POOL_PER_WARP + (tid & 31u)] = key;
+        }
+        __syncwarp();
+        if ((tid & 31u) == 0u) {
+            mbar_arrive(&sm->mbar[1]);
+        }
+    }
+    // ---- rounds until every warp's keys are in the pool
+    bool pooled = __all_sync(0xFFFFFFFFu, mbar_test_first(&sm->mbar[1]));
+    for (; rr < nproc && !pooled; ++rr) {
+        advance(rr);
+        Frag cur;
+        if (read_round(rr, cur)) {
+            track(cur, rr);
+        }
+        pooled = __all_sync(0xFFFFFFFFu, mbar_test_first(&sm->mbar[1]));
+    }
+    if (!pooled) {
+        // The stream ended first (every warp passes the round above on its own).
+        cp_async_wait<0>();
+        pooled = mbar_wait_first(&sm->mbar[1]);
+    }
+    pooled = __all_sync(0xFFFFFFFFu, pooled);
+    if (!pooled || *reinterpret_cast<volatile uint32_t *>(&sm->lean_abort) != 0u) {
+        cp_async_wait<0>();
+        return saw_nan | 2u;
+    }
+    // Every warp takes the bound for itself (the same pool, the same result).
+    const uint32_t kth = pool_kth(sm->thist, gs->k);
+    const uint32_t kstar = kth > 0u ? kth - 1u : 0u;  // ties with the k-th value must still pass
+    const float c_fix = raw_threshold(kstar, sm->ctx.T, sm->ctx.argmax_mode);
+    if (tid == 0) {
+        raise_threshold(sm, c_fix, kstar);  // for the selection after the stream
+        if (stamps) {
+            stamps[PH_SPARE0] = global_ns();
+        }
+    }
+
+    {
+        // What the rounds [0, rr) of this thread hold above the bound: its best
+        // fragment is still in registers; a second or third is read again (L2 by
+        // now; the partial round ends anywhere, so it comes element by element).
+        const uint32_t base0 = gs->lo + tid * GROUP;
+        const char *first = src - (size_t)(rr + 3u) * ROUND_BYTES;  // the thread's 32 bytes of round 0
+        const uint32_t pv = part_valid();
+        auto valid_of = [&](uint32_t r) -> uint32_t { return r < nfull ? 0xFFFFFFFFu : (1u << pv) - 1u; };
+        auto reread = [&](uint32_t r, Frag &f) {
+            if (r < nfull) {
+                const uint4 *p = reinterpret_cast<const uint4 *>(first + (size_t)r * ROUND_BYTES);
+                f.v[0] = __ldcg(p);
+                f.v[1] = __ldcg(p + 1);
+            } else {
+                f.v[0] = make_uint4(0, 0, 0, 0);
+                f.v[1] = make_uint4(0, 0, 0, 0);
+                const T *p = reinterpret_cast<const T *>(first + (size_t)r * ROUND_BYTES);
+                uint32_t *w = reinterpret_cast<uint32_t *>(&f);
+                for (uint32_t e = 0; e < pv; ++e) {
+                    if (sizeof(T) == 4) {
+                        w[e] = __float_as_uint(widen(p[e]));
+                    } else {
+                        const uint32_t b = reinterpret_cast<const uint16_t *>(p)[e];
+                        w[e >> 1] |= (e & 1u) ? (b << 16) : b;
+                    }
+                }
+                frag_mask_tail<T>(f, pv);
+            }
+        };
+        if (best_r != NONE && !(best <= c_fix)) {
+            lean_take<T>(sm, keep, base0 + best_r * ROUND, valid_of(best_r), c_fix);
+        }
+        const bool second = r2 != NONE && !(m2 <= c_fix);
+        const bool third = r3 != NONE && !(m3 <= c_fix);
+        Frag f2, f3;
+        if (second) {
+            reread(r2, f2);
+        }
+        if (third) {
+            reread(r3, f3);
+        }
+        if (second) {
+            lean_take<T>(sm, f2, base0 + r2 * ROUND, valid_of(r2), c_fix);
+        }
+        if (third) {
+            lean_take<T>(sm, f3, base0 + r3 * ROUND, valid_of(r3), c_fix);
+        }
+        if (!(m4 <= c_fix)) {
+            // Very rare: a fourth fragment of this thread may matter.
+            for (uint32_t r = 0; r < rr; ++r) {
+                if (r == best_r || r == r2 || r == r3) {
+                    continue;
+                }
+                Frag f;
+                reread(r, f);
+                if (!(frag_max<T>(f) <= c_fix)) {
+                    lean_take<T>(sm, f, base0 + r * ROUND, valid_of(r), c_fix);
+                }
+            }
+        }
+    }
+    if (stamps && tid == 0) {
+        stamps[PH_SPARE1] = global_ns();
+    }
+    // ---- the remaining rounds: every fragment straight against the bound
+    for (; rr < nproc; ++rr) {
+        advance(rr);
+        Frag cur;
+        if (read_round(rr, cur)) {
+            const float m = frag_max<T>(cur);
+            saw_nan |= m != m ? 1u : 0u;
+            if (!(m <= c_fix)) {
+                const uint32_t valid = rr < nfull ? 0xFFFFFFFFu : (1u << part_valid()) - 1u;
+                lean_take<T>(sm, cur, gs->lo + rr * ROUND + tid * GROUP, valid, c_fix);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    return saw_nan;
+}
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constant__ KArgs a) {
@@ -1503,10 +2047,67 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     const uint32_t row = a.row0 + blockIdx.y;  // every per-row array is indexed by this
     const uint32_t slice = blockIdx.x;
     const uint32_t out_row = row;
+    LILY_STAMP(PH_ENTRY);
 
-    // The row's history length is asked for now: its latency overlaps that
-    // of the parameters below.
+    // What needs no input is done first: when the launch carries the
+    // programmatic-serialisation attribute, the blocks of this grid start while
+    // the previous kernel of the stream is still finishing, and wait below for
+    // its memory before they read anything. (Without the attribute the two
+    // instructions do nothing.)
+    const bool whole_row_seen = a.n_slices == 1u;  // the block's slice is the whole row: the bitmap's size is known
+    if (tid < BLOOM_WORDS) {
+        sm->bloom[tid] = 0;
+    }
+    for (uint32_t b = tid; b < TH_BINS; b += NT) {
+        sm->thist[b] = 0;
+    }
+    if (whole_row_seen) {
+        const uint32_t words = (a.vocab + 31u) >> 5;
+        for (uint32_t w = tid; w < words; w += NT) {
+            seen[w] = 0;
+        }
+    }
+    if (tid == 0) {
+        mbar_init(&sm->mbar[0], NT);
+        mbar_init(&sm->mbar[1], NT / 32);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // Everything the block has to know about its row is asked for first, in
+    // one go: these few loads would otherwise queue behind the first rounds of
+    // logits that every block of the launch asks for below.
     const uint32_t hist_len_row = (a.history_ids && a.history_len) ? __ldg(a.history_len + row) : 0u;
+    const int32_t forced = a.forced_ids ? __ldg(a.forced_ids + row) : -1;
+    const uint32_t bias_len_row = (a.bias_ids && a.bias_len) ? __ldg(a.bias_len + row) : 0u;
+    const uint32_t ban_len_row = (a.ban_ids && a.ban_len) ? __ldg(a.ban_len + row) : 0u;
+    const uint32_t slot_row = a.count_slots ? __ldg(a.count_slots + row) : 0u;
+    const float u_row = a.uniforms ? __ldg(a.uniforms + row) : 0.0f;
+    const uint32_t step_row = (!a.uniforms && a.steps) ? __ldg(a.steps + row) : 0u;
+    lily_sampling_params_t P;
+    if (a.force_greedy) {
+        P.temperature = 0.0f;
+        P.top_k = 1;
+        P.top_p = 1.0f;
+        P.min_p = 0.0f;
+        P.presence_penalty = 0.0f;
+        P.frequency_penalty = 0.0f;
+        P.repetition_penalty = 1.0f;
+        P.seed = 0;
+    } else {
+        // 40 bytes, 8-byte aligned: five 8-byte loads.
+        const uint2 *pp = reinterpret_cast<const uint2 *>(a.params + row);
+        const uint2 w0 = __ldg(pp), w1 = __ldg(pp + 1), w2 = __ldg(pp + 2), w3 = __ldg(pp + 3), w4 = __ldg(pp + 4);
+        P.temperature = __uint_as_float(w0.x);
+        P.top_k = w0.y;
+        P.top_p = __uint_as_float(w1.x);
+        P.min_p = __uint_as_float(w1.y);
+        P.presence_penalty = __uint_as_float(w2.x);
+        P.frequency_penalty = __uint_as_float(w2.y);
+        P.repetition_penalty = __uint_as_float(w3.x);
+        P.reserved = w3.y;
+        P.seed = (uint64_t)w4.x | ((uint64_t)w4.y << 32);
+    }
     // With one slice per row, where the logits are does not depend on the
     // row's parameters: the first three rounds are asked for before the
     // parameters have arrived (into the stages pass 1 reads them from).
@@ -1524,36 +2125,20 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         }
     }
     // ---- forced rows and parameters (uniform per block, before any barrier)
-    if (a.forced_ids) {
-        const int32_t forced = a.forced_ids[row];
-        if (forced >= 0) {
-            if (slice == 0 && tid == 0) {
-                a.out_ids[out_row] = (uint32_t)forced;
-                if (a.out_status) {
-                    a.out_status[out_row] = LILY_ROW_FORCED;
-                }
-                if (a.kept_n) {
-                    a.kept_n[out_row] = 0;
-                }
+    if (forced >= 0) {
+        if (slice == 0 && tid == 0) {
+            a.out_ids[out_row] = (uint32_t)forced;
+            if (a.out_status) {
+                a.out_status[out_row] = LILY_ROW_FORCED;
             }
-            if (early) {
-                cp_async_wait<0>();
+            if (a.kept_n) {
+                a.kept_n[out_row] = 0;
             }
-            return;
         }
-    }
-    lily_sampling_params_t P;
-    if (a.force_greedy) {
-        P.temperature = 0.0f;
-        P.top_k = 1;
-        P.top_p = 1.0f;
-        P.min_p = 0.0f;
-        P.presence_penalty = 0.0f;
-        P.frequency_penalty = 0.0f;
-        P.repetition_penalty = 1.0f;
-        P.seed = 0;
-    } else {
-        P = a.params[row];
+        if (early) {
+            cp_async_wait<0>();
+        }
+        return;
     }
     {
         // src/kernels/sample.rs:57-79, for parameters the host never saw.
@@ -1580,6 +2165,28 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         }
     }
 
+    // A list length is a device value: one beyond what the handle was made for,
+    // or beyond the row pitch, would walk into the next row or past the buffer.
+    // (A pitch of 0 means one list shared by every row.)
+    if (hist_len_row > a.max_history || (a.history_ld != 0u && hist_len_row > a.history_ld) ||
+        bias_len_row > a.max_list || (a.bias_ld != 0u && bias_len_row > a.bias_ld) ||
+        ban_len_row > a.max_list || (a.ban_ld != 0u && ban_len_row > a.ban_ld)) {
+        if (slice == 0 && tid == 0) {
+            a.out_ids[out_row] = 0xFFFFFFFFu;
+            if (a.out_status) {
+                a.out_status[out_row] = LILY_ROW_LIST;
+            }
+            if (a.kept_n) {
+                a.kept_n[out_row] = 0;
+            }
+            atomicOr(a.status_word, 1u << LILY_ROW_LIST);
+        }
+        if (early) {
+            cp_async_wait<0>();
+        }
+        return;
+    }
+
     RowCtx c;
     const bool greedy = P.temperature <= 0.0f || P.top_k == 1u;
     c.use_pen = P.presence_penalty != 0.0f || P.frequency_penalty != 0.0f ||
@@ -1594,8 +2201,8 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     c.frequency = P.frequency_penalty;
     c.top_p = P.top_p;
     c.min_p = P.min_p;
-    c.bias_len = (a.bias_ids && a.bias_len) ? a.bias_len[row] : 0u;
-    c.ban_len = (a.ban_ids && a.ban_len) ? a.ban_len[row] : 0u;
+    c.bias_len = bias_len_row;
+    c.ban_len = ban_len_row;
     c.bias_ids = a.bias_ids ? a.bias_ids + (uint64_t)row * a.bias_ld : nullptr;
     c.bias_vals = a.bias_vals ? a.bias_vals + (uint64_t)row * a.bias_ld : nullptr;
     c.ban_ids = a.ban_ids ? a.ban_ids + (uint64_t)row * a.ban_ld : nullptr;
@@ -1624,7 +2231,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     c.hi = min(a.vocab, c.lo + slice_len);
     c.seen = seen;
     const bool table_mode = a.count_slots != nullptr;
-    const uint32_t slot = table_mode ? a.count_slots[row] : 0u;
+    const uint32_t slot = table_mode ? slot_row : 0u;
     uint32_t *counts_rw = nullptr;
     if (c.need_counts) {
         counts_rw = table_mode ? a.counts_table + (uint64_t)slot * a.vocab
@@ -1691,6 +2298,14 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     const bool lean_wide = c.k > 128u;
     const bool lean_cand = (!c.use_pen || c.monotone) && nrounds > 0u &&
                            (!lean_wide || (VEC && nfull >= 3u && c.k <= 3u * NT));
+    // Rows that keep few candidates and have no bias / ban list stream once
+    // and take their threshold on the way (lean_stream): the threshold after
+    // about half the rounds, and after the rounds that mark the history (two
+    // 16-byte loads of ids per thread and round; what does not fit is marked
+    // before the stream starts).
+    constexpr uint32_t STREAM_MIN_ROUNDS = 8;
+    const bool stream_route = VEC && early && lean_cand && !lean_wide && !c.has_special &&
+                              nfull >= STREAM_MIN_ROUNDS;
     constexpr int P1_STAGES = 4;
     static_assert(STAGES == 2 && CAP * 4u == NT * FRAG_BYTES, "pass 1 stages 2 and 3 are key[] and id[]");
     const uint32_t p1_slot[P1_STAGES] = {
@@ -1725,9 +2340,10 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     part.v[0] = make_uint4(0, 0, 0, 0);
     part.v[1] = make_uint4(0, 0, 0, 0);
     const uint32_t part_base = c.lo + nfull * ROUND + tid * GROUP;
-    const uint32_t part_valid = (lean_cand && nrounds > nfull && part_base < c.hi)
-                                    ? min(GROUP, c.hi - part_base)
-                                    : 0u;
+    const uint32_t part_have = (lean_cand && nrounds > nfull && part_base < c.hi)
+                                   ? min(GROUP, c.hi - part_base)
+                                   : 0u;
+    const uint32_t part_valid = stream_route ? 0u : part_have;  // (lean_stream takes the partial round through the ring)
     if (part_valid != 0u) {
         load_frag_scalar<T>(part, row_ptr, part_base, c.hi);
     }
@@ -1750,8 +2366,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // The first part of a plain history list is marked inside pass 1, one
     // 16-byte load per thread and round, hidden behind the logits' latency.
     const bool hist_vec = (reinterpret_cast<uintptr_t>(hist) & 15u) == 0u;
+    const uint32_t stream_mark_cap = (nfull / 2u) * 2u * (uint32_t)NT;  // 16-byte words marked on the way
     const uint32_t fused4 = (VEC && lean_cand && hist_vec && !c.need_counts && hist_len > 0u)
-                                ? min(hist_len / 4u, nfull * (uint32_t)NT)
+                                ? min(hist_len / 4u, stream_route ? stream_mark_cap : nfull * (uint32_t)NT)
                                 : 0u;
     if (tid == 0) {
         sm->ctx = c;
@@ -1764,15 +2381,14 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         sm->th_base = 0;
         sm->th_new = 0;
         sm->overflow = 0;
+        sm->ckey = stream_route ? sm->lkey : sm->key;
+        sm->cid = stream_route ? sm->lid : sm->id;
+        sm->ccap = stream_route ? LCAP : CAP;
+        sm->u_draw = a.uniforms ? u_row : uniform_for(P.seed, step_row);
+        sm->lean_abort = 0;
 #ifdef LILY_DEBUG
         sm->dbg_hits = sm->dbg_hit_warps = sm->dbg_tighten = 0;
 #endif
-    }
-    if (tid < BLOOM_WORDS) {
-        sm->bloom[tid] = 0;
-    }
-    for (uint32_t b = tid; b < TH_BINS; b += NT) {
-        sm->thist[b] = 0;
     }
     if (c.use_pen) {
         if (table_mode) {
@@ -1780,7 +2396,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
             for (uint32_t w = tid; w < slice_words; w += NT) {
                 seen[w] = src[w];
             }
-        } else {
+        } else if (!whole_row_seen) {
             for (uint32_t w = tid; w < slice_words; w += NT) {
                 seen[w] = 0;
             }
@@ -1883,9 +2499,44 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // looked at closely. Pass 2 (after the lists, below) streams the slice
     // again, from L2 this time, against that fixed threshold.
     bool lean = lean_cand;
+    bool streamed = false;                 // lean_stream ran: the candidates are in the buffer already
     float full_best = neg_inf();           // pass 1's result over the full rounds, for pass 2
     uint32_t full_best_r = 0xFFFFFFFFu;
-    if (lean) {
+    if (lean && stream_route) {
+        if (tid == 0) {
+            sm->stream.nfull = nfull;
+            sm->stream.has_part = nrounds > nfull ? 1u : 0u;
+            sm->stream.r_check = max((fused4 + 2u * NT - 1u) / (2u * NT), nfull / 2u);
+            sm->stream.k = c.k;
+            sm->stream.lo = c.lo;
+            sm->stream.hi = c.hi;
+        }
+        __syncthreads();
+        const uint32_t res = lean_stream<T>(sm, &sm->stream, p1_slot[0], p1_slot[2], my_src,
+                                            reinterpret_cast<const uint4 *>(hist), fused4,
+                                            (uint32_t)__cvta_generic_to_shared(seen),
+                                            a.phase_clocks ? a.phase_clocks + ((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES : nullptr);
+        LILY_STAMP(PH_PASS1);
+        // A NaN anywhere (or a wait that gave up): the general path, from the start.
+        streamed = !__syncthreads_or(res != 0u);
+        LILY_STAMP(PH_PASS1_MET);
+        if (!streamed) {
+            lean = false;
+            if (tid == 0) {
+                sm->n = 0;
+                sm->n_adj = 0;
+                sm->overflow = 0;
+                sm->ckey = sm->key;
+                sm->cid = sm->id;
+                sm->ccap = CAP;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int st = 0; st < STAGES - 1; ++st) {
+                issue((uint32_t)st);
+            }
+        }
+    } else if (lean) {
         constexpr uint32_t NONE = 0xFFFFFFFFu;
         float best = neg_inf();
         uint32_t best_r = NONE;
@@ -2177,25 +2828,13 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 
     // ---- C'. pass 2 of the two-pass route: the fixed threshold, no meetings
     if (lean) {
-        const uint32_t n_lists = min(sm->n, CAP);  // what the lists pushed
+        const uint32_t n_lists = streamed ? 0u : min(sm->n, CAP);  // what the lists pushed
         const float c_fix = sm->c_raw;
-        {
+        if (!streamed) {
             uint32_t base = c.lo + tid * GROUP;
             if (VEC) {
-                const uint32_t took =
-                    lean_pass2<T>(sm, my_src, nfull, base, c_fix, p1_slot[1], lean_tab, full_best, full_best_r);
+                (void)lean_pass2<T>(sm, my_src, nfull, base, c_fix, p1_slot[1], lean_tab, full_best, full_best_r);
                 base += nfull * ROUND;
-                if (a.phase_clocks != nullptr) {
-                    // The trace's two spare words: threads that read a second or third
-                    // fragment again, threads that walked all their rounds.
-                    const int again = __syncthreads_count((took & 3u) != 0u);
-                    const int walked = __syncthreads_count((took & 4u) != 0u);
-                    if (tid == 0) {
-                        long long *w = a.phase_clocks + ((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES;
-                        w[PH_SPARE0] = again;
-                        w[PH_SPARE1] = walked;
-                    }
-                }
             } else {
                 for (uint32_t r = 0; r < nfull; ++r) {
                     Frag cur;
@@ -2218,6 +2857,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 sm->n = n_lists;
                 sm->n_adj = n_lists;
                 sm->overflow = 0;
+                sm->ckey = sm->key;
+                sm->cid = sm->id;
+                sm->ccap = CAP;
             }
             lean = false;
 #pragma unroll
@@ -2566,7 +3208,11 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
                 sort_candidates<true>(sm, n);
             }
             LILY_STAMP(PH_SORT);
-            finalize<true>(sm, a, row, n, P.seed);
+            if (row < a.spec.n_spec) {
+                finalize<true>(sm, a, row, n, P.seed);
+            } else {
+                finalize_warp(sm, a, row, n, P.seed);
+            }
             LILY_STAMP(PH_END);
         }
     } else {
@@ -2612,6 +3258,10 @@ __global__ void __launch_bounds__(NT, 2) merge_rows_kernel(const __grid_constant
         sm->ctx = c;
         sm->n = 0;
         sm->err = 0;
+        sm->u_draw = a.uniforms ? a.uniforms[row] : uniform_for(P.seed, a.steps ? a.steps[row] : 0u);
+        sm->ckey = sm->key;
+        sm->cid = sm->id;
+        sm->ccap = CAP;
     }
     __syncthreads();
     const uint32_t slots = a.merge_shards * LILY_SHARD_CANDIDATES;
@@ -2671,7 +3321,7 @@ __global__ void __launch_bounds__(NT, 2) merge_rows_kernel(const __grid_constant
             if (!sorted) {
                 sort_candidates<true>(sm, n);
             }
-            finalize<true>(sm, a, row, n, P.seed);
+            finalize_warp(sm, a, row, n, P.seed);
         }
     } else {
         if (!sorted) {

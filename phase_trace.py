@@ -1,25 +1,30 @@
-"""Per-block phase times of one sampler launch, from the SM clock stamps the
+"""Per-block phase times of one sampler launch, from the time stamps the
 kernel leaves with LILY_FLAG_PHASE_CLOCKS (the counterpart of the reference's
 LILY_KERNEL_PROFILE, src/metal.rs:140-198).
 
-    python -m lily_b200.phase_trace b4 [step ...]     # the 4-row server batch
-    python -m lily_b200.phase_trace b256              # the 256-row batch (summary)
+    python phase_trace.py b4 [step ...]     # the 4-row server batch
+    python phase_trace.py b256              # the 256-row batch (summary)
 
-Stamps of different blocks come from different SMs' clocks: only differences
-inside one block mean anything. Times assume the 1965 MHz maximum SM clock.
+Stamps are nanoseconds of the GPU's global timer, so stamps of different
+blocks of a launch can be compared with each other.
 """
 from __future__ import annotations
 
+import os
 import sys
 
 import numpy as np
 
-MHZ = 1965.0
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
 NAMES = ["start", "bitmaps", "lists", "pass 2 / stream", "adjust + select", "merge", "sort", "end",
          "first threshold", "pass 1", "pass 1 met", "maxima", "search", "threshold set",
-         "threads reading again", "threads walking"]
+         "threshold taken", "collected", "entry"]
+ENTRY = 16
 # The order in which a block of the two-pass route reaches its stamps.
-ORDER = [0, 1, 9, 10, 11, 12, 13, 8, 2, 3, 4, 5, 6, 7]
+ORDER = [16, 0, 1, 14, 15, 9, 10, 11, 12, 13, 8, 2, 3, 4, 5, 6, 7]
 
 
 def _device_batch(torch, lily, x):
@@ -52,10 +57,10 @@ def trace(torch, lily, scratch, x, launches: int = 3):
 
 def segments(stamps):
     """[(phase name, microseconds since the previous stamp)] of one block."""
-    out, prev = [], float(stamps[0])
+    out, prev = [], float(stamps[ORDER[0]])
     for i in ORDER[1:]:
         if stamps[i] != 0:
-            out.append((NAMES[i], (float(stamps[i]) - prev) / MHZ))
+            out.append((NAMES[i], (float(stamps[i]) - prev) / 1e3))
             prev = float(stamps[i])
     return out
 
@@ -64,7 +69,7 @@ def main(argv) -> None:
     import torch
 
     import lily_b200 as lily
-    import lily_b200.workloads as w
+    import workloads as w
 
     which = argv[1] if len(argv) > 1 else "b4"
     if which == "b4":
@@ -73,31 +78,38 @@ def main(argv) -> None:
         for step in steps:
             x = w.config2_step(step)
             clk = trace(torch, lily, scratch, x)
+            t0 = clk[:, :, ENTRY][clk[:, :, ENTRY] != 0].min()
             print(f"step {step}: (T, top_k, top_p) per row",
                   [(p.get("temperature"), p.get("top_k"), p.get("top_p")) for p in x.params])
             for r in range(clk.shape[0]):
                 for sl in range(clk.shape[1]):
                     c = clk[r, sl]
-                    if c[0] == 0:
+                    if c[ENTRY] == 0:
                         continue
-                    total = f"{(c[7] - c[0]) / MHZ:6.1f} us" if c[7] != 0 else "   (not the row's last block)"
-                    print(f"  row {r} block {sl}: {total} | " +
-                          " ".join(f"{n} {us:.1f}" for n, us in segments(c)) +
-                          f" | read again {int(c[14])}, walked {int(c[15])}")
+                    last = max(int(v) for v in c)
+                    print(f"  row {r} block {sl}: enters {(c[ENTRY] - t0) / 1e3:5.1f}, leaves "
+                          f"{(last - t0) / 1e3:5.1f} us after the launch's first block | " +
+                          " ".join(f"{n} {us:.1f}" for n, us in segments(c)))
     else:
         scratch = lily.SamplerScratch(w.VOCAB, max_rows=256, phase_clocks=True)
         clk = trace(torch, lily, scratch, w.config4_batch(), launches=4)
-        live = clk[clk[:, :, 0] != 0].astype(np.float64)
+        live = clk[clk[:, :, ENTRY] != 0].astype(np.float64)
+        t0 = live[:, ENTRY].min()
         print("blocks", len(live))
-        prev = 0
+        print(f"  block entry after the first block's: mean {(live[:, ENTRY] - t0).mean() / 1e3:6.2f} us"
+              f"  max {(live[:, ENTRY] - t0).max() / 1e3:6.2f}")
+        prev = ENTRY
         for i in ORDER[1:]:
             ok = (live[:, i] != 0) & (live[:, prev] != 0)
             if ok.any():
-                d = (live[ok, i] - live[ok, prev]) / MHZ
-                print(f"  {NAMES[i]:18s} mean {d.mean():6.2f} us  max {d.max():6.2f}")
+                d = (live[ok, i] - live[ok, prev]) / 1e3
+                at = (live[ok, i] - t0) / 1e3
+                print(f"  {NAMES[i]:18s} mean {d.mean():6.2f} us  max {d.max():6.2f}   reached at "
+                      f"{at.mean():6.2f} (mean) {at.max():6.2f} (last block)")
                 prev = i
-        tot = (live[:, 7] - live[:, 0]) / MHZ
-        print(f"  block total mean {tot.mean():.1f} us, max {tot.max():.1f}")
+        tot = (live[:, 7] - live[:, ENTRY]) / 1e3
+        print(f"  block lifetime mean {tot.mean():.1f} us, max {tot.max():.1f}; "
+              f"last block ends {(live[:, 7].max() - t0) / 1e3:.1f} us after the first block enters")
     scratch.close()
 
 

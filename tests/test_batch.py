@@ -106,7 +106,7 @@ def test_draw_step(bt):
 @pytest.mark.gpu
 def test_counts_follow_a_request_between_engine_and_batch_slot(cuda, lily, bt):
     torch = cuda
-    import lily_b200.workloads as W
+    import workloads as W
     from gpu_util import run_batch
 
     v = 4096

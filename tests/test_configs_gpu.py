@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def W(lily):
-    import lily_b200.workloads as w
+    import workloads as w
     return w
 
 

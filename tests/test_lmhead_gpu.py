@@ -23,7 +23,7 @@ def _bf16(torch, bits):
 
 
 def _to_bf16_bits(x):
-    import lily_b200.workloads as wl
+    import workloads as wl
 
     return wl.to_bf16_bits(np.asarray(x, dtype=np.float32))
 
@@ -125,7 +125,7 @@ def _check_against_oracle(lf, plist, uniforms, got):
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_sharded_draw_equals_the_whole_row_draw(cuda, lily, n_shards, dtype):
     torch = cuda
-    import lily_b200.workloads as wl
+    import workloads as wl
 
     rows, vocab = 12, 65_536
     rng = np.random.default_rng([73, n_shards])
@@ -184,7 +184,7 @@ def test_head_then_sharded_draw_small(cuda, lily, n_shards):
     """The fused call of each shard (head into the handle's logits, then the
     records), merged; the oracle draws from the logits the GPU head produced."""
     torch = cuda
-    import lily_b200.workloads as wl
+    import workloads as wl
 
     cfg = wl.config5(tokens=64, hidden=1024, vocab=16_384, seed=77)
     rows, vocab = 64, 16_384
@@ -223,7 +223,7 @@ def test_config5_full_size(cuda, lily):
     GPU. The head is checked on three bands of rows against the oracle; the
     sharded draw against the oracle's draw from the GPU's own logits."""
     torch = cuda
-    import lily_b200.workloads as wl
+    import workloads as wl
 
     cfg = wl.config5()
     rows, vocab, n_shards = 64, 262_144, 8

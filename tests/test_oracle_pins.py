@@ -218,7 +218,7 @@ def test_bias_ban_order():
 
 def test_lmhead_matches_float64():
     rng = np.random.default_rng(1)
-    import lily_b200.workloads as w
+    import workloads as w
     cfg = w.config5(tokens=3, hidden=256, vocab=64, group=64, seed=9)
     got = oracle.lmhead_int8(cfg.hidden, cfg.weight, cfg.scales, 64, 0, 64)
     h = w.bf16_bits_to_f32(cfg.hidden).astype(np.float64)

@@ -54,7 +54,7 @@ def make_batch(w, rng, rows, vocab, k, bf16, *, temperature=0.8, top_p=0.9, min_
 
 @pytest.fixture(scope="module")
 def W(lily):
-    import lily_b200.workloads as w
+    import workloads as w
     return w
 
 

@@ -36,7 +36,7 @@ def _worker(rank, world, port, rows, vocab, out):
 
     import lily_b200  # noqa: F401
     import lily_b200.shard as sh
-    import lily_b200.workloads as w
+    import workloads as w
     import oracle
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -63,7 +63,7 @@ def _worker(rank, world, port, rows, vocab, out):
 def test_two_ranks_draw_the_same_tokens_as_one(lily, tmp_path):
     import torch.multiprocessing as mp
 
-    import lily_b200.workloads as w
+    import workloads as w
     import oracle
 
     rows, vocab = 7, 4099
@@ -110,7 +110,7 @@ def _vocab_worker(rank, world, port, rows, vocab, out):
 
     import lily_b200  # noqa: F401
     import lily_b200.shard as sh
-    import lily_b200.workloads as w
+    import workloads as w
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -135,7 +135,7 @@ def test_vocab_shards_gather_records_that_hold_the_global_top_k(lily, tmp_path):
     import torch.multiprocessing as mp
 
     import lily_b200.shard as sh
-    import lily_b200.workloads as w
+    import workloads as w
 
     rows, vocab, world = 3, 8192, 2
     with socket.socket() as s:

@@ -39,7 +39,7 @@ def run_noalloc(torch, lily, vocab, batch):
 
 
 def test_the_allocation_free_draw_equals_the_regular_one_call_after_call(cuda, lily):
-    import lily_b200.workloads as w
+    import workloads as w
 
     vocab = 151_936
     scratch = lily.SamplerScratch(vocab, max_rows=8, max_list=64)
@@ -62,7 +62,7 @@ def test_the_allocation_free_draw_equals_the_regular_one_call_after_call(cuda, l
 
 
 def test_the_allocation_free_draw_refuses_what_it_has_no_room_for(cuda, lily):
-    import lily_b200.workloads as w
+    import workloads as w
 
     vocab = 32_768
     batch = w.config2_step(0, vocab=vocab, rows=4, history=256)  # frequency penalty 0.2 + history
