@@ -15,6 +15,7 @@
 #include "../../include/lily_batch.h"
 #include "../../include/lily_sampler.h"
 #include "sample_kernel.cuh"
+#include "stream_kernel.cuh"
 #include "lmhead_kernel.cuh"
 
 namespace {
@@ -163,21 +164,14 @@ size_t smem_bytes(uint32_t vocab, uint32_t n_slices) {
     return sizeof(lily::SmemFixed) + lily::RING_BYTES + words * sizeof(uint32_t);
 }
 
-template <typename T, bool VEC>
-int32_t launch_one(lily_sampler *h, cudaStream_t stream, const lily::KArgs &a, uint32_t rows,
-                   size_t smem) {
-    auto kernel = lily::sample_rows_kernel<T, VEC>;
-    const uint32_t bit = 1u << ((sizeof(T) == 4 ? 0 : 2) + (VEC ? 1 : 0));
-    if (!(h->attr_mask & bit)) {
-        CU(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   h->max_smem));
-        h->attr_mask |= bit;
-    }
-    // Programmatic stream serialisation: the grid may be set up and its blocks may
-    // start while the stream's previous kernel drains; the kernel waits
-    // (griddepcontrol.wait) before it reads or writes any global memory.
+// Programmatic stream serialisation: the grid may be set up and its blocks may
+// start while the stream's previous kernel drains; the kernels wait
+// (griddepcontrol.wait) before they read or write any global memory.
+template <typename Kernel>
+int32_t launch_serialised(lily_sampler *h, cudaStream_t stream, Kernel kernel, dim3 grid, size_t smem,
+                          const lily::KArgs &a) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.n_slices, rows, 1);
+    cfg.gridDim = grid;
     cfg.blockDim = dim3(lily::NT, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -188,6 +182,41 @@ int32_t launch_one(lily_sampler *h, cudaStream_t stream, const lily::KArgs &a, u
     cfg.numAttrs = 1;
     CU(h, cudaLaunchKernelEx(&cfg, kernel, a));
     return LILY_OK;
+}
+
+template <typename Kernel>
+int32_t raise_smem_limit(lily_sampler *h, Kernel kernel, uint32_t bit) {
+    if (!(h->attr_mask & bit)) {
+        CU(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->max_smem));
+        h->attr_mask |= bit;
+    }
+    return LILY_OK;
+}
+
+template <typename T, bool VEC>
+int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, uint32_t rows,
+                   size_t smem) {
+    // A launch with a block slot's worth of rows or more, aligned logits, long
+    // rows and nothing special about the call goes to the large-batch kernel
+    // (which runs the general code itself for the rows it does not take).
+    constexpr uint32_t round = lily::Geo<T>::ROUND;
+    const bool stream = VEC && a.n_slices == 1u && a.vocab / round >= lily::STREAM_MIN_ROUNDS &&
+                        a.cand_out == nullptr && a.merge_in == nullptr && a.spec.n_spec == 0u &&
+                        a.extra_len == 0u;
+    if (stream) {
+        auto kernel = lily::stream_rows_kernel<T>;
+        const int32_t st = raise_smem_limit(h, kernel, 1u << (sizeof(T) == 4 ? 4 : 5));
+        if (st != LILY_OK) {
+            return st;
+        }
+        return launch_serialised(h, stream_, kernel, dim3(rows, 1, 1), smem, a);
+    }
+    auto kernel = lily::sample_rows_kernel<T, VEC>;
+    const int32_t st = raise_smem_limit(h, kernel, 1u << ((sizeof(T) == 4 ? 0 : 2) + (VEC ? 1 : 0)));
+    if (st != LILY_OK) {
+        return st;
+    }
+    return launch_serialised(h, stream_, kernel, dim3(a.n_slices, rows, 1), smem, a);
 }
 
 int32_t launch(lily_sampler *h, cudaStream_t stream, const lily::KArgs &a, uint32_t rows,

@@ -54,7 +54,7 @@ constexpr uint32_t H0_SHIFT = 19;       // first-round histogram: raw key >> 19,
 constexpr uint32_t H0_BINS = 1u << (32 - H0_SHIFT);
 constexpr uint32_t TH_BINS = 1024;      // tightening histogram: raw key >> 16 above a base
 constexpr uint32_t RANKSORT_MAX = 384;  // candidate counts up to this are rank-sorted
-constexpr uint32_t LCAP = 1024;         // candidates of a row that streams with the full ring (see lean_stream)
+constexpr uint32_t LCAP = 1024;         // candidates of a row in stream_rows_kernel, whose ring borrows key and id
 
 // Per logit type: 16 bf16 or 8 f32 per thread per round.
 template <typename T>
@@ -160,16 +160,6 @@ struct RowCtx {
     bool sp_in_smem;
 };
 
-// What lean_stream needs beyond its register arguments; read when the
-// threshold is taken or a fragment has to be read again, not in the rounds.
-struct StreamShared {
-    uint32_t nfull;       // full rounds (rounds 0..2 are already on their way)
-    uint32_t has_part;    // whether a partial round follows them
-    uint32_t r_check;     // the round after which the threshold is taken
-    uint32_t k;
-    uint32_t lo, hi;      // the slice's ids
-};
-
 struct alignas(16) SmemFixed {
     uint32_t key[CAP];    // candidates: adjusted keys below n_adj, raw logit bits above;
     uint32_t id[CAP];     //   during the first round key+id hold the 8192-bin histogram
@@ -206,11 +196,10 @@ struct alignas(16) SmemFixed {
     uint32_t *cid;
     uint32_t ccap;
     float u_draw;         // the row's uniform, fetched (or derived) when the block starts
-    uint32_t lean_abort;  // lean_stream: a thread saw a NaN before the threshold was taken
-    alignas(8) unsigned long long mbar[2];  // lean_stream: history marked; thread maxima written
+    uint32_t lean_abort;  // stream_rows_kernel: a thread saw a NaN before the threshold was taken
+    alignas(8) unsigned long long mbar[2];  // stream_rows_kernel: history marked; thread maxima written
     uint32_t lkey[LCAP];
     uint32_t lid[LCAP];
-    StreamShared stream;
 #ifdef LILY_DEBUG
     uint32_t dbg_hits, dbg_hit_warps, dbg_tighten;
 #endif
@@ -1646,406 +1635,15 @@ enum { PH_START = 0, PH_BITMAPS, PH_LISTS, PH_STREAM, PH_LOCAL_SELECT, PH_MERGE,
         }                                                                                  \
     } while (0)
 
-// ---- One pass with the threshold taken on the way (rows that keep few
-// candidates, aligned logits, no bias / ban list).
-//
-// The row streams through the four-stage ring exactly once. Up to round
-// `r_check` a thread only tracks maxima, as lean_pass1 does. At `r_check`
-// every thread adjusts its largest logit so far and leaves the key in shared
-// memory; warp 0 alone takes the k-th largest of those 512 keys (keys of 512
-// different ids: a lower bound of the row's k-th largest adjusted value),
-// turns it into the raw-space bound and publishes it, while the other warps
-// keep streaming. A thread that sees the bound collects what its rounds so
-// far hold above it (its best fragment is still in registers; a second or
-// third fragment is read again) and from then on tests every new fragment
-// against the bound directly. Nobody waits at a block barrier inside the
-// stream, so DRAM stays busy, and when the last round has landed the
-// candidates are already in the buffer.
-//
-// History ids are marked in the seen bitmap inside the first rounds (two
-// 16-byte loads per thread and round); an mbarrier tells the threads that take
-// the threshold that every mark is in place.
-
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count) {
-    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(at), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
-    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
-    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}" ::"r"(at) : "memory");
-}
-
-// Waits for the barrier's first phase, at most about a millisecond; false if
-// it gave up (a bug elsewhere: the caller leaves the two-pass route).
-__device__ __forceinline__ bool mbar_wait_first(unsigned long long *bar) {
-    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
-    for (uint32_t i = 0; i < (1u << 16); ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
-            : "=r"(done)
-            : "r"(at)
-            : "memory");
-        if (done) {
-            return true;
-        }
-    }
-    return false;
-}
-
-// The threshold of lean_stream. Every warp sorts its 32 thread keys and
-// leaves its best POOL_PER_WARP in a pool of 128: keys of 128 different ids,
-// whose k-th largest (k <= 128) is a lower bound of the row's k-th largest
-// adjusted value, and equals the k-th largest of all 512 keys unless one warp
-// holds more than eight of the best k.
-constexpr uint32_t POOL_PER_WARP = 8;
-constexpr uint32_t POOL = POOL_PER_WARP * (NT / 32);
-static_assert(POOL == 128, "four pool keys per lane");
-
-__device__ __forceinline__ uint32_t warp_sort_desc(uint32_t v) {
-    const uint32_t lane = threadIdx.x & 31u;
-#pragma unroll
-    for (uint32_t size = 2u; size <= 32u; size <<= 1) {
-#pragma unroll
-        for (uint32_t stride = size >> 1; stride > 0u; stride >>= 1) {
-            const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, v, stride);
-            const bool first = ((lane & size) == 0u) == ((lane & stride) == 0u);
-            v = first ? max(v, other) : min(v, other);
-        }
-    }
-    return v;  // lane 0 holds the largest
-}
-
-// Any full warp: the largest v with its low 16 bits clear that at least k of
-// the pool's keys reach, bit by bit from the top.
-__device__ __forceinline__ uint32_t pool_kth(const uint32_t *pool, uint32_t k) {
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t v0 = pool[lane], v1 = pool[lane + 32u], v2 = pool[lane + 64u], v3 = pool[lane + 96u];
-    uint32_t kth = 0u;
-#pragma unroll 1
-    for (int bit = 31; bit >= 16; --bit) {
-        const uint32_t cand = kth | (1u << bit);
-        const uint32_t cnt = (v0 >= cand ? 1u : 0u) + (v1 >= cand ? 1u : 0u) + (v2 >= cand ? 1u : 0u) +
-                             (v3 >= cand ? 1u : 0u);
-        if (__reduce_add_sync(0xFFFFFFFFu, cnt) >= k) {
-            kth = cand;
-        }
-    }
-    return kth;
-}
-
-// Whether the barrier's first phase is over (does not wait).
-__device__ __forceinline__ bool mbar_test_first(unsigned long long *bar) {
-    const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
-    uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(done)
-                 : "r"(at)
-                 : "memory");
-    return done != 0u;
-}
-
-// Elements of a fragment from `nvalid` on become -inf (the row's last,
-// partial round: cp.async filled them with zeros).
-template <typename T>
-__device__ __forceinline__ void frag_mask_tail(Frag &f, uint32_t nvalid) {
-    uint32_t *w = reinterpret_cast<uint32_t *>(&f);
-    if (sizeof(T) == 4) {
-#pragma unroll
-        for (uint32_t e = 0; e < 8u; ++e) {
-            if (e >= nvalid) {
-                w[e] = 0xFF800000u;
-            }
-        }
-    } else {
-#pragma unroll
-        for (uint32_t e = 0; e < 8u; ++e) {
-            const uint32_t lo = 2u * e < nvalid ? (w[e] & 0xFFFFu) : 0xFF80u;
-            const uint32_t hi = 2u * e + 1u < nvalid ? (w[e] & 0xFFFF0000u) : 0xFF800000u;
-            w[e] = lo | hi;
-        }
-    }
-}
-
-template <typename T>
-__device__ __noinline__ uint32_t lean_stream(SmemFixed *sm, const StreamShared *gs, uint32_t slot_a,
-                                             uint32_t slot_b, const char *src0, const uint4 *h4, uint32_t n4,
-                                             uint32_t seen_at, long long *stamps) {
-    constexpr uint32_t NONE = 0xFFFFFFFFu;
-    constexpr uint32_t GROUP = Geo<T>::GROUP, ROUND = Geo<T>::ROUND;
-    const uint32_t tid = threadIdx.x;
-    const uint32_t nfull = gs->nfull;
-    const uint32_t nproc = nfull + gs->has_part;
-    const uint32_t r_check = gs->r_check;
-    const uint32_t mark_rounds = (n4 + 2u * NT - 1u) / (2u * NT);  // <= r_check < nfull
-
-    float best = neg_inf(), m2 = neg_inf(), m3 = neg_inf(), m4 = neg_inf();
-    uint32_t best_r = NONE, r2 = NONE, r3 = NONE;
-    Frag keep;
-    keep.v[0] = make_uint4(0, 0, 0, 0);
-    keep.v[1] = make_uint4(0, 0, 0, 0);
-    uint32_t saw_nan = 0u;
-
-    // The thread's logits in the partial round (0 if it has none).
-    auto part_valid = [&]() -> uint32_t {
-        const uint32_t at = gs->lo + nfull * ROUND + tid * GROUP;
-        return (gs->has_part && at < gs->hi) ? min(GROUP, gs->hi - at) : 0u;
-    };
-    const char *src = src0 + 3u * ROUND_BYTES;  // the round three ahead of the one being read
-    // Starts the copy of round rr + 3 (into the stage round rr - 1 has left) and
-    // waits for round rr.
-    auto advance = [&](uint32_t rr) {
-        if (rr + 3u < nproc) {
-            const uint32_t st = (rr + 3u) & 3u;
-            const uint32_t dst = ((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES;
-            if (rr + 3u < nfull) {
-                lean_copy_round(dst, src);
-            } else {
-                const uint32_t bytes = part_valid() * (uint32_t)sizeof(T);
-                const uint32_t b0 = min(bytes, 16u), b1 = bytes > 16u ? bytes - 16u : 0u;
-                // (A source of zero bytes is never read; it still has to be an address.)
-                const char *base = src - (size_t)(rr + 3u) * ROUND_BYTES;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst),
-                             "l"(b0 ? src : base), "r"(b0)
-                             : "memory");
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst + 16u),
-                             "l"(b1 ? src + 16 : base), "r"(b1)
-                             : "memory");
-            }
-        }
-        cp_async_commit();
-        src += ROUND_BYTES;
-        cp_async_wait<3>();
-    };
-    auto read_round = [&](uint32_t rr, Frag &cur) -> bool {
-        const uint32_t st = rr & 3u;
-        lean_read_slot(((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES, cur);
-        if (rr == nfull) {
-            const uint32_t pv = part_valid();
-            frag_mask_tail<T>(cur, pv);
-            return pv != 0u;
-        }
-        return true;
-    };
-    auto track = [&](const Frag &cur, uint32_t rr) {
-        const float m = frag_max<T>(cur);
-        saw_nan |= m != m ? 1u : 0u;
-        // The three best fragments by maximum (rounds best_r, r2, r3) and the
-        // largest maximum among all the others (m4).
-        if (best_r == NONE || m > best) {
-            m4 = fmaxf(m4, m3);
-            m3 = m2;
-            r3 = r2;
-            m2 = best;
-            r2 = best_r;
-            best = m;
-            best_r = rr;
-            keep = cur;
-        } else if (r2 == NONE || m > m2) {
-            m4 = fmaxf(m4, m3);
-            m3 = m2;
-            r3 = r2;
-            m2 = m;
-            r2 = rr;
-        } else if (r3 == NONE || m > m3) {
-            m4 = fmaxf(m4, m3);
-            m3 = m;
-            r3 = rr;
-        } else {
-            m4 = fmaxf(m4, m);
-        }
-    };
-
-    uint32_t rr = 0;
-    // ---- rounds that also mark history ids (two 16-byte loads ahead)
-    if (mark_rounds != 0u) {
-        const uint4 no_ids = make_uint4(NONE, NONE, NONE, NONE);
-        const uint32_t lo = gs->lo, width = gs->hi - gs->lo;
-        uint32_t hnext = tid;
-        uint4 hq0 = hnext < n4 ? __ldg(h4 + hnext) : no_ids;
-        uint4 hq1 = hnext + NT < n4 ? __ldg(h4 + hnext + NT) : no_ids;
-        hnext += 2u * NT;
-        for (; rr < mark_rounds; ++rr) {
-            advance(rr);
-            {
-                const uint32_t ids[8] = {hq0.x, hq0.y, hq0.z, hq0.w, hq1.x, hq1.y, hq1.z, hq1.w};
-                hq0 = hnext < n4 ? __ldg(h4 + hnext) : no_ids;
-                hq1 = hnext + NT < n4 ? __ldg(h4 + hnext + NT) : no_ids;
-                hnext += 2u * NT;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t off = ids[i] - lo;
-                    if (off < width) {
-                        asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(seen_at + (off >> 5) * 4u),
-                                     "r"(1u << (off & 31u))
-                                     : "memory");
-                    }
-                }
-            }
-            Frag cur;
-            read_round(rr, cur);  // (a full round: mark_rounds < nfull)
-            track(cur, rr);
-        }
-    }
-    mbar_arrive(&sm->mbar[0]);  // this thread's history marks are in place
-    // ---- rounds up to the one after which the threshold is taken
-    for (; rr <= r_check; ++rr) {
-        advance(rr);
-        Frag cur;
-        read_round(rr, cur);
-        track(cur, rr);
-    }
-    {
-        // The threshold, this warp's share: every thread adjusts its largest logit
-        // so far; the warp's best eight keys go to the pool.
-        bool ok = mbar_wait_first(&sm->mbar[0]);
-        uint32_t key = 0u;
-        if (!ok || saw_nan != 0u || best_r == NONE) {
-            sm->lean_abort = 1u;
-        } else {
-            uint32_t at = 0;
-#pragma unroll
-            for (int e = (int)GROUP - 1; e >= 0; --e) {
-                if (frag_get<T>(keep, e) == best) {
-                    at = (uint32_t)e;
-                }
-            }
-            key = adjusted_key(sm, gs->lo + best_r * ROUND + tid * GROUP + at, best, false);
-        }
-        __syncwarp();
-        key = warp_sort_desc(key);
-        uint32_t *pool = sm->thist;  // POOL words
-        if ((tid & 31u) < POOL_PER_WARP) {
-            pool[(tid >> 5) * POOL_PER_WARP + (tid & 31u)] = key;
-        }
-        __syncwarp();
-        if ((tid & 31u) == 0u) {
-            mbar_arrive(&sm->mbar[1]);
-        }
-    }
-    // ---- rounds until every warp's keys are in the pool
-    bool pooled = __all_sync(0xFFFFFFFFu, mbar_test_first(&sm->mbar[1]));
-    for (; rr < nproc && !pooled; ++rr) {
-        advance(rr);
-        Frag cur;
-        if (read_round(rr, cur)) {
-            track(cur, rr);
-        }
-        pooled = __all_sync(0xFFFFFFFFu, mbar_test_first(&sm->mbar[1]));
-    }
-    if (!pooled) {
-        // The stream ended first (every warp passes the round above on its own).
-        cp_async_wait<0>();
-        pooled = mbar_wait_first(&sm->mbar[1]);
-    }
-    pooled = __all_sync(0xFFFFFFFFu, pooled);
-    if (!pooled || *reinterpret_cast<volatile uint32_t *>(&sm->lean_abort) != 0u) {
-        cp_async_wait<0>();
-        return saw_nan | 2u;
-    }
-    // Every warp takes the bound for itself (the same pool, the same result).
-    const uint32_t kth = pool_kth(sm->thist, gs->k);
-    const uint32_t kstar = kth > 0u ? kth - 1u : 0u;  // ties with the k-th value must still pass
-    const float c_fix = raw_threshold(kstar, sm->ctx.T, sm->ctx.argmax_mode);
-    if (tid == 0) {
-        raise_threshold(sm, c_fix, kstar);  // for the selection after the stream
-        if (stamps) {
-            stamps[PH_SPARE0] = global_ns();
-        }
-    }
-
-    {
-        // What the rounds [0, rr) of this thread hold above the bound: its best
-        // fragment is still in registers; a second or third is read again (L2 by
-        // now; the partial round ends anywhere, so it comes element by element).
-        const uint32_t base0 = gs->lo + tid * GROUP;
-        const char *first = src - (size_t)(rr + 3u) * ROUND_BYTES;  // the thread's 32 bytes of round 0
-        const uint32_t pv = part_valid();
-        auto valid_of = [&](uint32_t r) -> uint32_t { return r < nfull ? 0xFFFFFFFFu : (1u << pv) - 1u; };
-        auto reread = [&](uint32_t r, Frag &f) {
-            if (r < nfull) {
-                const uint4 *p = reinterpret_cast<const uint4 *>(first + (size_t)r * ROUND_BYTES);
-                f.v[0] = __ldcg(p);
-                f.v[1] = __ldcg(p + 1);
-            } else {
-                f.v[0] = make_uint4(0, 0, 0, 0);
-                f.v[1] = make_uint4(0, 0, 0, 0);
-                const T *p = reinterpret_cast<const T *>(first + (size_t)r * ROUND_BYTES);
-                uint32_t *w = reinterpret_cast<uint32_t *>(&f);
-                for (uint32_t e = 0; e < pv; ++e) {
-                    if (sizeof(T) == 4) {
-                        w[e] = __float_as_uint(widen(p[e]));
-                    } else {
-                        const uint32_t b = reinterpret_cast<const uint16_t *>(p)[e];
-                        w[e >> 1] |= (e & 1u) ? (b << 16) : b;
-                    }
-                }
-                frag_mask_tail<T>(f, pv);
-            }
-        };
-        if (best_r != NONE && !(best <= c_fix)) {
-            lean_take<T>(sm, keep, base0 + best_r * ROUND, valid_of(best_r), c_fix);
-        }
-        const bool second = r2 != NONE && !(m2 <= c_fix);
-        const bool third = r3 != NONE && !(m3 <= c_fix);
-        Frag f2, f3;
-        if (second) {
-            reread(r2, f2);
-        }
-        if (third) {
-            reread(r3, f3);
-        }
-        if (second) {
-            lean_take<T>(sm, f2, base0 + r2 * ROUND, valid_of(r2), c_fix);
-        }
-        if (third) {
-            lean_take<T>(sm, f3, base0 + r3 * ROUND, valid_of(r3), c_fix);
-        }
-        if (!(m4 <= c_fix)) {
-            // Very rare: a fourth fragment of this thread may matter.
-            for (uint32_t r = 0; r < rr; ++r) {
-                if (r == best_r || r == r2 || r == r3) {
-                    continue;
-                }
-                Frag f;
-                reread(r, f);
-                if (!(frag_max<T>(f) <= c_fix)) {
-                    lean_take<T>(sm, f, base0 + r * ROUND, valid_of(r), c_fix);
-                }
-            }
-        }
-    }
-    if (stamps && tid == 0) {
-        stamps[PH_SPARE1] = global_ns();
-    }
-    // ---- the remaining rounds: every fragment straight against the bound
-    for (; rr < nproc; ++rr) {
-        advance(rr);
-        Frag cur;
-        if (read_round(rr, cur)) {
-            const float m = frag_max<T>(cur);
-            saw_nan |= m != m ? 1u : 0u;
-            if (!(m <= c_fix)) {
-                const uint32_t valid = rr < nfull ? 0xFFFFFFFFu : (1u << part_valid()) - 1u;
-                lean_take<T>(sm, cur, gs->lo + rr * ROUND + tid * GROUP, valid, c_fix);
-            }
-        }
-    }
-    cp_async_wait<0>();
-    return saw_nan;
-}
-
+// One slice (thread block) of one row. `row` indexes every per-row array.
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constant__ KArgs a) {
+__device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, const uint32_t slice) {
     extern __shared__ uint4 smem_raw[];
     SmemFixed *sm = reinterpret_cast<SmemFixed *>(smem_raw);
     uint4 *ring = reinterpret_cast<uint4 *>(sm + 1);
     uint32_t *seen = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(ring) + RING_BYTES);
 
     const uint32_t tid = threadIdx.x;
-    const uint32_t row = a.row0 + blockIdx.y;  // every per-row array is indexed by this
-    const uint32_t slice = blockIdx.x;
     const uint32_t out_row = row;
     LILY_STAMP(PH_ENTRY);
 
@@ -2066,10 +1664,6 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         for (uint32_t w = tid; w < words; w += NT) {
             seen[w] = 0;
         }
-    }
-    if (tid == 0) {
-        mbar_init(&sm->mbar[0], NT);
-        mbar_init(&sm->mbar[1], NT / 32);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -2298,14 +1892,6 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     const bool lean_wide = c.k > 128u;
     const bool lean_cand = (!c.use_pen || c.monotone) && nrounds > 0u &&
                            (!lean_wide || (VEC && nfull >= 3u && c.k <= 3u * NT));
-    // Rows that keep few candidates and have no bias / ban list stream once
-    // and take their threshold on the way (lean_stream): the threshold after
-    // about half the rounds, and after the rounds that mark the history (two
-    // 16-byte loads of ids per thread and round; what does not fit is marked
-    // before the stream starts).
-    constexpr uint32_t STREAM_MIN_ROUNDS = 8;
-    const bool stream_route = VEC && early && lean_cand && !lean_wide && !c.has_special &&
-                              nfull >= STREAM_MIN_ROUNDS;
     constexpr int P1_STAGES = 4;
     static_assert(STAGES == 2 && CAP * 4u == NT * FRAG_BYTES, "pass 1 stages 2 and 3 are key[] and id[]");
     const uint32_t p1_slot[P1_STAGES] = {
@@ -2340,10 +1926,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     part.v[0] = make_uint4(0, 0, 0, 0);
     part.v[1] = make_uint4(0, 0, 0, 0);
     const uint32_t part_base = c.lo + nfull * ROUND + tid * GROUP;
-    const uint32_t part_have = (lean_cand && nrounds > nfull && part_base < c.hi)
-                                   ? min(GROUP, c.hi - part_base)
-                                   : 0u;
-    const uint32_t part_valid = stream_route ? 0u : part_have;  // (lean_stream takes the partial round through the ring)
+    const uint32_t part_valid = (lean_cand && nrounds > nfull && part_base < c.hi)
+                                    ? min(GROUP, c.hi - part_base)
+                                    : 0u;
     if (part_valid != 0u) {
         load_frag_scalar<T>(part, row_ptr, part_base, c.hi);
     }
@@ -2366,9 +1951,8 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // The first part of a plain history list is marked inside pass 1, one
     // 16-byte load per thread and round, hidden behind the logits' latency.
     const bool hist_vec = (reinterpret_cast<uintptr_t>(hist) & 15u) == 0u;
-    const uint32_t stream_mark_cap = (nfull / 2u) * 2u * (uint32_t)NT;  // 16-byte words marked on the way
     const uint32_t fused4 = (VEC && lean_cand && hist_vec && !c.need_counts && hist_len > 0u)
-                                ? min(hist_len / 4u, stream_route ? stream_mark_cap : nfull * (uint32_t)NT)
+                                ? min(hist_len / 4u, nfull * (uint32_t)NT)
                                 : 0u;
     if (tid == 0) {
         sm->ctx = c;
@@ -2381,9 +1965,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         sm->th_base = 0;
         sm->th_new = 0;
         sm->overflow = 0;
-        sm->ckey = stream_route ? sm->lkey : sm->key;
-        sm->cid = stream_route ? sm->lid : sm->id;
-        sm->ccap = stream_route ? LCAP : CAP;
+        sm->ckey = sm->key;
+        sm->cid = sm->id;
+        sm->ccap = CAP;
         sm->u_draw = a.uniforms ? u_row : uniform_for(P.seed, step_row);
         sm->lean_abort = 0;
 #ifdef LILY_DEBUG
@@ -2499,44 +2083,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
     // looked at closely. Pass 2 (after the lists, below) streams the slice
     // again, from L2 this time, against that fixed threshold.
     bool lean = lean_cand;
-    bool streamed = false;                 // lean_stream ran: the candidates are in the buffer already
     float full_best = neg_inf();           // pass 1's result over the full rounds, for pass 2
     uint32_t full_best_r = 0xFFFFFFFFu;
-    if (lean && stream_route) {
-        if (tid == 0) {
-            sm->stream.nfull = nfull;
-            sm->stream.has_part = nrounds > nfull ? 1u : 0u;
-            sm->stream.r_check = max((fused4 + 2u * NT - 1u) / (2u * NT), nfull / 2u);
-            sm->stream.k = c.k;
-            sm->stream.lo = c.lo;
-            sm->stream.hi = c.hi;
-        }
-        __syncthreads();
-        const uint32_t res = lean_stream<T>(sm, &sm->stream, p1_slot[0], p1_slot[2], my_src,
-                                            reinterpret_cast<const uint4 *>(hist), fused4,
-                                            (uint32_t)__cvta_generic_to_shared(seen),
-                                            a.phase_clocks ? a.phase_clocks + ((uint64_t)row * MAX_SLICES + blockIdx.x) * LILY_PHASES : nullptr);
-        LILY_STAMP(PH_PASS1);
-        // A NaN anywhere (or a wait that gave up): the general path, from the start.
-        streamed = !__syncthreads_or(res != 0u);
-        LILY_STAMP(PH_PASS1_MET);
-        if (!streamed) {
-            lean = false;
-            if (tid == 0) {
-                sm->n = 0;
-                sm->n_adj = 0;
-                sm->overflow = 0;
-                sm->ckey = sm->key;
-                sm->cid = sm->id;
-                sm->ccap = CAP;
-            }
-            __syncthreads();
-#pragma unroll
-            for (int st = 0; st < STAGES - 1; ++st) {
-                issue((uint32_t)st);
-            }
-        }
-    } else if (lean) {
+    if (lean) {
         constexpr uint32_t NONE = 0xFFFFFFFFu;
         float best = neg_inf();
         uint32_t best_r = NONE;
@@ -2828,9 +2377,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
 
     // ---- C'. pass 2 of the two-pass route: the fixed threshold, no meetings
     if (lean) {
-        const uint32_t n_lists = streamed ? 0u : min(sm->n, CAP);  // what the lists pushed
+        const uint32_t n_lists = min(sm->n, CAP);  // what the lists pushed
         const float c_fix = sm->c_raw;
-        if (!streamed) {
+        {
             uint32_t base = c.lo + tid * GROUP;
             if (VEC) {
                 (void)lean_pass2<T>(sm, my_src, nfull, base, c_fix, p1_slot[1], lean_tab, full_best, full_best_r);
@@ -3223,6 +2772,19 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constan
         finalize<false>(sm, a, row, n, P.seed);
         LILY_STAMP(PH_END);
     }
+}
+
+// Grid (slices, rows): block (x, y) takes slice x of row row0 + y.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(NT, 2) sample_rows_kernel(const __grid_constant__ KArgs a) {
+    sample_row<T, VEC>(a, a.row0 + blockIdx.y, blockIdx.x);
+}
+
+// The whole row in one block, out of line: what stream_rows_kernel calls for a
+// row it does not take itself.
+template <typename T>
+__device__ __noinline__ void sample_whole_row(const KArgs &a, uint32_t row) {
+    sample_row<T, true>(a, row, 0u);
 }
 
 // The draw of a vocabulary-sharded row: the shards' records hold every

@@ -104,8 +104,10 @@ def main(argv) -> None:
             if ok.any():
                 d = (live[ok, i] - live[ok, prev]) / 1e3
                 at = (live[ok, i] - t0) / 1e3
+                q = np.percentile(at, [10, 50, 90])
                 print(f"  {NAMES[i]:18s} mean {d.mean():6.2f} us  max {d.max():6.2f}   reached at "
-                      f"{at.mean():6.2f} (mean) {at.max():6.2f} (last block)")
+                      f"{at.mean():6.2f} (mean), p10 / p50 / p90 {q[0]:.2f} / {q[1]:.2f} / {q[2]:.2f}, "
+                      f"{at.max():6.2f} (last block)")
                 prev = i
         tot = (live[:, 7] - live[:, ENTRY]) / 1e3
         print(f"  block lifetime mean {tot.mean():.1f} us, max {tot.max():.1f}; "
