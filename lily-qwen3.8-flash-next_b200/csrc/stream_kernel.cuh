@@ -34,6 +34,10 @@ namespace lily {
 
 constexpr uint32_t STREAM_MIN_ROUNDS = 8;  // launches with shorter rows use sample_rows_kernel
 constexpr uint32_t STREAM_K_MAX = 64;      // finalize_warp holds two candidates per lane
+// Rounds of the ring in flight beyond the one being read. Two measured faster
+// than three (33.4 against 34.0 us per 256-row launch), and asking L2 for further
+// rounds ahead of the ring slower still: the stream is not short of requests.
+constexpr uint32_t AHEAD = 2;
 
 __device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count) {
     const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
@@ -238,8 +242,7 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     cp_async_commit();
     lean_copy_round(slot_a + ROUND_BYTES, src0 + ROUND_BYTES);
     cp_async_commit();
-    lean_copy_round(slot_b, src0 + 2u * ROUND_BYTES);
-    cp_async_commit();
+    static_assert(AHEAD == 2u, "rounds 0 and 1 are on their way when the stream starts");
 
     auto refuse = [&](uint32_t status) {
         if (tid == 0) {
@@ -374,14 +377,14 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     keep.v[0] = make_uint4(0, 0, 0, 0);
     keep.v[1] = make_uint4(0, 0, 0, 0);
     uint32_t saw_nan = 0u;
-    const char *src = src0 + 3u * ROUND_BYTES;  // the round three ahead of the one being read
-    // Starts the copy of round rr + 3 (into the stage round rr - 1 has left) and
-    // waits for round rr.
+    const char *src = src0 + AHEAD * ROUND_BYTES;  // the round AHEAD ahead of the one being read
+    // Starts the copy of round rr + AHEAD (into a stage whose round has been read)
+    // and waits for round rr.
     auto advance = [&](uint32_t rr) {
-        if (rr + 3u < nproc) {
-            const uint32_t st = (rr + 3u) & 3u;
+        if (rr + AHEAD < nproc) {
+            const uint32_t st = (rr + AHEAD) & 3u;
             const uint32_t dst = ((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES;
-            if (rr + 3u < nfull) {
+            if (rr + AHEAD < nfull) {
                 lean_copy_round(dst, src);
             } else {
                 const uint32_t bytes = part_valid * (uint32_t)sizeof(T);
@@ -397,7 +400,7 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
         }
         cp_async_commit();
         src += ROUND_BYTES;
-        cp_async_wait<3>();
+        cp_async_wait<AHEAD>();
     };
     auto read_round = [&](uint32_t rr, Frag &cur) -> bool {
         const uint32_t st = rr & 3u;
