@@ -6,8 +6,10 @@
 Workload: the large-batch configuration, B=256 rows of bf16 logits at
 V=151,936 with 32,768-id histories per row (top-k 50, top-p 0.9, min-p 0.05,
 T 0.8, repetition 1.1). A step is one pass of the sampler over one batch.
-With N GPUs every rank draws its own 256-row batch per step (rows are
-independent: no collective), so `value` is N x 256 rows per step time.
+With N GPUs the 256 rows are split evenly: rank r draws rows
+[r * 256 / N, (r + 1) * 256 / N) of every batch (rows are independent: no
+collective), so `value` is 256 rows per step time and the scaling is strong.
+`weak_scaling` has the other figure: every rank drawing 256 rows of its own.
 
 `value`   rows/s with inputs resident in HBM (CUDA events around K steps).
 `e2e`     the same through the C ABI with HOST buffers: pinned host logits,
@@ -40,6 +42,16 @@ HISTORY = 32_768
 NB = 4  # distinct resident batches rotated through, 445 MB in all (> the 126 MB L2)
 METRIC = "sampled rows/s at B=256,V=151,936"
 UNIT = "rows/s"
+
+
+def workload_config(world: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    alg_bytes = ROWS * (151_936 * 2 + HISTORY * 4)
+    return {"workload": "large-batch B=256 V=151936 bf16 history=32768 "
+                        "(top-k 50, top-p 0.9, min-p 0.05, T 0.8, repetition 1.1)",
+            "rows_per_gpu": ROWS // world, "global_rows": ROWS, "vocab": 151_936, "history": HISTORY,
+            "logits_dtype": "bf16", "parallelism": f"rows x{world}, no collective",
+            "l2": f"{NB} resident batches rotated ({NB * alg_bytes / 1e6:.0f} MB > 126 MB L2)"}
 
 
 def peaks():
@@ -114,33 +126,45 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_rows_per_s(batch, threads: int, min_seconds: float, mode: int = 1):
-    """Times the CPU oracle over the rows of `batch` on `threads` host threads
-    (ctypes releases the GIL), repeating the batch until min_seconds passed."""
-    from concurrent.futures import ThreadPoolExecutor
+class CpuSampler:
+    """The CPU oracle over the rows of one batch on `threads` host threads
+    (ctypes releases the GIL). The thread pool, the parameter structs and the
+    widened logits are made once: a timed pass is only the sampler."""
 
-    import oracle
+    def __init__(self, batch, threads: int, mode: int = 1):
+        from concurrent.futures import ThreadPoolExecutor
 
-    lf_bits = batch.logits
-    params = [oracle.params(**p) for p in batch.params]
+        import oracle
 
-    def one(r):
-        logits = oracle.widen_bf16(lf_bits[r])
-        d = oracle.sample(logits, params[r], float(batch.uniforms[r]),
-                          history=batch.history[r, :batch.history_len[r]], mode=mode)
-        return d.token
+        self.oracle = oracle
+        self.batch = batch
+        self.mode = mode
+        self.rows = batch.logits.shape[0]
+        self.logits = [oracle.widen_bf16(batch.logits[r]) for r in range(self.rows)]
+        self.params = [oracle.params(**p) for p in batch.params]
+        self.pool = ThreadPoolExecutor(max_workers=threads)
 
-    rows = lf_bits.shape[0]
-    done = 0
-    t0 = time.perf_counter()
-    with ThreadPoolExecutor(max_workers=threads) as pool:
+    def _one(self, r):
+        b = self.batch
+        return self.oracle.sample(self.logits[r], self.params[r], float(b.uniforms[r]),
+                                  history=b.history[r, :b.history_len[r]], mode=self.mode).token
+
+    def one_pass(self):
+        return list(self.pool.map(self._one, range(self.rows)))
+
+    def rows_per_s(self, min_seconds: float):
+        done = 0
+        t0 = time.perf_counter()
         while True:
-            list(pool.map(one, range(rows)))
-            done += rows
+            self.one_pass()
+            done += self.rows
             if time.perf_counter() - t0 >= min_seconds:
                 break
-    dt = time.perf_counter() - t0
-    return done / dt, done, dt
+        dt = time.perf_counter() - t0
+        return done / dt, done, dt
+
+    def close(self):
+        self.pool.shutdown()
 
 
 def run_reference(args):
@@ -154,22 +178,23 @@ def run_reference(args):
     oracle.build()
     cores = os.cpu_count() or 1
     batch = w.config4_batch(rows=ROWS, history=HISTORY)
+    cpu = CpuSampler(batch, cores)
     # One step = one 256-row batch through the CPU sampler.
     times = []
     for i in range(args.warmup + args.steps):
         t0 = time.perf_counter()
-        cpu_rows_per_s(batch, cores, 0.0)
+        cpu.one_pass()
         if i >= args.warmup:
             times.append(time.perf_counter() - t0)
+    cpu.close()
     total = sum(times)
     value = ROWS * len(times) / total
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic (seeded numpy; shapes and distributions of the large-batch configuration)",
-        "config": {"workload": "large-batch B=256 V=151936 bf16 history=32768", "rows": ROWS,
-                   "vocab": w.VOCAB, "history": HISTORY},
+        "config": workload_config(max(1, args.gpus)),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{len(times)} steps of one 256-row batch, partial-selection "
                                    "variant of the CPU sampler (identical outputs to the full sort)"},
@@ -215,10 +240,15 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     vocab = w.VOCAB
-    # Seeded host batches (pinned: the end-to-end leg copies from them).
+    import lily_b200.shard as sh
+
+    rows_here = sh.row_range(ROWS, world, rank)       # this rank's rows of every 256-row batch
+    lo, hi_row = rows_here.start, rows_here.stop
+    n_here = hi_row - lo
+    # Seeded host batches, the same on every rank (pinned: the end-to-end leg copies from them).
     host = []
     for b in range(NB):
-        batch = w.config4_batch(rows=ROWS, history=HISTORY, seed=4004 + 97 * rank, step=b)
+        batch = w.config4_batch(rows=ROWS, history=HISTORY, seed=4004, step=b)
         lg = torch.from_numpy(batch.logits.view(np.int16)).pin_memory()
         hi = torch.from_numpy(batch.history.view(np.int32)).pin_memory()
         un = torch.from_numpy(batch.uniforms).pin_memory()
@@ -234,75 +264,93 @@ def main():
 
     # The argument block of each resident batch is built once: the timed loop
     # is then one C-ABI call per step, so that the host keeps ahead of the GPU.
-    prepared = [scratch.prepare_sample_batch(lg, d_params, out, uniforms=un, history_ids=hi,
-                                             history_len=hist_len, params_on_device=True)
+    def prepare(first, last):
+        return [scratch.prepare_sample_batch(lg[first:last], d_params[40 * first:40 * last], out[first:last],
+                                             uniforms=un[first:last], history_ids=hi[first:last],
+                                             history_len=hist_len[first:last], params_on_device=True)
                 for lg, hi, un in resident]
 
-    def step_resident(i):
-        scratch.sample_prepared(prepared[i % NB], stream=stream)
+    split = prepare(lo, hi_row)                        # the 256 rows split over the ranks
+    whole = prepare(0, ROWS) if world > 1 else split   # every rank its own 256 rows
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def timed(prepared, steps):
+        """Exactly `steps` steps between two events, nothing else in the stream (an
+        event between two launches would keep a launch from being set up while
+        the one before it drains). Max over ranks."""
+        e_first, e_last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e_first.record(stream)
+        for i in range(steps):
+            scratch.sample_prepared(prepared[i % NB], stream=stream)
+        e_last.record(stream)
+        barrier()
+        return max_over_ranks(e_first.elapsed_time(e_last))
+
     # ---- device-resident throughput -------------------------------------
     for i in range(args.warmup):
-        step_resident(i)
+        scratch.sample_prepared(split[i % NB], stream=stream)
     barrier()
     clocks = ClockSampler(local)
     clocks.start()
     time.sleep(0.3)
-    # The timed region: exactly K steps between two events, nothing else in the
-    # stream (an event between two launches would keep a launch from being set
-    # up while the one before it drains).
-    e_first, e_last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e_first.record(stream)
-    for i in range(args.steps):
-        step_resident(i)
-    e_last.record(stream)
-    barrier()
-    total_ms = e_first.elapsed_time(e_last)
+    total_ms = timed(split, args.steps)
     # The same steps once more with an event after every launch: the spread of
     # single launches (each then pays its own start-up).
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     ev[0].record(stream)
     for i in range(args.steps):
-        step_resident(i)
+        scratch.sample_prepared(split[i % NB], stream=stream)
         ev[i + 1].record(stream)
     barrier()
     per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    weak = None
+    if world > 1:
+        for i in range(3):
+            scratch.sample_prepared(whole[i % NB], stream=stream)
+        weak_ms = timed(whole, args.steps)
+        weak = {"value": world * ROWS * args.steps / (weak_ms * 1e-3), "unit": UNIT,
+                "us_per_step": weak_ms * 1e3 / args.steps, "rows_per_gpu": ROWS,
+                "scaling": "weak: every rank draws 256 rows of its own per step"}
     # Keep the GPU busy a little longer so that nvidia-smi sees it under load.
     t_end = time.time() + 1.0
     i = 0
     while time.time() < t_end:
-        step_resident(i)
+        scratch.sample_prepared(split[i % NB], stream=stream)
         i += 1
     torch.cuda.synchronize()
     clock_info = clocks.stop()
-    if world > 1:
-        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
-    value = world * ROWS * args.steps / (total_ms * 1e-3)
+    value = ROWS * args.steps / (total_ms * 1e-3)
     assert scratch.status(stream) == lily.OK
 
     # ---- end to end through the C ABI with host buffers ------------------
-    d_lg = torch.empty_like(resident[0][0])
-    d_hi = torch.empty_like(resident[0][1])
-    d_un = torch.empty_like(resident[0][2])
-    h_out = torch.zeros(ROWS, dtype=torch.int32).pin_memory()
+    # Every rank copies in its own rows of the step's batch and copies its ids out.
+    d_lg = torch.empty_like(resident[0][0][lo:hi_row])
+    d_hi = torch.empty_like(resident[0][1][lo:hi_row])
+    d_un = torch.empty_like(resident[0][2][lo:hi_row])
+    h_out = torch.zeros(n_here, dtype=torch.int32).pin_memory()
+    params_here = params[lo:hi_row]
 
     def step_e2e(i):
         _, lg, hi, un = host[i % NB]
-        d_lg.view(torch.int16).copy_(lg, non_blocking=True)
-        d_hi.copy_(hi, non_blocking=True)
-        d_un.copy_(un, non_blocking=True)
-        scratch.sample_batch(d_lg, params, out, uniforms=d_un, history_ids=d_hi,
-                             history_len=hist_len, stream=stream)
-        h_out.copy_(out, non_blocking=True)
+        d_lg.view(torch.int16).copy_(lg[lo:hi_row], non_blocking=True)
+        d_hi.copy_(hi[lo:hi_row], non_blocking=True)
+        d_un.copy_(un[lo:hi_row], non_blocking=True)
+        scratch.sample_batch(d_lg, params_here, out[lo:hi_row], uniforms=d_un, history_ids=d_hi,
+                             history_len=hist_len[lo:hi_row], stream=stream)
+        h_out.copy_(out[lo:hi_row], non_blocking=True)
 
     e2e_steps = max(10, min(args.steps, 50))
     for i in range(3):
@@ -314,12 +362,9 @@ def main():
         step_e2e(i)
     e1.record(stream)
     barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = world * ROWS * e2e_steps / (e2e_ms * 1e-3)
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    e2e_value = ROWS * e2e_steps / (e2e_ms * 1e-3)
+    h2d_rank = n_here * vocab * 2 + n_here * HISTORY * 4 + n_here * 4 + n_here * 40
     h2d = ROWS * vocab * 2 + ROWS * HISTORY * 4 + ROWS * 4 + ROWS * 40
     d2h = ROWS * 4
     check = host[(e2e_steps - 1) % NB][0]
@@ -327,24 +372,33 @@ def main():
     # ---- p50 latency of the 4-row server batch ----------------------------
     b4 = None
     if rank == 0 and args.b4_steps > 0:
+        cs = ClockSampler(local)
+        cs.start()
         b4 = b4_latency(torch, lily, w, dev, stream, args.b4_steps)
+        b4["clocks"] = cs.stop()
 
     # ---- vocab-sharded 8-bit LM head + sampling (every rank takes part) -----
     lm = None
     if args.lmhead_steps > 0:
+        cs = ClockSampler(local)
+        cs.start()
         lm = lmhead_sharded(torch, dist, lily, dev, stream, world, rank, args.lmhead_steps)
+        lm["clocks"] = cs.stop()
 
     # ---- roofline ----------------------------------------------------------
-    alg_bytes = ROWS * (vocab * 2 + HISTORY * 4)
+    # Algorithmic bytes of one launch on this GPU: its rows' logits and history, read once.
+    alg_bytes = n_here * (vocab * 2 + HISTORY * 4)
     kernel_ms = total_ms / args.steps  # average launch duration over the timed region (one launch per step)
     peak, peak_kind = peaks()
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    kernel_name = ("stream_rows_kernel<bf16> (one block per row)" if n_here > 148
+                   else "sample_rows_kernel<bf16, vec> (rows cut into slices)")
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": ncu_traffic(), "peak_kind": peak_kind,
-                "kernel": "sample_rows_kernel<bf16, vec>", "kernel_ms": kernel_ms,
+                "frac": achieved / peak, "traffic": ncu_traffic() if world == 1 else None,
+                "peak_kind": peak_kind, "kernel": kernel_name, "kernel_ms": kernel_ms,
                 "single_launch_ms_mean": statistics.mean(per_launch_ms),
                 "single_launch_ms_p50": statistics.median(per_launch_ms),
-                "algorithmic_bytes_per_launch": alg_bytes}
+                "algorithmic_bytes_per_launch": alg_bytes, "rows_per_launch": n_here}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -352,7 +406,9 @@ def main():
 
         oracle.build()
         cores = os.cpu_count() or 1
-        v, done, dt = cpu_rows_per_s(host[0][0], cores, args.cpu_seconds)
+        sampler = CpuSampler(host[0][0], cores)
+        v, done, dt = sampler.rows_per_s(args.cpu_seconds)
+        sampler.close()
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": f"{done} rows (the 256-row batch repeated for {dt:.1f} s), "
                          "partial-selection variant of the CPU sampler"}
@@ -367,17 +423,17 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic (seeded numpy; shapes and distributions of the large-batch configuration)",
-            "config": {"workload": "large-batch B=256 V=151936 bf16 history=32768 "
-                                   "(top-k 50, top-p 0.9, min-p 0.05, T 0.8, repetition 1.1)",
-                       "rows_per_gpu": ROWS, "global_rows": ROWS * world, "vocab": vocab,
-                       "history": HISTORY, "parallelism": f"rows x{world}, no collective",
-                       "l2": f"{NB} resident batches rotated ({NB * alg_bytes / 1e6:.0f} MB > 126 MB L2)"},
+            "config": workload_config(world),
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": args.steps, "clocks": clock_info, "latency_b4": b4,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps,
+                    "h2d_bytes_per_step_per_gpu": h2d_rank,
+                    "h2d_gbs_per_gpu": h2d_rank / (e2e_ms / e2e_steps * 1e-3) / 1e9,
+                    "note": "bound by the host-to-device copy of the step's logits and histories "
+                            "(all GPUs of the box copy through the same host)"},
+            "gpu_launches": args.steps, "clocks": clock_info, "weak_scaling": weak, "latency_b4": b4,
             "lmhead_sharded": lm,
             "us_per_step": ms_per_step * 1e3,
         }

@@ -89,14 +89,21 @@ def sharded_lmhead_draw(scratch, weights, scales, hidden, params, out_ids, first
     all-gather of the records, the merged draw (lily_merge_draw). Every rank
     ends with the same token ids in `out_ids`. `scratch` was created with
     lmhead=True for this rank's shard size."""
+    import contextlib
+
     import torch
 
     rows = hidden.shape[0]
     if records is None:
         records = torch.empty((rows, RECORD_BYTES), dtype=torch.uint8, device=hidden.device)
-    scratch.lmhead_shard_candidates(weights, scales, hidden, params, records, first_id=first_id,
-                                    want_sums=want_sums, stream=stream)
-    gathered = gather_records(records, group=group)
-    scratch.merge_draw(gathered, params, out_ids, uniforms=uniforms, steps=steps, out_lse=out_lse,
-                       stream=stream, **kept)
+    # The collective is ordered against torch's CURRENT stream only: a stream
+    # that is given is made current for the whole step, so that the records are
+    # written before the all-gather reads them and gathered before the merge.
+    current = torch.cuda.stream(stream) if (stream is not None and hidden.is_cuda) else contextlib.nullcontext()
+    with current:
+        scratch.lmhead_shard_candidates(weights, scales, hidden, params, records, first_id=first_id,
+                                        want_sums=want_sums, stream=stream)
+        gathered = gather_records(records, group=group)
+        scratch.merge_draw(gathered, params, out_ids, uniforms=uniforms, steps=steps, out_lse=out_lse,
+                           stream=stream, **kept)
     return gathered

@@ -263,6 +263,33 @@ def lmhead_int8(hidden_bf16, w, scales_bf16, group: int, n_begin: int, n_end: in
     return out
 
 
+def lmhead_int8_all(hidden_bf16, w, scales_bf16, group: int, threads: int | None = None) -> np.ndarray:
+    """lmhead_int8 over every row of the head, bands of rows on `threads` host
+    threads (the C call releases the GIL); the sums of a logit do not depend on
+    the band it falls in."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    hidden_bf16 = np.ascontiguousarray(hidden_bf16, dtype=np.uint16)
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    scales_bf16 = np.ascontiguousarray(scales_bf16, dtype=np.uint16)
+    tokens, hidden = hidden_bf16.shape
+    rows = w.shape[0]
+    out = np.zeros((tokens, rows), dtype=np.float32)
+    threads = threads or os.cpu_count() or 1
+    band = max(256, -(-rows // (threads * 8)))
+    f = lib().lo_lmhead_int8
+
+    def one(lo):
+        f(hidden_bf16.ctypes.data_as(C.POINTER(C.c_uint16)), tokens, hidden,
+          w.ctypes.data_as(C.POINTER(C.c_int8)), scales_bf16.ctypes.data_as(C.POINTER(C.c_uint16)),
+          group, lo, min(rows, lo + band), _ptr(out, _f32p), out.shape[1])
+
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        list(pool.map(one, range(0, rows, band)))
+    return out
+
+
 def dequant_affine(codes, scales, biases, rows: int, cols: int, group: int, bits: int) -> np.ndarray:
     """tests/support/cpu_ref.rs:402-430: MLX affine codes -> f32 [rows, cols]."""
     codes = np.ascontiguousarray(codes, dtype=np.uint32)

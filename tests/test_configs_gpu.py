@@ -42,23 +42,39 @@ def test_config2_server_batch(cuda, lily, W):
     s.close()
 
 
-def test_config3_speculative_verification(cuda, lily, W):
+def test_config3_speculative_verification_10000_steps(cuda, lily, W):
+    # The configuration's full length: 10 000 seeded steps in each acceptance
+    # mode. Host threads make a step's inputs and run the CPU oracle on them
+    # (numpy and the oracle both release the GIL); this thread runs the GPU.
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    steps = 10_000
     s = lily.SamplerScratch(W.VOCAB, max_rows=3)
     hist = {False: np.zeros(3, dtype=np.int64), True: np.zeros(3, dtype=np.int64)}
-    for greedy in (False, True):
-        for step in range(40, 240):
-            c = W.config3_step(step, greedy=greedy)
-            st, want, want_acc = oracle.spec_verify(c.target_f32(), oracle.params(**c.params),
-                                                    c.draft_ids, c.u_accept, c.u_resid, q_dense=c.q)
-            assert st == 0
-            got, acc, status = gpu_verify(cuda, lily, s, c.target, c.params, c.draft_ids, c.u_accept,
-                                          c.u_resid, q_dense=c.q,
-                                          mode=lily.SPEC_GREEDY_MATCH if greedy else lily.SPEC_REJECTION)
-            assert np.array_equal(got, want), f"config3 greedy={greedy} step {step}"
-            assert acc == want_acc and not status.any()
-            hist[greedy][acc] += 1
-    print("config 3 accepted-draft histogram, rejection sampling:", hist[False].tolist(),
-          "greedy match:", hist[True].tolist())
+
+    def host_side(args):
+        step, greedy = args
+        c = W.config3_step(step, greedy=greedy)
+        st, want, want_acc = oracle.spec_verify(c.target_f32(), oracle.params(**c.params),
+                                                c.draft_ids, c.u_accept, c.u_resid, q_dense=c.q)
+        return step, greedy, c, st, want, want_acc
+
+    work = [(step, greedy) for greedy in (False, True) for step in range(steps)]
+    with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        chunk = 256  # bounds the inputs held in memory (2 MB a step)
+        for at in range(0, len(work), chunk):
+            for step, greedy, c, st, want, want_acc in pool.map(host_side, work[at:at + chunk]):
+                assert st == 0
+                got, acc, status = gpu_verify(cuda, lily, s, c.target, c.params, c.draft_ids, c.u_accept,
+                                              c.u_resid, q_dense=c.q,
+                                              mode=lily.SPEC_GREEDY_MATCH if greedy else lily.SPEC_REJECTION)
+                assert np.array_equal(got, want), f"config3 greedy={greedy} step {step}"
+                assert acc == want_acc and not status.any()
+                hist[greedy][acc] += 1
+    assert hist[False].sum() == steps and hist[True].sum() == steps
+    print(f"config 3, {steps} steps per mode, accepted-draft histogram (0 / 1 / 2 drafts): rejection "
+          f"sampling {hist[False].tolist()}, greedy match {hist[True].tolist()}")
     s.close()
 
 

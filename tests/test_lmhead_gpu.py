@@ -254,9 +254,30 @@ def test_config5_full_size(cuda, lily):
     torch.cuda.synchronize()
     assert whole.status() == 0
     lf = lf_t.cpu().numpy()
-    for lo in (0, 131_000, vocab - 72):
-        ref = oracle.lmhead_int8(cfg.hidden, cfg.weight, cfg.scales, 64, lo, lo + 72)
-        assert np.abs(lf[:, lo:lo + 72] - ref[:, lo:lo + 72]).max() <= 4e-6 * np.abs(ref[:, lo:lo + 72]).max()
+    # The whole head against the oracle's fp32 product (all host threads).
+    ref = oracle.lmhead_int8_all(cfg.hidden, cfg.weight, cfg.scales, 64)
+    assert np.abs(lf - ref).max() <= 4e-6 * np.abs(ref).max()
     got = (np_u32(out), np_u32(status), np_u32(kept_n), np_u32(kept_ids), kept_probs.cpu().numpy(),
            lse.cpu().numpy())
     _check_against_oracle(lf, plist, cfg.uniforms, got)
+    # End to end: the oracle's product, then the oracle's draw, against the GPU
+    # head and its sharded draw. The two products differ in the order of a
+    # group's 64 adds (a few 1e-6 relative), so a token may differ only where
+    # the draw sits that close to a boundary: such rows are listed and checked.
+    differ = []
+    for r in range(rows):
+        d = oracle.sample(ref[r], oracle.params(**plist[r]), float(cfg.uniforms[r]), mode=1)
+        n = len(d.kept_ids)
+        # The global top-k lies inside the union of the shards' best 64.
+        sent = set(np_u32(rec[:, r, :512].contiguous().view(torch.int32)).reshape(n_shards, 64, 2)[:, :, 1]
+                   .ravel().tolist())
+        assert set(d.kept_ids.tolist()) <= sent, f"row {r}: a kept id is in no shard's record"
+        if got[0][r] != d.token:
+            cum = np.cumsum(d.kept_prob.astype(np.float64))
+            gap = np.abs(cum - float(cfg.uniforms[r]) * cum[-1]).min()
+            differ.append((r, int(got[0][r]), int(d.token), int(d.near_tie), float(gap)))
+    print(f"config 5 end to end: {rows - len(differ)} of {rows} tokens equal the oracle's; others "
+          f"(row, gpu, oracle, near-tie flag, distance of the draw to a boundary): {differ}")
+    assert len(differ) <= 2
+    for r, g, o, near, gap in differ:
+        assert near or gap < 1e-5, f"row {r}: token {g} vs {o} with no boundary near"

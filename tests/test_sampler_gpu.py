@@ -232,6 +232,31 @@ def test_error_rows(cuda, lily, W):
     s2.close()
 
 
+@pytest.mark.parametrize("vocab, rows", [(6007, 3), (151_936, 150)])
+def test_a_list_length_beyond_its_bound_refuses_the_row(cuda, lily, W, vocab, rows):
+    # The lengths are device values. One beyond max_history / max_list (or beyond
+    # the row pitch) would walk into the next row or past the buffer: the row is
+    # refused instead. The lists here are longer than the bound, so nothing is
+    # read out of bounds whatever the kernel does with the length.
+    rng = np.random.default_rng(3)
+    b = make_batch(W, rng, rows, vocab, 20, True, kind="zipf", history=256, rep=1.2, n_bias=8, n_ban=8)
+    b.history_len[:] = 100
+    b.history_len[0] = 200               # > max_history = 128, inside the 256-id row
+    b.bias_len[1] = 7                    # > max_list = 6, inside the 8-entry row
+    b.bias_len[2:] = 5
+    b.bias_len[0] = 5
+    b.ban_len[:] = 5
+    s = lily.SamplerScratch(vocab, max_rows=rows, max_history=128, max_list=6)
+    res = run_batch(cuda, lily, s, b)
+    want = oracle_rows(b)
+    for r in (0, 1):
+        assert res.status[r] == lily.ROW_LIST and res.ids[r] == 0xFFFFFFFF and res.kept_n[r] == 0
+    for r in range(2, rows):
+        assert res.status[r] == 0 and res.ids[r] == want[r].token, f"row {r}"
+    assert s.status() == lily.ERR_DEVICE_ROW
+    s.close()
+
+
 def test_host_side_argument_errors(cuda, lily, W):
     vocab = 1000
     s = lily.SamplerScratch(vocab, max_rows=2)

@@ -7,7 +7,7 @@ every call reuses the same array. Collected last on purpose."""
 import numpy as np
 import pytest
 
-from gpu_util import K_CAP, make_params, np_u32, run_batch, t_f32, t_logits, t_u32
+from gpu_util import K_CAP, Result, assert_parity, make_params, np_u32, oracle_rows, run_batch, t_f32, t_logits, t_u32
 
 pytestmark = pytest.mark.gpu
 
@@ -58,6 +58,9 @@ def test_the_allocation_free_draw_equals_the_regular_one_call_after_call(cuda, l
             n = kept_n[r]
             assert np.array_equal(kept_ids[r, :n], want.kept_ids[r, :n])
             assert np.abs(kept_probs[r, :n] - want.kept_probs[r, :n]).max(initial=0.0) <= 1e-5
+        # And against the CPU oracle directly, not only against the other CUDA path.
+        assert_parity(batch, Result(ids, status, kept_n, kept_ids, kept_probs), oracle_rows(batch),
+                      label=f"allocation-free call {call}")
     scratch.close()
 
 
