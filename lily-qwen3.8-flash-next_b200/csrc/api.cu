@@ -16,6 +16,7 @@
 #include "../../include/lily_sampler.h"
 #include "sample_kernel.cuh"
 #include "stream_kernel.cuh"
+#include "cluster_kernel.cuh"
 #include "lmhead_kernel.cuh"
 
 namespace {
@@ -54,6 +55,7 @@ struct lily_sampler {
     uint32_t *part_n = nullptr;
     uint32_t *tickets = nullptr;
     uint32_t *status_word = nullptr;
+    char *spill = nullptr;  // parameters of rows the small-batch kernel hands to the general code
     uint32_t *counts_scratch = nullptr;
     uint32_t *counts_table = nullptr;
     uint32_t *seen_table = nullptr;
@@ -219,11 +221,74 @@ int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, 
     return launch_serialised(h, stream_, kernel, dim3(a.n_slices, rows, 1), smem, a);
 }
 
+// Whether a call goes to the small-batch kernel (a cluster of eight blocks per
+// row): few enough rows for every cluster to have SMs of its own, aligned logits,
+// a vocabulary whose eighth fits a block's shared memory, a plain draw.
+bool cluster_call(const lily_sampler *h, const void *logits, uint64_t logits_ld, uint32_t dtype,
+                  uint32_t rows, bool plain) {
+    const size_t esize = dtype == LILY_F32 ? 4 : 2;
+    const bool vec = (reinterpret_cast<uintptr_t>(logits) % 16u == 0u) && ((logits_ld * esize) % 16u == 0u);
+    return plain && vec && rows * lily::CL <= (uint32_t)h->sm_count &&
+           lily::cluster_slice_len(h->vocab) <= lily::CL_SLICE_MAX && h->vocab >= 4096u;
+}
+
+int32_t launch_cluster(lily_sampler *h, cudaStream_t stream, const lily::ClusterArgs &ca_, uint32_t rows,
+                       uint32_t dtype) {
+    size_t smem = lily::cluster_smem_bytes(ca_.a.vocab);
+    const size_t general = smem_bytes(ca_.a.vocab, 1);  // the leader may run the general row code
+    smem = smem > general ? smem : general;
+    if (smem > (size_t)h->max_smem) {
+        return fail(h, LILY_ERR_CAPACITY, "vocabulary too large for the small-batch kernel");
+    }
+    lily::ClusterArgs ca = ca_;
+    ca.spill_params = reinterpret_cast<lily_sampling_params_t *>(h->spill);
+    ca.spill_steps = reinterpret_cast<uint32_t *>(h->spill + lily::CL_MAX_ROWS * sizeof(lily_sampling_params_t));
+    ca.spill_slots = ca.spill_steps + lily::CL_MAX_ROWS;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(lily::CL, rows, 1);
+    cfg.blockDim = dim3(lily::NT, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = lily::CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    if (dtype == LILY_F32) {
+        auto kernel = lily::cluster_rows_kernel<float>;
+        const int32_t st = raise_smem_limit(h, kernel, 1u << 8);
+        if (st != LILY_OK) {
+            return st;
+        }
+        CU(h, cudaLaunchKernelEx(&cfg, kernel, ca));
+    } else {
+        auto kernel = lily::cluster_rows_kernel<__nv_bfloat16>;
+        const int32_t st = raise_smem_limit(h, kernel, 1u << 9);
+        if (st != LILY_OK) {
+            return st;
+        }
+        CU(h, cudaLaunchKernelEx(&cfg, kernel, ca));
+    }
+    return LILY_OK;
+}
+
 int32_t launch(lily_sampler *h, cudaStream_t stream, const lily::KArgs &a, uint32_t rows,
                uint32_t dtype) {
     const size_t smem = smem_bytes(a.vocab, a.n_slices);
     if (smem > (size_t)h->max_smem) {
         return fail(h, LILY_ERR_CAPACITY, "vocabulary too large for the shared-memory bitmap");
+    }
+    const bool plain = a.cand_out == nullptr && a.merge_in == nullptr && a.spec.n_spec == 0u &&
+                       a.extra_len == 0u;
+    if (cluster_call(h, a.logits, a.logits_ld, dtype, rows, plain)) {
+        lily::ClusterArgs ca;
+        std::memset(&ca, 0, sizeof(ca));
+        ca.a = a;
+        return launch_cluster(h, stream, ca, rows, dtype);
     }
     const size_t esize = dtype == LILY_F32 ? 4 : 2;
     const bool vec = (reinterpret_cast<uintptr_t>(a.logits) % 16u == 0u) &&
@@ -384,6 +449,9 @@ int32_t lily_sampler_create(int32_t device, uint32_t vocab, uint32_t max_rows,
     if ((e = cudaMemset(h->tickets, 0, (size_t)max_rows * 4)) != cudaSuccess) {
         return bail(e, "tickets");
     }
+    if ((e = cudaMalloc(&h->spill, lily::CL_MAX_ROWS * (sizeof(lily_sampling_params_t) + 8))) != cudaSuccess) {
+        return bail(e, "parameter words of the small-batch kernel");
+    }
     if ((e = cudaMalloc(&h->status_word, 4)) != cudaSuccess ||
         (e = cudaMemset(h->status_word, 0, 4)) != cudaSuccess) {
         return bail(e, "status word");
@@ -452,6 +520,7 @@ void lily_sampler_destroy(lily_sampler_t *h) {
     cudaFree(h->part_n);
     cudaFree(h->tickets);
     cudaFree(h->status_word);
+    cudaFree(h->spill);
     cudaFree(h->counts_scratch);
     cudaFree(h->counts_table);
     cudaFree(h->seen_table);
@@ -691,7 +760,11 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
     const uint32_t *d_steps = g.steps;
     const uint32_t *d_slots = nullptr;
     int slot = -1;
-    if (!g.params_on_device || g.count_slots != nullptr) {
+    // A small batch's host parameters (and slots) travel in the kernel's own
+    // arguments: nothing is staged, no copy sits in front of the launch.
+    const bool in_args = !g.params_on_device && g.rows <= lily::CL_MAX_ROWS &&
+                         cluster_call(h, g.logits, g.logits_ld, g.logits_dtype, g.rows, true);
+    if (!in_args && (!g.params_on_device || g.count_slots != nullptr)) {
         st = next_stage(h, &slot);
         if (st != LILY_OK) {
             return st;
@@ -705,6 +778,15 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
                 return fail(h, LILY_ERR_PARAMS, buf);
             }
         }
+    }
+    if (g.count_slots != nullptr) {
+        for (uint32_t r = 0; r < g.rows; ++r) {
+            if (g.count_slots[r] >= h->max_rows) {
+                return fail(h, LILY_ERR_ARG, "no such histogram slot");
+            }
+        }
+    }
+    if (!g.params_on_device && !in_args) {
         char *hs = h->h_stage[slot];
         std::memcpy(hs + h->layout.params, g.params, sizeof(lily_sampling_params_t) * g.rows);
         d_params = reinterpret_cast<const lily_sampling_params_t *>(h->d_stage[slot] +
@@ -714,12 +796,7 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
             d_steps = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.steps);
         }
     }
-    if (g.count_slots != nullptr) {
-        for (uint32_t r = 0; r < g.rows; ++r) {
-            if (g.count_slots[r] >= h->max_rows) {
-                return fail(h, LILY_ERR_ARG, "no such histogram slot");
-            }
-        }
+    if (g.count_slots != nullptr && !in_args) {
         std::memcpy(h->h_stage[slot] + h->layout.slots, g.count_slots, sizeof(uint32_t) * g.rows);
         d_slots = reinterpret_cast<const uint32_t *>(h->d_stage[slot] + h->layout.slots);
     }
@@ -752,6 +829,23 @@ int32_t lily_sample_batch(lily_sampler_t *h, void *stream_, const lily_sample_ar
     a.kept_probs = g.kept_probs;
     a.kept_ld = g.kept_ld;
     a.n_slices = choose_slices(h, g.rows);
+    if (in_args) {
+        lily::ClusterArgs ca;
+        std::memset(&ca, 0, sizeof(ca));
+        ca.a = a;
+        ca.a.params = nullptr;
+        ca.a.steps = nullptr;
+        ca.inline_params = 1;
+        std::memcpy(ca.params, g.params, sizeof(lily_sampling_params_t) * g.rows);
+        if (g.steps != nullptr) {
+            std::memcpy(ca.steps, g.steps, sizeof(uint32_t) * g.rows);
+        }
+        if (g.count_slots != nullptr) {
+            ca.inline_slots = 1;
+            std::memcpy(ca.slots, g.count_slots, sizeof(uint32_t) * g.rows);
+        }
+        return launch_cluster(h, stream, ca, g.rows, g.logits_dtype);
+    }
     st = launch(h, stream, a, g.rows, g.logits_dtype);
     if (slot >= 0) {
         CU(h, cudaEventRecord(h->ev[slot], stream));
