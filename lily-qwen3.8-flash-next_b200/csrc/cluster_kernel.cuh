@@ -11,18 +11,25 @@
 //      shared memory (one shared-memory atomic per distinct id of a
 //      warp's 32 ids: real histories repeat a few ids very often);
 //   2. bias entries are added in place in list order, banned ids become -inf in
-//      place, then EVERY logit of the slice is adjusted (penalties, division by
-//      the temperature): no thresholds, no second pass;
-//   3. the cluster agrees on the row's largest adjusted logit (one exchange);
-//      every block bins its values by their distance from it (64 bins per unit,
-//      2048 bins) into a shared-memory histogram;
+//      place, then the penalties are applied to EVERY logit of the slice: no
+//      thresholds, no second pass. The division by the temperature keeps the
+//      order, so the selection works on the values before it and only the
+//      candidates are divided;
+//   3. the cluster agrees on the row's largest such value (one exchange); every
+//      block bins its values by their distance from it (64 bins per unit, 2048
+//      bins) into a shared-memory histogram;
 //   4. every block adds the eight histograms up for itself (distributed shared
 //      memory reads) and finds the bin in which the count from the top reaches
-//      k: the candidates are the values down to that bin, k plus a handful;
-//   5. every block sends its candidates to all eight blocks; each block ranks an
-//      eighth of them against all of them by counting ((key descending, id
-//      ascending), as the reference's CPU sampler orders them) and stores those
-//      of rank below k at their rank in the leader's shared memory;
+//      k. The candidates are the values down to one bin past it (the margin
+//      catches a value that rounds to the same quotient as the k-th): k plus a
+//      handful. The summed histogram also says where each bin's candidates go
+//      in the order of the bins, and the other blocks' histograms where this
+//      block's share of a bin starts;
+//   5. every block writes its candidates (divided, as key << 32 | ~id) to those
+//      places in all eight blocks, ranks each of its own against the few others
+//      of the same bin ((key descending, id ascending), as the reference's CPU
+//      sampler orders them) and stores those of rank below k at their rank in
+//      the leader's shared memory;
 //   6. the leader runs the softmax weights, the sequential prefix sums in rank
 //      order, the top-p / min-p cut and the draw (tests/unit/kernels/
 //      sample.rs:8-54 of the reference), and writes the outputs.
@@ -46,31 +53,35 @@ namespace cgx = cooperative_groups;
 constexpr uint32_t CL = 8;                   // blocks per row (the portable cluster size)
 constexpr uint32_t CL_SLICE_MAX = 20480;     // logits per block: 80 KB as f32 and as much for their counts
 constexpr uint32_t CL_BINS = 2048;
-constexpr float CL_BINS_PER_UNIT = 64.0f;    // of adjusted logit: the histogram spans 32 units below the top
+constexpr float CL_BINS_PER_UNIT = 64.0f;    // of logit: the histogram spans 32 units below the top
+constexpr float CL_TOP_MAX = 65536.0f;       // beyond it a bin is no wider than a rounding step: the general code
 constexpr uint32_t CL_CAND = 1536;           // candidates of a row, k = 1024 plus what shares the last bin
 constexpr uint32_t CL_LIST = SP_SMEM;        // bias + ban entries staged in shared memory
 constexpr uint32_t CL_MAX_ROWS = 8;          // rows whose parameters travel in the kernel's arguments
 
 struct alignas(16) ClusterSmem {
-    uint32_t hist[CL_BINS];            // this block's histogram; read by the whole cluster
+    uint32_t hist[CL_BINS];            // this block's histogram, read by the whole cluster; then fill[]: this
+                                       //   block's candidates placed so far, per bin
     uint32_t ghist[CL_BINS];           // the cluster's sum
-    unsigned long long cand[CL_CAND];  // every candidate of the row: key << 32 | ~id
-    unsigned long long mine[CL_CAND];  // this block's candidates; later the leader's p and prefix sums
+    uint32_t pre[CL_BINS];             // candidates in the bins before a bin; later the leader's weights p
+    uint32_t boff[CL_BINS];            // of a bin, what the blocks of lower rank hold; later the prefix sums
+    unsigned long long cand[CL_CAND];  // every candidate of the row in bin order: key << 32 | ~id
+    uint32_t myslot[CL_CAND];          // this block's candidates: place in cand[] | bin << 16
     unsigned long long sorted[KCAP];   // leader: the best k in rank order
-    float cmax[CL];                    // each block's largest adjusted logit
+    float cmax[CL];                    // each block's largest value
     uint32_t cerr[CL];                 // each block's error word
-    uint32_t lcount[CL];               // each block's number of candidates
     uint32_t warp_sums[NT / 32];
     float warp_max[NT / 32];
     alignas(16) uint32_t sp_ids[CL_LIST + 4];
     float sp_vals[CL_LIST];
     uint32_t n_mine;
     uint32_t bstar;
-    uint32_t n_upto;    // candidates of the row: the count of bins 0..bstar
     uint32_t err;
     uint32_t n_keep;
     uint32_t chosen;
 };
+static_assert(CL_CAND <= 65536u && CL_BINS <= 65536u, "place and bin share a word");
+static_assert(CL_BINS >= KCAP, "p and the prefix sums fit pre[] and boff[]");
 
 // The two arrays behind the fixed part: the slice as f32 (later its adjusted
 // values) and its counts.
@@ -84,7 +95,7 @@ __host__ __device__ inline size_t cluster_smem_bytes(uint32_t vocab) {
     return sizeof(ClusterSmem) + sl * 4u + sl * 4u + 16u;
 }
 
-// The bin of adjusted value q under the row's largest one: 0 holds the top.
+// The bin of value q under the row's largest one: 0 holds the top.
 __device__ __forceinline__ uint32_t cluster_bin(float q, float top) {
     if (q == top) {
         return 0u;
@@ -117,9 +128,8 @@ __device__ __forceinline__ void cluster_finalize(ClusterSmem *sm, const KArgs &a
                                                  float top_p, float min_p, bool argmax_mode, bool count_draw,
                                                  uint32_t slot, float u) {
     const uint32_t tid = threadIdx.x;
-    float *p = reinterpret_cast<float *>(sm->mine);
-    float *cum = p + KCAP;
-    static_assert(sizeof(unsigned long long) * CL_CAND >= 2u * KCAP * sizeof(float), "p and cum fit in mine[]");
+    float *p = reinterpret_cast<float *>(sm->pre);
+    float *cum = reinterpret_cast<float *>(sm->boff);
     const uint32_t top_key = (uint32_t)(sm->sorted[0] >> 32);
     const float top = float_of_key(top_key);
     if (argmax_mode) {
@@ -231,6 +241,12 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     if (stamps && tid == 0) {
         stamps[PH_ENTRY] = global_ns();
     }
+#define CL_STAMP(i)                      \
+    do {                                 \
+        if (stamps && tid == 0) {        \
+            stamps[(i)] = global_ns();   \
+        }                                \
+    } while (0)
 
     // What needs no input comes first (see sample_row on the launch attribute).
     for (uint32_t b = tid; b < CL_BINS; b += NT) {
@@ -348,6 +364,7 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     }
 
     cluster.sync();  // 0: every block of the cluster is running before shared memory is written across blocks
+    CL_STAMP(0);
 
     // ---- 1. the slice into shared memory as f32; the history into the count table
     {
@@ -400,6 +417,7 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
         }
     }
     __syncthreads();
+    CL_STAMP(1);
 
     // ---- 2. bias in list order (duplicates add), then bans, in place
     if (n_sp != 0u) {
@@ -434,7 +452,8 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
         __syncthreads();
     }
 
-    // ---- 3. every logit adjusted; the block's largest
+    CL_STAMP(2);
+    // ---- 3. the penalties on every logit; the block's largest value
     float tmax = neg_inf();
     for (uint32_t i = tid; i < len; i += NT) {
         float x = vals[i];
@@ -443,17 +462,19 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
             if (c != 0u) {
                 x = x > 0.0f ? __fdiv_rn(x, P.repetition_penalty) : __fmul_rn(x, P.repetition_penalty);
                 x = __fsub_rn(x, __fadd_rn(P.presence_penalty, __fmul_rn(P.frequency_penalty, (float)c)));
+                vals[i] = x;
             }
         }
-        float q = __fdiv_rn(x, temp);
-        if (argmax_mode) {
-            // NaN never wins and the two zeros tie (src/kernels/metal/elementwise.metal:145-150).
-            q = q != q ? neg_inf() : __fadd_rn(q, 0.0f);
-        } else if (q != q) {
-            sm->err = LILY_ROW_NAN;
+        if (x != x) {
+            if (argmax_mode) {
+                // NaN never wins (src/kernels/metal/elementwise.metal:145-150).
+                x = neg_inf();
+                vals[i] = x;
+            } else {
+                sm->err = LILY_ROW_NAN;
+            }
         }
-        vals[i] = q;
-        tmax = fmaxf(tmax, q);
+        tmax = fmaxf(tmax, x);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -471,7 +492,9 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
         cluster.map_shared_rank(sm->cmax, tid)[rank] = bm;
         cluster.map_shared_rank(sm->cerr, tid)[rank] = sm->err;
     }
+    CL_STAMP(2);
     cluster.sync();  // 1: every block has every block's maximum and error word
+    CL_STAMP(3);
     float top = neg_inf();
     uint32_t err = 0;
     for (uint32_t r = 0; r < CL; ++r) {
@@ -490,33 +513,36 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
         }
         return;
     }
+    if (!(fabsf(top) < CL_TOP_MAX)) {
+        leader_draws_alone();
+        return;
+    }
 
     // ---- 4. histogram of the distances from the top; the bin where the count reaches k
-    for (uint32_t i0 = 0; i0 < len; i0 += NT) {
-        const uint32_t i = i0 + tid;
-        const bool in = i < len;
-        const uint32_t bin = in ? cluster_bin(vals[i], top) : 0u;
-        const unsigned live = __ballot_sync(FULL, in);
-        if (in) {
-            const unsigned peers = __match_any_sync(live, bin);
-            if (lane == (uint32_t)(__ffs(peers) - 1)) {
-                atomicAdd(&sm->hist[bin], (uint32_t)__popc(peers));
-            }
+    for (uint32_t i = tid; i < len; i += NT) {
+        const uint32_t bin = cluster_bin(vals[i], top);
+        if (bin != CL_BINS - 1u) {  // (what lies 32 units below the top is never a candidate)
+            atomicAdd(&sm->hist[bin], 1u);
         }
     }
+    CL_STAMP(9);
     cluster.sync();  // 2: every block's histogram is complete
+    CL_STAMP(4);
     for (uint32_t b = tid; b < CL_BINS; b += NT) {
-        uint32_t s = 0;
+        uint32_t s = 0, lower = 0;
 #pragma unroll
         for (uint32_t r = 0; r < CL; ++r) {
-            s += cluster.map_shared_rank(sm->hist, r)[b];
+            const uint32_t v = cluster.map_shared_rank(sm->hist, r)[b];
+            s += v;
+            lower += r < rank ? v : 0u;
         }
         sm->ghist[b] = s;
+        sm->boff[b] = lower;
     }
     __syncthreads();
     {
-        // Thread t owns bins 4t .. 4t + 3; the bin in which the running count,
-        // from bin 0 up, reaches k.
+        // Thread t owns bins 4t .. 4t + 3: how many candidates lie in the bins
+        // before each, and the bin in which that count, from bin 0 up, reaches k.
         constexpr uint32_t BPT = CL_BINS / NT;
         uint32_t c[BPT], sum = 0;
 #pragma unroll
@@ -537,106 +563,93 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
         }
         if (tid == 0) {
             sm->bstar = NONE;
-            sm->n_upto = 0;
         }
         __syncthreads();
-        uint32_t before = 0;
+        uint32_t cum = incl - sum;
         for (uint32_t w = 0; w < warp; ++w) {
-            before += sm->warp_sums[w];
+            cum += sm->warp_sums[w];
         }
-        uint32_t cum = before + incl - sum;
-        if (cum < k && k <= cum + sum) {
 #pragma unroll
-            for (uint32_t j = 0; j < BPT; ++j) {
-                if (cum < k && k <= cum + c[j]) {
-                    sm->bstar = tid * BPT + j;
-                    sm->n_upto = cum + c[j];
-                }
-                cum += c[j];
+        for (uint32_t j = 0; j < BPT; ++j) {
+            sm->pre[tid * BPT + j] = cum;
+            if (cum < k && k <= cum + c[j]) {
+                sm->bstar = tid * BPT + j;
             }
+            cum += c[j];
         }
         __syncthreads();
     }
     const uint32_t bstar = sm->bstar;
-    const uint32_t n = sm->n_upto;
-    if (warp < CL && bstar != NONE) {
-        // How many candidates block `warp` will send: its bins 0 .. bstar.
-        const uint32_t *h = cluster.map_shared_rank(sm->hist, warp);
-        uint32_t s = 0;
-        for (uint32_t b = lane; b <= bstar; b += 32u) {
-            s += h[b];
-        }
-        s = __reduce_add_sync(FULL, s);
-        if (lane == 0) {
-            sm->lcount[warp] = s;
-        }
-    }
+    // One bin of margin: a value there may round to the quotient of the k-th.
+    const uint32_t blast = bstar == NONE ? NONE : min(bstar + 1u, CL_BINS - 2u);
+    const uint32_t n = bstar == NONE ? 0u : sm->pre[blast] + sm->ghist[blast];
     cluster.sync();  // 3: nobody reads another block's histogram any more
-    if (bstar == NONE || bstar == CL_BINS - 1u || n > CL_CAND) {
-        // Fewer than k values within 32 units of the top, or too many in the last
-        // bin (a flat row, heavy ties): the general code selects without binning.
+    CL_STAMP(5);
+    if (bstar == NONE || bstar + 1u > CL_BINS - 2u || n > CL_CAND) {
+        // Fewer than k values within 32 units of the top, or too many around the
+        // k-th (a flat row, heavy ties): the general code selects without binning.
         leader_draws_alone();
         return;
     }
 
-    // ---- 5. candidates to every block; each block ranks an eighth of them
-    for (uint32_t i0 = 0; i0 < len; i0 += NT) {
-        const uint32_t i = i0 + tid;
-        const float q = i < len ? vals[i] : 0.0f;
-        const bool take = i < len && cluster_bin(q, top) <= bstar;
-        const unsigned live = __ballot_sync(FULL, take);
-        if (take) {
-            uint32_t base = 0;
-            const int leader = __ffs(live) - 1;
-            if ((int)lane == leader) {
-                base = atomicAdd(&sm->n_mine, (uint32_t)__popc(live));
-            }
-            base = __shfl_sync(live, base, leader);
-            const uint32_t at = base + __popc(live & ((1u << lane) - 1u));
-            if (at < CL_CAND) {
-                sm->mine[at] = ((unsigned long long)key_of(q) << 32) | (uint32_t)~(lo + i);
-            }
-        }
+    // ---- 5. candidates to their places in every block; ranks within the bins
+    uint32_t *fill = sm->hist;
+    for (uint32_t b = tid; b <= blast; b += NT) {
+        fill[b] = 0;
     }
     __syncthreads();
-    {
-        uint32_t base = 0;
-        for (uint32_t r = 0; r < rank; ++r) {
-            base += sm->lcount[r];
-        }
-        const uint32_t mine_n = min(sm->lcount[rank], CL_CAND - min(base, CL_CAND));
-        for (uint32_t i = tid; i < mine_n; i += NT) {
-            const unsigned long long v = sm->mine[i];
+    for (uint32_t i = tid; i < len; i += NT) {
+        const float x = vals[i];
+        const uint32_t bin = cluster_bin(x, top);
+        if (bin <= blast) {
+            float q = __fdiv_rn(x, temp);
+            if (argmax_mode) {
+                q = __fadd_rn(q, 0.0f);  // the two zeros tie (src/kernels/metal/elementwise.metal:145-150)
+            }
+            const unsigned long long v = ((unsigned long long)key_of(q) << 32) | (uint32_t)~(lo + i);
+            const uint32_t at = sm->pre[bin] + sm->boff[bin] + atomicAdd(&fill[bin], 1u);
+            sm->myslot[atomicAdd(&sm->n_mine, 1u)] = at | (bin << 16);
 #pragma unroll
             for (uint32_t r = 0; r < CL; ++r) {
-                cluster.map_shared_rank(sm->cand, r)[base + i] = v;
+                cluster.map_shared_rank(sm->cand, r)[at] = v;
             }
         }
     }
-    cluster.sync();  // 4: every block holds all n candidates
+    CL_STAMP(10);
+    cluster.sync();  // 4: every block holds all n candidates, grouped by bin
+    CL_STAMP(6);
     {
-        const uint32_t i_lo = rank * n / CL, i_hi = (rank + 1u) * n / CL;
         unsigned long long *leader_sorted = cluster.map_shared_rank(sm->sorted, 0);
-        const uint32_t sub = tid & 3u, g = tid >> 2;
-        const uint32_t j_lo = sub * n / 4u, j_hi = (sub + 1u) * n / 4u;
-        // Four threads per candidate, each counting over a quarter of the
-        // candidates how many come before it.
-        for (uint32_t i0 = i_lo; i0 < i_hi; i0 += NT / 4) {
-            const uint32_t i = i0 + g;
-            const bool valid = i < i_hi;
-            const unsigned long long me = valid ? sm->cand[i] : ~0ull;
-            uint32_t before = 0;
-            for (uint32_t j = j_lo; j < j_hi; ++j) {
-                before += sm->cand[j] > me ? 1u : 0u;
+        const uint32_t mine_n = sm->n_mine;
+        for (uint32_t i = tid; i < mine_n; i += NT) {
+            const uint32_t at = sm->myslot[i] & 0xFFFFu, bin = sm->myslot[i] >> 16;
+            const unsigned long long me = sm->cand[at];
+            const uint32_t first = sm->pre[bin], last = first + sm->ghist[bin];
+            uint32_t place = first;
+            for (uint32_t j = first; j < last; ++j) {
+                place += sm->cand[j] > me ? 1u : 0u;
             }
-            before += __shfl_xor_sync(FULL, before, 1);
-            before += __shfl_xor_sync(FULL, before, 2);
-            if (valid && sub == 0u && before < k) {
-                leader_sorted[before] = me;
+            // Two values one rounding step apart can sit on the two sides of a bin
+            // edge and still divide to the same quotient: then the id decides
+            // across the edge as well. (Keys never rise from a bin to the next.)
+            if (bin < blast) {
+                for (uint32_t j = last; j < last + sm->ghist[bin + 1u]; ++j) {
+                    place += sm->cand[j] > me ? 1u : 0u;
+                }
+            }
+            if (bin > 0u) {
+                for (uint32_t j = sm->pre[bin - 1u]; j < first; ++j) {
+                    place -= sm->cand[j] < me ? 1u : 0u;
+                }
+            }
+            if (place < k) {
+                leader_sorted[place] = me;
             }
         }
     }
+    CL_STAMP(11);
     cluster.sync();  // 5: the leader holds the best min(n, k) in rank order
+    CL_STAMP(8);
     if (rank != 0u) {
         return;
     }
