@@ -289,6 +289,27 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     }
     const float u = a.uniforms ? __ldg(a.uniforms + row) : uniform_for(P.seed, step);
     const T *row_ptr = reinterpret_cast<const T *>(a.logits) + (uint64_t)row * a.logits_ld;
+    // ---- 1. the slice into shared memory as f32. It does not depend on the row's
+    // parameters, whose loads (above) are still on their way.
+    {
+        constexpr uint32_t PER = 16u / (uint32_t)sizeof(T);
+        const T *src = row_ptr + lo;
+        const uint32_t nvec = len / PER;
+        for (uint32_t v = tid; v < nvec; v += NT) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4 *>(src) + v);
+            float4 *dst = reinterpret_cast<float4 *>(vals + (size_t)v * PER);
+            if (sizeof(T) == 4) {
+                dst[0] = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z),
+                                     __uint_as_float(q.w));
+            } else {
+                dst[0] = make_float4(bf16_lo(q.x), bf16_hi(q.x), bf16_lo(q.y), bf16_hi(q.y));
+                dst[1] = make_float4(bf16_lo(q.z), bf16_hi(q.z), bf16_lo(q.w), bf16_hi(q.w));
+            }
+        }
+        for (uint32_t i = nvec * PER + tid; i < len; i += NT) {
+            vals[i] = widen(src[i]);
+        }
+    }
 
     auto refuse = [&](uint32_t status) {
         if (rank == 0 && tid == 0) {
@@ -363,47 +384,44 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
         return;
     }
 
-    cluster.sync();  // 0: every block of the cluster is running before shared memory is written across blocks
+    // ---- 1b. the history into the count table
+    cluster.sync();  // 0: every block of the cluster is running, its count table zeroed
     CL_STAMP(0);
-
-    // ---- 1. the slice into shared memory as f32; the history into the count table
-    {
-        constexpr uint32_t PER = 16u / (uint32_t)sizeof(T);
-        const T *src = row_ptr + lo;
-        const uint32_t nvec = len / PER;
-        for (uint32_t v = tid; v < nvec; v += NT) {
-            const uint4 q = __ldg(reinterpret_cast<const uint4 *>(src) + v);
-            float4 *dst = reinterpret_cast<float4 *>(vals + (size_t)v * PER);
-            if (sizeof(T) == 4) {
-                dst[0] = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z),
-                                     __uint_as_float(q.w));
-            } else {
-                dst[0] = make_float4(bf16_lo(q.x), bf16_hi(q.x), bf16_lo(q.y), bf16_hi(q.y));
-                dst[1] = make_float4(bf16_lo(q.z), bf16_hi(q.z), bf16_lo(q.w), bf16_hi(q.w));
-            }
-        }
-        for (uint32_t i = nvec * PER + tid; i < len; i += NT) {
-            vals[i] = widen(src[i]);
-        }
-    }
+    const bool scattered = use_pen && !table_mode && hist_len_row != 0u;
     if (use_pen) {
         if (table_mode) {
             const uint32_t *src = a.counts_table + (uint64_t)slot * vocab + lo;
             for (uint32_t i = tid; i < len; i += NT) {
                 cnt[i] = src[i];
             }
-        } else {
+        } else if (hist_len_row != 0u) {
+            // Each block takes an eighth of the LIST, whatever ids it holds, and adds
+            // into the count table of the block that owns an id (a real history
+            // repeats a few ids very often, and they all live in one block's range:
+            // this spreads the work of counting them). One atomic per distinct id of
+            // a warp's 32.
             const uint32_t *hist = a.history_ids + (uint64_t)row * a.history_ld;
-            for (uint32_t i0 = 0; i0 < hist_len_row; i0 += NT) {
-                const uint32_t i = i0 + tid;
-                const uint32_t off = (i < hist_len_row ? __ldg(hist + i) : NONE) - lo;
-                const bool in = off < len;
-                const unsigned live = __ballot_sync(FULL, in);
-                if (in) {
-                    // One atomic per distinct id of the warp's 32.
-                    const unsigned peers = __match_any_sync(live, off);
-                    if (lane == (uint32_t)(__ffs(peers) - 1)) {
-                        atomicAdd(&cnt[off], (uint32_t)__popc(peers));
+            const uint32_t share = (hist_len_row + CL - 1u) / CL;
+            const uint32_t h_lo = min(hist_len_row, rank * share), h_hi = min(hist_len_row, h_lo + share);
+            constexpr uint32_t HB = 4;  // loads in flight per thread
+            for (uint32_t i0 = h_lo; i0 < h_hi; i0 += NT * HB) {
+                uint32_t ids[HB];
+#pragma unroll
+                for (uint32_t j = 0; j < HB; ++j) {
+                    const uint32_t i = i0 + j * NT + tid;
+                    ids[j] = i < h_hi ? __ldg(hist + i) : NONE;
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < HB; ++j) {
+                    const bool in = ids[j] < vocab;
+                    const unsigned live = __ballot_sync(FULL, in);
+                    if (in) {
+                        const unsigned peers = __match_any_sync(live, ids[j]);
+                        if (lane == (uint32_t)(__ffs(peers) - 1)) {
+                            const uint32_t owner = ids[j] / sl;
+                            atomicAdd(cluster.map_shared_rank(cnt, owner) + (ids[j] - owner * sl),
+                                      (uint32_t)__popc(peers));
+                        }
                     }
                 }
             }
@@ -416,7 +434,11 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
             sm->sp_vals[j] = j < n_bias ? a.bias_vals[(uint64_t)row * a.bias_ld + j] : 0.0f;
         }
     }
-    __syncthreads();
+    if (scattered) {
+        cluster.sync();  // every block's counts have arrived
+    } else {
+        __syncthreads();
+    }
     CL_STAMP(1);
 
     // ---- 2. bias in list order (duplicates add), then bans, in place
@@ -425,15 +447,24 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
             const uint32_t id = sm->sp_ids[j];
             const uint32_t off = id - lo;
             if (off < len) {
-                bool first = true;
-                for (uint32_t e = 0; e < j && first; ++e) {
-                    first = sm->sp_ids[e] != id;
+                // The first entry of an id adds every entry of that id, in list order.
+                uint32_t earlier = 0;
+#pragma unroll 8
+                for (uint32_t e = 0; e < j; ++e) {
+                    earlier += sm->sp_ids[e] == id ? 1u : 0u;
                 }
-                if (first) {
-                    float x = vals[off];
-                    for (uint32_t e = j; e < n_bias; ++e) {
-                        if (sm->sp_ids[e] == id) {
-                            x = __fadd_rn(x, sm->sp_vals[e]);
+                if (earlier == 0u) {
+                    float x = __fadd_rn(vals[off], sm->sp_vals[j]);
+                    uint32_t later = 0;
+#pragma unroll 8
+                    for (uint32_t e = j + 1u; e < n_bias; ++e) {
+                        later += sm->sp_ids[e] == id ? 1u : 0u;
+                    }
+                    if (later != 0u) {
+                        for (uint32_t e = j + 1u; e < n_bias; ++e) {
+                            if (sm->sp_ids[e] == id) {
+                                x = __fadd_rn(x, sm->sp_vals[e]);
+                            }
                         }
                     }
                     vals[off] = x;
@@ -455,12 +486,15 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     CL_STAMP(2);
     // ---- 3. the penalties on every logit; the block's largest value
     float tmax = neg_inf();
+#pragma unroll 4
     for (uint32_t i = tid; i < len; i += NT) {
         float x = vals[i];
         if (use_pen) {
             const uint32_t c = cnt[i];
             if (c != 0u) {
-                x = x > 0.0f ? __fdiv_rn(x, P.repetition_penalty) : __fmul_rn(x, P.repetition_penalty);
+                if (P.repetition_penalty != 1.0f) {  // (x / 1 and x * 1 are x)
+                    x = x > 0.0f ? __fdiv_rn(x, P.repetition_penalty) : __fmul_rn(x, P.repetition_penalty);
+                }
                 x = __fsub_rn(x, __fadd_rn(P.presence_penalty, __fmul_rn(P.frequency_penalty, (float)c)));
                 vals[i] = x;
             }
@@ -519,6 +553,7 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     }
 
     // ---- 4. histogram of the distances from the top; the bin where the count reaches k
+#pragma unroll 4
     for (uint32_t i = tid; i < len; i += NT) {
         const uint32_t bin = cluster_bin(vals[i], top);
         if (bin != CL_BINS - 1u) {  // (what lies 32 units below the top is never a candidate)
@@ -528,16 +563,27 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     CL_STAMP(9);
     cluster.sync();  // 2: every block's histogram is complete
     CL_STAMP(4);
-    for (uint32_t b = tid; b < CL_BINS; b += NT) {
-        uint32_t s = 0, lower = 0;
+    {
+        constexpr uint32_t BPT = CL_BINS / NT;
+        uint32_t v[BPT][CL];
 #pragma unroll
-        for (uint32_t r = 0; r < CL; ++r) {
-            const uint32_t v = cluster.map_shared_rank(sm->hist, r)[b];
-            s += v;
-            lower += r < rank ? v : 0u;
+        for (uint32_t j = 0; j < BPT; ++j) {
+#pragma unroll
+            for (uint32_t r = 0; r < CL; ++r) {
+                v[j][r] = cluster.map_shared_rank(sm->hist, r)[tid + j * NT];
+            }
         }
-        sm->ghist[b] = s;
-        sm->boff[b] = lower;
+#pragma unroll
+        for (uint32_t j = 0; j < BPT; ++j) {
+            uint32_t s = 0, lower = 0;
+#pragma unroll
+            for (uint32_t r = 0; r < CL; ++r) {
+                s += v[j][r];
+                lower += r < rank ? v[j][r] : 0u;
+            }
+            sm->ghist[tid + j * NT] = s;
+            sm->boff[tid + j * NT] = lower;
+        }
     }
     __syncthreads();
     {
@@ -598,6 +644,7 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
         fill[b] = 0;
     }
     __syncthreads();
+#pragma unroll 4
     for (uint32_t i = tid; i < len; i += NT) {
         const float x = vals[i];
         const uint32_t bin = cluster_bin(x, top);
