@@ -48,7 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    extra = os.environ.get("LILY_NVCC_EXTRA", "").split()  # e.g. -DLILY_DEBUG for device printf
+    extra = os.environ.get("LILY_NVCC_EXTRA", "").split()  # extra nvcc flags, e.g. -Xptxas -v
     cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", INCLUDE, "-o", LIB, *sources()]
     if verbose:
         cmd.insert(1, "-Xptxas")

@@ -332,10 +332,6 @@ void base_args(const lily_sampler *h, lily::KArgs *a) {
     a->tickets = h->tickets;
     a->status_word = h->status_word;
     a->phase_clocks = h->phase_clocks;
-#ifdef LILY_DEBUG
-    const char *stop = std::getenv("LILY_DEBUG_STOP");
-    a->debug_stop = stop ? (uint32_t)std::atoi(stop) : 0u;
-#endif
 }
 
 int32_t check_handle(lily_sampler *h) {
@@ -933,20 +929,6 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
     auto kernel = affine ? lily_head::lmhead_int8_kernel<lily_head::VARIANT_AFFINE>
                          : lily_head::lmhead_int8_kernel<0>;
     bool &attr_set = affine ? h->lm_attr_affine : h->lm_attr;
-#ifdef LILY_DEBUG
-    if (const char *v = std::getenv("LILY_LMHEAD_VARIANT")) {
-        const int variant = affine ? -1 : std::atoi(v);
-        kernel = variant < 0     ? kernel
-                 : variant == 1    ? lily_head::lmhead_int8_kernel<1>
-                 : variant == 2  ? lily_head::lmhead_int8_kernel<2>
-                 : variant == 3  ? lily_head::lmhead_int8_kernel<3>
-                 : variant == 11 ? lily_head::lmhead_int8_kernel<11>
-                 : variant == 19 ? lily_head::lmhead_int8_kernel<19>
-                 : variant == 27 ? lily_head::lmhead_int8_kernel<27>
-                                 : lily_head::lmhead_int8_kernel<0>;
-        attr_set = false;
-    }
-#endif
     if (!attr_set) {
         CU(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)lily_head::Smem::BYTES));

@@ -16,7 +16,7 @@
 //      order, so the selection works on the values before it and only the
 //      candidates are divided;
 //   3. the cluster agrees on the row's largest such value (one exchange); every
-//      block bins its values by their distance from it (64 bins per unit, 2048
+//      block bins its values by their distance from it (32 bins per unit, 1024
 //      bins) into a shared-memory histogram;
 //   4. every block adds the eight histograms up for itself (distributed shared
 //      memory reads) and finds the bin in which the count from the top reaches
@@ -52,8 +52,8 @@ namespace cgx = cooperative_groups;
 
 constexpr uint32_t CL = 8;                   // blocks per row (the portable cluster size)
 constexpr uint32_t CL_SLICE_MAX = 20480;     // logits per block: 80 KB as f32 and as much for their counts
-constexpr uint32_t CL_BINS = 2048;
-constexpr float CL_BINS_PER_UNIT = 64.0f;    // of logit: the histogram spans 32 units below the top
+constexpr uint32_t CL_BINS = 1024;
+constexpr float CL_BINS_PER_UNIT = 32.0f;    // of logit: the histogram spans 32 units below the top
 constexpr float CL_TOP_MAX = 65536.0f;       // beyond it a bin is no wider than a rounding step: the general code
 constexpr uint32_t CL_CAND = 1536;           // candidates of a row, k = 1024 plus what shares the last bin
 constexpr uint32_t CL_LIST = SP_SMEM;        // bias + ban entries staged in shared memory
@@ -388,6 +388,14 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     cluster.sync();  // 0: every block of the cluster is running, its count table zeroed
     CL_STAMP(0);
     const bool scattered = use_pen && !table_mode && hist_len_row != 0u;
+    // (The lists first: their loads are on their way while the history is counted.)
+    if (n_sp != 0u) {
+        for (uint32_t j = tid; j < n_sp; j += NT) {
+            sm->sp_ids[j] = j < n_bias ? a.bias_ids[(uint64_t)row * a.bias_ld + j]
+                                       : a.ban_ids[(uint64_t)row * a.ban_ld + (j - n_bias)];
+            sm->sp_vals[j] = j < n_bias ? a.bias_vals[(uint64_t)row * a.bias_ld + j] : 0.0f;
+        }
+    }
     if (use_pen) {
         if (table_mode) {
             const uint32_t *src = a.counts_table + (uint64_t)slot * vocab + lo;
@@ -425,13 +433,6 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
                     }
                 }
             }
-        }
-    }
-    if (n_sp != 0u) {
-        for (uint32_t j = tid; j < n_sp; j += NT) {
-            sm->sp_ids[j] = j < n_bias ? a.bias_ids[(uint64_t)row * a.bias_ld + j]
-                                       : a.ban_ids[(uint64_t)row * a.ban_ld + (j - n_bias)];
-            sm->sp_vals[j] = j < n_bias ? a.bias_vals[(uint64_t)row * a.bias_ld + j] : 0.0f;
         }
     }
     if (scattered) {
@@ -587,7 +588,7 @@ __global__ void __launch_bounds__(NT, 1) cluster_rows_kernel(const __grid_consta
     }
     __syncthreads();
     {
-        // Thread t owns bins 4t .. 4t + 3: how many candidates lie in the bins
+        // Thread t owns BPT neighbouring bins: how many candidates lie in the bins
         // before each, and the bin in which that count, from bin 0 up, reaches k.
         constexpr uint32_t BPT = CL_BINS / NT;
         uint32_t c[BPT], sum = 0;

@@ -50,9 +50,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#ifdef LILY_DEBUG
-#include <cstdio>
-#endif
 
 namespace lily_head {
 
@@ -292,13 +289,8 @@ __device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
     hi = __uint_as_float(b);
 }
 
-#ifdef LILY_DEBUG
-#define LM_T0() long long t_mark = clock64()
-#define LM_ACC(var) do { const long long t_now = clock64(); var += t_now - t_mark; t_mark = t_now; } while (0)
-#else
 #define LM_T0() do {} while (0)
 #define LM_ACC(var) do {} while (0)
-#endif
 
 // VARIANT is 0 in the product; debug builds instantiate others that leave
 // out the epilogue's math (bit 0), the conversion (bit 1), the hidden-state
@@ -382,13 +374,6 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                 mma_commit(base + Smem::DONE + 8 * (q % DONE_SLOTS));
                 LM_ACC(t_commit);
             }
-#ifdef LILY_DEBUG
-            if (blockIdx.x == 0 && half == 0) {
-                printf("mma: groups %u wait_h %lld wait_acc %lld wait_a %lld issue %lld commit %lld (clocks per group)\n",
-                       total_groups, tw_h / total_groups, tw_acc / total_groups, tw_a / total_groups,
-                       t_issue / total_groups, t_commit / total_groups);
-            }
-#endif
         }
         __syncwarp();
     } else if (warp == WARP_LOAD) {
@@ -429,12 +414,6 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                     }
                 }
             }
-#ifdef LILY_DEBUG
-            if (blockIdx.x == 0 && total_groups) {
-                printf("load: wait_raw_empty %lld wait_h_empty %lld\n", tw_re / total_groups,
-                       tw_he / total_groups);
-            }
-#endif
         }
         __syncwarp();
     } else if (warp < WARP_EPI0) {
@@ -508,12 +487,6 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                 mbar_arrive(base + Smem::RAW_EMPTY + 8 * st);
             }
         }
-#ifdef LILY_DEBUG
-        if (blockIdx.x == 0 && ct == 0 && total_groups) {
-            printf("conv: wait_raw %lld wait_a_empty %lld convert %lld st+arrive %lld\n",
-                   tw_raw / total_groups, tw_ae / total_groups, t_conv / total_groups, t_st / total_groups);
-        }
-#endif
     } else {
         // ---- scale each group's sums and add them up; write the tile
         const uint32_t e = warp - WARP_EPI0;
@@ -603,12 +576,6 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             }
             LM_ACC(t_store);
         }
-#ifdef LILY_DEBUG
-        if (blockIdx.x == 0 && e == 0 && lane == 0 && total_groups) {
-            printf("epi: wait_acc_full %lld math %lld store %lld\n", tw_af / total_groups,
-                   t_math / total_groups, t_store / total_groups);
-        }
-#endif
     }
 
     tc_fence_before();

@@ -30,10 +30,6 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
-#ifdef LILY_DEBUG
-#include <cstdio>
-static __device__ const bool a_debug_print = false;
-#endif
 
 #include "../../include/lily_sampler.h"
 #include "lily_math.cuh"
@@ -131,7 +127,6 @@ struct KArgs {
     uint32_t *tickets;             // [max_rows], zero between launches
     uint32_t *status_word;
     long long *phase_clocks;       // optional [max_rows, MAX_SLICES, LILY_PHASES] SM clock stamps
-    uint32_t debug_stop;           // debug builds only: leave after this phase (0 = run all)
     // Vocabulary shards. A shard launch (cand_out set) keeps each row's best
     // shard_k candidates and writes them, sorted, as a ShardRecord instead of
     // drawing; the merge kernel draws from the records of all shards.
@@ -200,9 +195,6 @@ struct alignas(16) SmemFixed {
     alignas(8) unsigned long long mbar[2];  // stream_rows_kernel: history marked; thread maxima written
     uint32_t lkey[LCAP];
     uint32_t lid[LCAP];
-#ifdef LILY_DEBUG
-    uint32_t dbg_hits, dbg_hit_warps, dbg_tighten;
-#endif
     RowCtx ctx;  // the row's parameters, for the out-of-line helpers
 };
 
@@ -380,12 +372,6 @@ __device__ __noinline__ void filter_adjust(SmemFixed *sm) {
     }
     __syncthreads();
     if (tid == 0) {
-#ifdef LILY_DEBUG
-        if (blockIdx.y < 2 && a_debug_print) {
-            printf("filter_adjust: n %u alive %u hits %u hit_warp_rounds %u tightens %u c_raw %g\n", n,
-                   sm->cnt, sm->dbg_hits, sm->dbg_hit_warps, sm->dbg_tighten, sm->c_raw);
-        }
-#endif
         sm->n = sm->cnt;
         sm->n_adj = sm->cnt;
         sm->ckey = sm->key;  // from here on the candidates live in key / id
@@ -584,10 +570,6 @@ __device__ __noinline__ void select_topk(SmemFixed *sm, uint32_t n, uint32_t k) 
     if (tid == 0) {
         if (sm->cnt != k) {
             sm->err = ROW_INTERNAL;
-#ifdef LILY_DEBUG
-            printf("select_topk: n %u k %u cnt %u kstar %08x istar %08x count_eq %u remaining %u\n", n, k,
-                   sm->cnt, kstar, istar, count_eq, remaining);
-#endif
         }
         sm->n = k;
         sm->n_adj = k;
@@ -1970,9 +1952,6 @@ __device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, c
         sm->ccap = CAP;
         sm->u_draw = a.uniforms ? u_row : uniform_for(P.seed, step_row);
         sm->lean_abort = 0;
-#ifdef LILY_DEBUG
-        sm->dbg_hits = sm->dbg_hit_warps = sm->dbg_tighten = 0;
-#endif
     }
     if (c.use_pen) {
         if (table_mode) {
@@ -2071,9 +2050,6 @@ __device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, c
     }
     __syncthreads();
     LILY_STAMP(PH_BITMAPS);
-#ifdef LILY_DEBUG
-    if (a.debug_stop == 1u) return;
-#endif
 
     // ---- C0'. small k, penalties that only lower: two passes over the slice
     // Pass 1 keeps each thread's largest logit (one packed max per round).
@@ -2127,9 +2103,6 @@ __device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, c
             }
             cp_async_wait<0>();
         }
-#ifdef LILY_DEBUG
-        if (a.debug_stop == 6u) return;
-#endif
         LILY_STAMP(PH_PASS1);
         // A NaN anywhere, or fewer than k threads with a logit: the general path.
         const uint32_t have = (uint32_t)__syncthreads_count(best_r != NONE) * (lean_wide ? 3u : 1u);
@@ -2343,9 +2316,6 @@ __device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, c
     }
     }  // !lean
     LILY_STAMP(PH_FIRST_THRESHOLD);
-#ifdef LILY_DEBUG
-    if (a.debug_stop == 2u) return;
-#endif
 
     // ---- B. ids on the bias / ban lists, each once (adjusted right away)
     if (c.has_special) {
@@ -2435,9 +2405,6 @@ __device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, c
         // A thread looks closer when its largest logit beats the threshold (in
         // a partial round: when it holds any logit at all).
         c_raw = *reinterpret_cast<volatile float *>(&sm->c_raw);
-#ifdef LILY_DEBUG
-        if (a.debug_stop == 5u) c_raw = -neg_inf();  // nothing passes: the bare streaming loop
-#endif
         bool hit = full ? !(frag_max<T>(cur) <= c_raw) : base < c.hi;
         if (always_seen && !hit && full) {
             const uint32_t off = base - c.lo;
@@ -2573,9 +2540,6 @@ __device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, c
     __syncthreads();
 
     LILY_STAMP(PH_STREAM);
-#ifdef LILY_DEBUG
-    if (a.debug_stop == 3u) return;
-#endif
     if (tid < 32u && sm->th_new != 0u) {
         tighten(sm);
     }
@@ -2622,9 +2586,6 @@ __device__ __forceinline__ void sample_row(const KArgs &a, const uint32_t row, c
         n = c.k;
     }
     LILY_STAMP(PH_LOCAL_SELECT);
-#ifdef LILY_DEBUG
-    if (a.debug_stop == 4u) return;
-#endif
 
     // ---- D. merge the slices
     if (n_slices > 1u) {

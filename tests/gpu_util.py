@@ -7,6 +7,7 @@ import numpy as np
 import oracle
 
 K_CAP = 1024
+POISON = 0x5A5A5A5A
 
 
 def t_u32(torch, a, device="cuda"):
@@ -41,8 +42,12 @@ def run_batch(torch, lily, scratch, batch, want_kept=True, count_slots=None, use
               params_on_device=False):
     rows = batch.logits.shape[0]
     logits = t_logits(torch, batch)
-    out = torch.full((rows + 2,), 0x5A5A5A5A, dtype=torch.int32, device="cuda")
-    status = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    # Every output buffer sits between poisoned guard words (rows): the stand-in
+    # for a memory checker, which this GPU pool does not offer.
+    out = torch.full((rows + 2,), POISON, dtype=torch.int32, device="cuda")
+    status_g = torch.full((rows + 2,), POISON, dtype=torch.int32, device="cuda")
+    status = status_g[1:rows + 1]
+    status.fill_(-1)
     kw = {}
     if batch.history is not None:
         kw["history_ids"] = t_u32(torch, batch.history)
@@ -56,10 +61,17 @@ def run_batch(torch, lily, scratch, batch, want_kept=True, count_slots=None, use
         kw["ban_len"] = t_u32(torch, batch.ban_len)
     if batch.forced is not None:
         kw["forced_ids"] = torch.from_numpy(batch.forced).to("cuda")
+    guards = [status_g]
     if want_kept:
-        kw["kept_n"] = torch.zeros(rows, dtype=torch.int32, device="cuda")
-        kw["kept_ids"] = torch.zeros((rows, K_CAP), dtype=torch.int32, device="cuda")
-        kw["kept_probs"] = torch.zeros((rows, K_CAP), dtype=torch.float32, device="cuda")
+        kept_n_g = torch.full((rows + 2,), POISON, dtype=torch.int32, device="cuda")
+        kept_ids_g = torch.full((rows + 2, K_CAP), POISON, dtype=torch.int32, device="cuda")
+        kept_probs_g = torch.full((rows + 2, K_CAP), POISON, dtype=torch.int32, device="cuda")
+        for g in (kept_n_g, kept_ids_g, kept_probs_g):
+            g[1:rows + 1].zero_()
+        guards += [kept_n_g, kept_ids_g, kept_probs_g]
+        kw["kept_n"] = kept_n_g[1:rows + 1]
+        kw["kept_ids"] = kept_ids_g[1:rows + 1]
+        kw["kept_probs"] = kept_probs_g[1:rows + 1].view(torch.float32)
     if count_slots is not None:
         kw["count_slots"] = count_slots
     params = make_params(lily, batch)
@@ -76,7 +88,10 @@ def run_batch(torch, lily, scratch, batch, want_kept=True, count_slots=None, use
     scratch.sample_batch(logits, params, out[1:rows + 1], out_status=status, **kw)
     torch.cuda.synchronize()
     o = np_u32(out)
-    assert o[0] == 0x5A5A5A5A and o[rows + 1] == 0x5A5A5A5A, "the kernel wrote outside out_ids"
+    assert o[0] == POISON and o[rows + 1] == POISON, "the kernel wrote outside out_ids"
+    for g in guards:
+        edge = np_u32(torch.stack([g[0].reshape(-1), g[rows + 1].reshape(-1)]))
+        assert (edge == POISON).all(), "the kernel wrote outside an output buffer"
     res = Result(o[1:rows + 1].copy(), np_u32(status))
     if want_kept:
         res.kept_n = np_u32(kw["kept_n"])
