@@ -391,8 +391,8 @@ def main():
     kernel_ms = total_ms / args.steps  # average launch duration over the timed region (one launch per step)
     peak, peak_kind = peaks()
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    kernel_name = ("stream_rows_kernel<bf16> (one block per row)" if n_here > 148
-                   else "sample_rows_kernel<bf16, vec> (rows cut into slices)")
+    kernel_name = ("stream_rows_kernel<bf16> (one block per row)" if n_here * 8 > 148
+                   else "cluster_rows_kernel<bf16> (a cluster of eight blocks per row)")
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": ncu_traffic() if world == 1 else None,
                 "peak_kind": peak_kind, "kernel": kernel_name, "kernel_ms": kernel_ms,

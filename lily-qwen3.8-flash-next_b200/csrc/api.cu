@@ -56,6 +56,7 @@ struct lily_sampler {
     uint32_t *tickets = nullptr;
     uint32_t *status_word = nullptr;
     char *spill = nullptr;  // parameters of rows the small-batch kernel hands to the general code
+    int max_clusters = -1;  // clusters of the small-batch kernel the GPU runs at once (-1: not asked yet)
     uint32_t *counts_scratch = nullptr;
     uint32_t *counts_table = nullptr;
     uint32_t *seen_table = nullptr;
@@ -198,20 +199,34 @@ int32_t raise_smem_limit(lily_sampler *h, Kernel kernel, uint32_t bit) {
 template <typename T, bool VEC>
 int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, uint32_t rows,
                    size_t smem) {
-    // A launch with a block slot's worth of rows or more, aligned logits, long
-    // rows and nothing special about the call goes to the large-batch kernel
-    // (which runs the general code itself for the rows it does not take).
+    // More rows than the small-batch kernel takes (and at least 16: fewer rows with
+    // lists or wide cuts are better off cut into slices), aligned logits, long rows
+    // and nothing special about the call: the kernel of one block per row (which runs
+    // the general code itself, on the whole row, for the rows it does not take).
+    // Below a block slot's worth of rows a block streams alone, and gets a deeper
+    // ring. (Short rows, unaligned logits, speculative and sharded calls: the
+    // general kernel, rows cut into slices.)
     constexpr uint32_t round = lily::Geo<T>::ROUND;
-    const bool stream = VEC && a.n_slices == 1u && a.vocab / round >= lily::STREAM_MIN_ROUNDS &&
-                        a.cand_out == nullptr && a.merge_in == nullptr && a.spec.n_spec == 0u &&
-                        a.extra_len == 0u;
+    const bool stream = VEC && a.vocab / round >= lily::STREAM_MIN_ROUNDS && a.cand_out == nullptr &&
+                        a.merge_in == nullptr && a.spec.n_spec == 0u && a.extra_len == 0u && rows >= 16u;
     if (stream) {
-        auto kernel = lily::stream_rows_kernel<T>;
-        const int32_t st = raise_smem_limit(h, kernel, 1u << (sizeof(T) == 4 ? 4 : 5));
+        lily::KArgs whole = a;
+        whole.n_slices = 1;
+        const size_t smem1 = smem_bytes(a.vocab, 1);
+        if (rows > (uint32_t)h->sm_count) {
+            auto kernel = lily::stream_rows_kernel<T, 2>;
+            const int32_t st = raise_smem_limit(h, kernel, 1u << (sizeof(T) == 4 ? 4 : 5));
+            if (st != LILY_OK) {
+                return st;
+            }
+            return launch_serialised(h, stream_, kernel, dim3(rows, 1, 1), smem1, whole);
+        }
+        auto kernel = lily::stream_rows_kernel<T, 3>;
+        const int32_t st = raise_smem_limit(h, kernel, 1u << (sizeof(T) == 4 ? 6 : 7));
         if (st != LILY_OK) {
             return st;
         }
-        return launch_serialised(h, stream_, kernel, dim3(rows, 1, 1), smem, a);
+        return launch_serialised(h, stream_, kernel, dim3(rows, 1, 1), smem1, whole);
     }
     auto kernel = lily::sample_rows_kernel<T, VEC>;
     const int32_t st = raise_smem_limit(h, kernel, 1u << ((sizeof(T) == 4 ? 0 : 2) + (VEC ? 1 : 0)));
@@ -224,19 +239,54 @@ int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, 
 // Whether a call goes to the small-batch kernel (a cluster of eight blocks per
 // row): few enough rows for every cluster to have SMs of its own, aligned logits,
 // a vocabulary whose eighth fits a block's shared memory, a plain draw.
-bool cluster_call(const lily_sampler *h, const void *logits, uint64_t logits_ld, uint32_t dtype,
+size_t cluster_launch_smem(uint32_t vocab) {
+    const size_t own = lily::cluster_smem_bytes(vocab);
+    const size_t general = smem_bytes(vocab, 1);  // the leader may run the general row code
+    return own > general ? own : general;
+}
+
+// How many clusters of the small-batch kernel run at once: a launch of more
+// rows than that would take its rows in turns, which the kernel of one block per
+// row does not. (A cluster needs eight free SMs of one GPC.)
+int max_active_clusters(lily_sampler *h) {
+    if (h->max_clusters < 0) {
+        h->max_clusters = 0;
+        auto kernel = lily::cluster_rows_kernel<__nv_bfloat16>;
+        const size_t smem = cluster_launch_smem(h->vocab);
+        if (smem <= (size_t)h->max_smem &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->max_smem) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(lily::CL, 64, 1);
+            cfg.blockDim = dim3(lily::NT, 1, 1);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = lily::CL;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess) {
+                h->max_clusters = n;
+            }
+        }
+        (void)cudaGetLastError();
+    }
+    return h->max_clusters;
+}
+
+bool cluster_call(lily_sampler *h, const void *logits, uint64_t logits_ld, uint32_t dtype,
                   uint32_t rows, bool plain) {
     const size_t esize = dtype == LILY_F32 ? 4 : 2;
     const bool vec = (reinterpret_cast<uintptr_t>(logits) % 16u == 0u) && ((logits_ld * esize) % 16u == 0u);
-    return plain && vec && rows * lily::CL <= (uint32_t)h->sm_count &&
-           lily::cluster_slice_len(h->vocab) <= lily::CL_SLICE_MAX && h->vocab >= 4096u;
+    return plain && vec && lily::cluster_slice_len(h->vocab) <= lily::CL_SLICE_MAX && h->vocab >= 4096u &&
+           (int)rows <= max_active_clusters(h);
 }
 
 int32_t launch_cluster(lily_sampler *h, cudaStream_t stream, const lily::ClusterArgs &ca_, uint32_t rows,
                        uint32_t dtype) {
-    size_t smem = lily::cluster_smem_bytes(ca_.a.vocab);
-    const size_t general = smem_bytes(ca_.a.vocab, 1);  // the leader may run the general row code
-    smem = smem > general ? smem : general;
+    const size_t smem = cluster_launch_smem(ca_.a.vocab);
     if (smem > (size_t)h->max_smem) {
         return fail(h, LILY_ERR_CAPACITY, "vocabulary too large for the small-batch kernel");
     }

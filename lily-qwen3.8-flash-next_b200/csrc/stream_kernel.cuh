@@ -34,10 +34,12 @@ namespace lily {
 
 constexpr uint32_t STREAM_MIN_ROUNDS = 8;  // launches with shorter rows use sample_rows_kernel
 constexpr uint32_t STREAM_K_MAX = 64;      // finalize_warp holds two candidates per lane
-// Rounds of the ring in flight beyond the one being read. Two measured faster
-// than three (33.4 against 34.0 us per 256-row launch), and asking L2 for further
-// rounds ahead of the ring slower still: the stream is not short of requests.
-constexpr uint32_t AHEAD = 2;
+// AHEAD (template argument of the kernel): rounds of the ring in flight beyond the
+// one being read. With a block slot's worth of rows two measured faster than
+// three (33.4 against 34.0 us per 256-row launch; asking L2 for further rounds
+// ahead of the ring was slower still: the stream is not short of requests). With
+// fewer rows than SMs a block streams alone against the latency of its own
+// requests, and three are the better choice.
 
 __device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count) {
     const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
@@ -169,8 +171,9 @@ __device__ __forceinline__ uint32_t small_select(SmemFixed *sm, uint32_t n, uint
     return min(live, k);
 }
 
-template <typename T>
+template <typename T, uint32_t AHEAD>
 __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constant__ KArgs a) {
+    static_assert(AHEAD == 2u || AHEAD == 3u, "the ring has four stages");
     extern __shared__ uint4 smem_raw[];
     SmemFixed *sm = reinterpret_cast<SmemFixed *>(smem_raw);
     uint4 *ring = reinterpret_cast<uint4 *>(sm + 1);
@@ -242,7 +245,10 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     cp_async_commit();
     lean_copy_round(slot_a + ROUND_BYTES, src0 + ROUND_BYTES);
     cp_async_commit();
-    static_assert(AHEAD == 2u, "rounds 0 and 1 are on their way when the stream starts");
+    if (AHEAD == 3u) {
+        lean_copy_round(slot_b, src0 + 2u * ROUND_BYTES);
+        cp_async_commit();
+    }
 
     auto refuse = [&](uint32_t status) {
         if (tid == 0) {
