@@ -62,7 +62,7 @@ def peaks():
     return 6650.0, "fallback"
 
 
-def ncu_traffic(key="sample_rows_kernel_b256_dram_bytes_per_launch"):
+def ncu_traffic(key="stream_rows_kernel_b256_dram_bytes_per_launch"):
     """DRAM bytes per launch of a kernel from the committed ncu summary, if
     one has been recorded."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
