@@ -171,6 +171,11 @@ int32_t lily_sampler_write_counts(lily_sampler_t *h, void *stream, uint32_t slot
  * 14, 15: on the route that takes its threshold while the row streams,
  * thread 0 has the threshold / has collected what its earlier rounds hold
  * above it; 16 is the block's first instruction.
+ * The small-batch kernel (a cluster of eight blocks per row, block r of the
+ * cluster in place of slice r) stamps 16 entry, 0 slice loaded and cluster
+ * running, 1 history counted, 2 lists / penalties / block maximum, 3 cluster
+ * maximum, 9 histogram, 4 barrier, 5 histograms summed and k-th bin found,
+ * 10 candidates placed, 6 barrier, 11 ranked, 8 barrier, 7 draw written.
  */
 int32_t lily_sampler_read_phase_clocks(lily_sampler_t *h, void *stream, int64_t *host_out);
 

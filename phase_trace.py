@@ -23,6 +23,13 @@ NAMES = ["start", "bitmaps", "lists", "pass 2 / stream", "adjust + select", "mer
          "first threshold", "pass 1", "pass 1 met", "maxima", "search", "threshold set",
          "threshold taken", "collected", "entry"]
 ENTRY = 16
+# The small-batch kernel (a cluster of eight blocks per row) leaves its own stamps;
+# block r of a row's cluster is listed as "slice" r.
+CLUSTER_NAMES = {0: "slice loaded, cluster running", 1: "history counted", 2: "lists, penalties, block maximum",
+                 3: "cluster maximum", 9: "histogram", 4: "cluster barrier", 5: "histograms summed, k-th bin",
+                 10: "candidates placed in every block", 6: "cluster barrier", 11: "ranked within bins",
+                 8: "cluster barrier", 7: "draw written"}
+CLUSTER_ORDER = [16, 0, 1, 2, 3, 9, 4, 5, 10, 6, 11, 8, 7]
 # The order in which a block of the two-pass route reaches its stamps.
 ORDER = [16, 0, 1, 14, 15, 9, 10, 11, 12, 13, 8, 2, 3, 4, 5, 6, 7]
 
@@ -55,12 +62,13 @@ def trace(torch, lily, scratch, x, launches: int = 3):
     return clk
 
 
-def segments(stamps):
+def segments(stamps, cluster=False):
     """[(phase name, microseconds since the previous stamp)] of one block."""
-    out, prev = [], float(stamps[ORDER[0]])
-    for i in ORDER[1:]:
+    order, names = (CLUSTER_ORDER, CLUSTER_NAMES) if cluster else (ORDER, NAMES)
+    out, prev = [], float(stamps[order[0]])
+    for i in order[1:]:
         if stamps[i] != 0:
-            out.append((NAMES[i], (float(stamps[i]) - prev) / 1e3))
+            out.append((names[i], (float(stamps[i]) - prev) / 1e3))
             prev = float(stamps[i])
     return out
 
@@ -87,9 +95,11 @@ def main(argv) -> None:
                     if c[ENTRY] == 0:
                         continue
                     last = max(int(v) for v in c)
+                    # (The 4-row batch goes to the small-batch kernel: eight blocks per row.)
+                    cluster = clk.shape[0] <= 8 and c[13] == 0 and c[12] == 0
                     print(f"  row {r} block {sl}: enters {(c[ENTRY] - t0) / 1e3:5.1f}, leaves "
                           f"{(last - t0) / 1e3:5.1f} us after the launch's first block | " +
-                          " ".join(f"{n} {us:.1f}" for n, us in segments(c)))
+                          " | ".join(f"{n} {us:.1f}" for n, us in segments(c, cluster)))
     else:
         scratch = lily.SamplerScratch(w.VOCAB, max_rows=256, phase_clocks=True)
         clk = trace(torch, lily, scratch, w.config4_batch(), launches=4)
