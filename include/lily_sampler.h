@@ -46,7 +46,8 @@ enum lily_status {
     LILY_ERR_FAULT = -4,      /* an injected or latched fault (see inject_fault) */
     LILY_ERR_VOCAB = -5,      /* handles of different vocabularies */
     LILY_ERR_CUDA = 1,        /* a CUDA runtime call failed */
-    LILY_ERR_DEVICE_ROW = 2   /* a row reported an error word (see row status) */
+    LILY_ERR_DEVICE_ROW = 2,  /* a row reported an error word (see row status) */
+    LILY_ERR_TIMEOUT = 3      /* a bounded wait inside a kernel ran out (lily_sampler_status) */
 };
 
 /* Per-row status words written to `out_status` (0 = drawn normally). */
@@ -142,6 +143,26 @@ const char *lily_sampler_last_error(const lily_sampler_t *h);
 void lily_sampler_inject_fault(lily_sampler_t *h, int32_t code);
 void lily_sampler_clear_fault(lily_sampler_t *h);
 int32_t lily_sampler_status(lily_sampler_t *h, void *stream);
+
+/*
+ * src/metal.rs:856-861 wait_fence and :1276-1279 Fence::wait_until(value,
+ * timeout_ms): the reference bounds its waits on the GPU on the host side. Here
+ * the only waits are inside the LM-head kernel (one role of a block waiting for
+ * another's copies, conversions or multiplies), and each is bounded on the
+ * device: after `nanoseconds` (default and 0: one second) the block gives up,
+ * lets the copies and multiplies it still has in flight land, frees its tensor
+ * memory and returns. The launch completes like any other; the logits it was to
+ * write are not valid, and the next lily_sampler_status returns
+ * LILY_ERR_TIMEOUT (once: the status is cleared by reading it). The handle stays
+ * usable. The sampler's own kernels wait on nothing another block produces.
+ *
+ * inject_lost_copy is the device-side sibling of inject_fault, for tests: the
+ * next LM-head launch on this handle (and only that one) leaves out the copy of
+ * weight stage `stage` of its first block, so that the wait of the stage's
+ * consumers runs out. No reference counterpart.
+ */
+int32_t lily_sampler_set_wait_limit(lily_sampler_t *h, uint64_t nanoseconds);
+void lily_sampler_inject_lost_copy(lily_sampler_t *h, uint32_t stage);
 
 /*
  * src/kernels/sample.rs:145-174 reset_counts / uncount / copy_counts_from on

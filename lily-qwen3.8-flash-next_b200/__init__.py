@@ -28,7 +28,7 @@ MAX_SLICES, PHASES = 128, 20
 
 OK = 0
 ERR_ARG, ERR_PARAMS, ERR_CAPACITY, ERR_FAULT, ERR_VOCAB = -1, -2, -3, -4, -5
-ERR_CUDA, ERR_DEVICE_ROW = 1, 2
+ERR_CUDA, ERR_DEVICE_ROW, ERR_TIMEOUT = 1, 2, 3
 ROW_OK, ROW_NAN, ROW_NONFINITE, ROW_PARAMS, ROW_LIST, ROW_FORCED = 0, 1, 2, 3, 4, 16
 
 
@@ -160,6 +160,10 @@ def lib():
         L.lily_sampler_last_error.restype = C.c_char_p
         L.lily_sampler_inject_fault.argtypes = [C.c_void_p, C.c_int32]
         L.lily_sampler_inject_fault.restype = None
+        L.lily_sampler_set_wait_limit.argtypes = [C.c_void_p, C.c_uint64]
+        L.lily_sampler_set_wait_limit.restype = C.c_int32
+        L.lily_sampler_inject_lost_copy.argtypes = [C.c_void_p, C.c_uint32]
+        L.lily_sampler_inject_lost_copy.restype = None
         L.lily_sampler_clear_fault.argtypes = [C.c_void_p]
         L.lily_sampler_clear_fault.restype = None
         L.lily_sampler_status.argtypes = [C.c_void_p, C.c_void_p]
@@ -307,6 +311,14 @@ class SamplerScratch:
 
     def status(self, stream=None) -> int:
         return int(lib().lily_sampler_status(self._h, _stream_ptr(stream)))
+
+    # -- bounded waits of the LM-head kernel (src/metal.rs:856-861, 1276-1279)
+    def set_wait_limit(self, nanoseconds: int):
+        self._check(lib().lily_sampler_set_wait_limit(self._h, nanoseconds))
+
+    def inject_lost_copy(self, stage: int):
+        """Test hook: the next LM-head launch leaves out one weight copy of its first block."""
+        lib().lily_sampler_inject_lost_copy(self._h, stage)
 
     # -- histogram slots (src/kernels/sample.rs:145-174)
     def reset_counts(self, slot: int = 0, stream=None):

@@ -49,6 +49,8 @@ struct lily_sampler {
     uint32_t vocab = 0, max_rows = 0, max_history = 0, max_list = 0, flags = 0;
     std::string last_error;
     int32_t fault = 0;
+    uint64_t wait_ns = 1000000000ull;     // bound of the waits inside the LM-head kernel
+    uint32_t lost_stage = 0xFFFFFFFFu;    // test hook: a weight copy the next head launch leaves out
     int sm_count = 0;
     int max_smem = 0;
     uint2 *part = nullptr;
@@ -606,6 +608,20 @@ void lily_sampler_clear_fault(lily_sampler_t *h) {
     }
 }
 
+int32_t lily_sampler_set_wait_limit(lily_sampler_t *h, uint64_t nanoseconds) {
+    if (h == nullptr) {
+        return LILY_ERR_ARG;
+    }
+    h->wait_ns = nanoseconds == 0 ? 1000000000ull : nanoseconds;
+    return LILY_OK;
+}
+
+void lily_sampler_inject_lost_copy(lily_sampler_t *h, uint32_t stage) {
+    if (h) {
+        h->lost_stage = stage;
+    }
+}
+
 int32_t lily_sampler_status(lily_sampler_t *h, void *stream_) {
     if (h == nullptr) {
         return LILY_ERR_ARG;
@@ -618,6 +634,9 @@ int32_t lily_sampler_status(lily_sampler_t *h, void *stream_) {
     CU(h, cudaMemcpyAsync(h->h_status, h->status_word, 4, cudaMemcpyDeviceToHost, stream));
     CU(h, cudaMemsetAsync(h->status_word, 0, 4, stream));
     CU(h, cudaStreamSynchronize(stream));
+    if (*h->h_status & (1u << lily_head::STATUS_TIMEOUT_BIT)) {
+        return fail(h, LILY_ERR_TIMEOUT, "a wait inside the LM-head kernel ran out; its logits are not valid");
+    }
     if (*h->h_status != 0u) {
         char buf[96];
         std::snprintf(buf, sizeof buf, "rows reported error bits 0x%x", *h->h_status);
@@ -1038,6 +1057,9 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
     a.out = out;
     a.ldo = out_ld;
     a.status_word = h->status_word;
+    a.wait_ns = h->wait_ns;
+    a.lost_stage = h->lost_stage;
+    h->lost_stage = 0xFFFFFFFFu;  // one launch only
     const uint32_t tiles = (head->rows + lily_head::TILE_ROWS - 1) / lily_head::TILE_ROWS;
     const uint32_t grid = tiles < (uint32_t)h->sm_count ? tiles : (uint32_t)h->sm_count;
     kernel<<<grid, lily_head::THREADS, lily_head::Smem::BYTES, stream>>>(a);

@@ -100,7 +100,8 @@ struct Smem {
     // q + 2), the loader (slot free for q + 8) and the epilogue (sums ready).
     static constexpr uint32_t DONE = H_FULL + 8 * H_SLOTS;          // [DONE_SLOTS]
     static constexpr uint32_t ACC_EMPTY = DONE + 8 * DONE_SLOTS;    // [ACC_BUFS]
-    static constexpr uint32_t TMEM_ADDR = ACC_EMPTY + 8 * ACC_BUFS;
+    static constexpr uint32_t FINAL = ACC_EMPTY + 8 * ACC_BUFS;     // [2] an issuing thread's last commit
+    static constexpr uint32_t TMEM_ADDR = FINAL + 8 * 2;
     static constexpr uint32_t ABORT = TMEM_ADDR + 4;
     static constexpr uint32_t END = ABORT + 4;
     static constexpr uint32_t BYTES = END + 1024;  // room to align the base
@@ -120,6 +121,10 @@ struct Args {
     float *out;                 // [tokens, ldo]
     uint64_t ldo;
     uint32_t *status_word;
+    uint64_t wait_ns;           // the bound of every wait inside the kernel
+    // Test hook: block 0 does not ask for the weights of this stage (~0: none),
+    // so that the wait of their consumers runs out.
+    uint32_t lost_stage;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -140,9 +145,14 @@ __device__ __forceinline__ uint64_t global_ns() {
     return t;
 }
 
-// Waits for the phase with the given parity to complete, for at most about a
-// second; once any wait of the block has run out, none blocks any more.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_word) {
+// Waits for the phase with the given parity to complete, for at most
+// `limit_ns`; once any wait of the block has run out, none blocks any more.
+// Returns true if it gave up (this wait ran out, or another had): the caller
+// then leaves its loop. A phase that is complete at the first look returns
+// false without reading the abort word, so the path that never waits pays
+// nothing for the bound.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_word,
+                                          uint64_t limit_ns) {
     uint64_t t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         uint32_t done;
@@ -154,19 +164,40 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
             : "r"(bar), "r"(parity)
             : "memory");
         if (done) {
-            return;
+            return false;
         }
         if ((spin & 15u) == 15u) {
             if (*abort_word) {
-                return;
+                return true;
             }
             const uint64_t now = global_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > 1000000000ull) {
+            } else if (now - t0 > limit_ns) {
                 *abort_word = 1u;
-                return;
+                return true;
             }
+        }
+    }
+}
+
+// The same wait for the way out of a block that has given up: it does not look
+// at the abort word (which is set by then), only at its own clock. Used to let
+// copies and multiplies that are still in flight land before the block frees
+// its tensor memory and returns.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+    const uint64_t t0 = global_ns();
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done || ((spin & 15u) == 15u && global_ns() - t0 > limit_ns)) {
+            return;
         }
     }
 }
@@ -314,6 +345,7 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
     const uint32_t n_tiles = (a.rows + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
     const uint32_t total_groups = my_tiles * groups;
+    const uint64_t wait_ns = a.wait_ns;
 
     if (tid == 0) {
         for (int s = 0; s < RAW_STAGES; ++s) {
@@ -332,6 +364,8 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
         for (int b = 0; b < ACC_BUFS; ++b) {
             mbar_init(base + Smem::ACC_EMPTY + 8 * b, N_EPI_WARPS);
         }
+        mbar_init(base + Smem::FINAL, 1);
+        mbar_init(base + Smem::FINAL + 8, 1);
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -356,11 +390,17 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             LM_T0();
             for (uint32_t q = 0; q < total_groups; ++q) {
                 const uint32_t as = q % A_SLOTS, hs = q % H_SLOTS, b = q % ACC_BUFS;
-                mbar_wait(base + Smem::H_FULL + 8 * hs, (q / H_SLOTS) & 1u, abort_word);
+                if (mbar_wait(base + Smem::H_FULL + 8 * hs, (q / H_SLOTS) & 1u, abort_word, wait_ns)) {
+                    break;
+                }
                 LM_ACC(tw_h);
-                mbar_wait(base + Smem::ACC_EMPTY + 8 * b, ((q / ACC_BUFS) & 1u) ^ 1u, abort_word);
+                if (mbar_wait(base + Smem::ACC_EMPTY + 8 * b, ((q / ACC_BUFS) & 1u) ^ 1u, abort_word, wait_ns)) {
+                    break;
+                }
                 LM_ACC(tw_acc);
-                mbar_wait(base + Smem::A_FULL + 8 * as, (q / A_SLOTS) & 1u, abort_word);
+                if (mbar_wait(base + Smem::A_FULL + 8 * as, (q / A_SLOTS) & 1u, abort_word, wait_ns)) {
+                    break;
+                }
                 LM_ACC(tw_a);
                 tc_fence_after();
                 const uint32_t h_addr = base + Smem::HID + hs * H_BYTES;
@@ -374,6 +414,12 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                 mma_commit(base + Smem::DONE + 8 * (q % DONE_SLOTS));
                 LM_ACC(t_commit);
             }
+            // The multiplies this thread has issued must have run before the tensor
+            // memory they use is freed. On the normal way out the epilogue has seen
+            // to that already and this wait finds its phase complete; it matters
+            // when the block has given up.
+            mma_commit(base + Smem::FINAL + 8 * half);
+            mbar_drain(base + Smem::FINAL + 8 * half, 0u, wait_ns);
         }
         __syncwarp();
     } else if (warp == WARP_LOAD) {
@@ -383,14 +429,24 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             const uint32_t stages_per_tile = groups / RAW_GROUPS;
             const uint32_t n_stages = my_tiles * stages_per_tile;
             long long tw_re = 0, tw_he = 0;
+            // The copies asked for last, per slot (bit s: slot s has one; its phase's
+            // parity beside it): what the way out has to wait for if the block gives up.
+            uint32_t raw_asked = 0, raw_parity = 0, h_asked = 0, h_parity = 0;
+            bool gave_up = false;
             LM_T0();
-            for (uint32_t i = 0; i < n_stages; ++i) {
+            for (uint32_t i = 0; i < n_stages && !gave_up; ++i) {
                 const uint32_t st = i % RAW_STAGES;
                 const uint32_t tile = blockIdx.x + (i / stages_per_tile) * gridDim.x;
                 const uint32_t kb = (i % stages_per_tile) * (GROUP_K * RAW_GROUPS);
-                mbar_wait(base + Smem::RAW_EMPTY + 8 * st, ((i / RAW_STAGES) & 1u) ^ 1u, abort_word);
+                if (mbar_wait(base + Smem::RAW_EMPTY + 8 * st, ((i / RAW_STAGES) & 1u) ^ 1u, abort_word, wait_ns)) {
+                    break;
+                }
                 LM_ACC(tw_re);
-                if (!(VARIANT & 16)) {
+                if (i == a.lost_stage && blockIdx.x == 0) {
+                    // test hook: nothing is asked for, the stage never fills
+                } else if (!(VARIANT & 16)) {
+                    raw_asked |= 1u << st;
+                    raw_parity = (raw_parity & ~(1u << st)) | (((i / RAW_STAGES) & 1u) << st);
                     mbar_expect_tx(base + Smem::RAW_FULL + 8 * st, RAW_STAGE_BYTES);
                     tma_load_2d(base + Smem::RAW + st * RAW_STAGE_BYTES, &a.w_map, base + Smem::RAW_FULL + 8 * st,
                                 (int32_t)kb, (int32_t)(tile * TILE_ROWS));
@@ -402,15 +458,36 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                     const uint32_t q = i * RAW_GROUPS + gg;
                     const uint32_t hs = q % H_SLOTS;
                     if (q >= (uint32_t)H_SLOTS) {  // the slot's previous group has been multiplied
-                        mbar_wait(base + Smem::DONE + 8 * hs, ((q / H_SLOTS) & 1u) ^ 1u, abort_word);
+                        if (mbar_wait(base + Smem::DONE + 8 * hs, ((q / H_SLOTS) & 1u) ^ 1u, abort_word, wait_ns)) {
+                            gave_up = true;
+                            break;
+                        }
                     }
                     LM_ACC(tw_he);
                     if (!(VARIANT & 8)) {
+                        h_asked |= 1u << hs;
+                        h_parity = (h_parity & ~(1u << hs)) | (((q / H_SLOTS) & 1u) << hs);
                         mbar_expect_tx(base + Smem::H_FULL + 8 * hs, H_BYTES);
                         tma_load_2d(base + Smem::HID + hs * H_BYTES, &a.h_map, base + Smem::H_FULL + 8 * hs,
                                     (int32_t)(kb + gg * GROUP_K), 0);
                     } else {
                         mbar_arrive(base + Smem::H_FULL + 8 * hs);
+                    }
+                }
+            }
+            if (*abort_word) {
+                // The block has given up: the copies asked for land in this block's
+                // shared memory, so it stays until they have.
+#pragma unroll
+                for (uint32_t s2 = 0; s2 < (uint32_t)RAW_STAGES; ++s2) {
+                    if ((raw_asked >> s2) & 1u) {
+                        mbar_drain(base + Smem::RAW_FULL + 8 * s2, (raw_parity >> s2) & 1u, wait_ns);
+                    }
+                }
+#pragma unroll
+                for (uint32_t s2 = 0; s2 < (uint32_t)H_SLOTS; ++s2) {
+                    if ((h_asked >> s2) & 1u) {
+                        mbar_drain(base + Smem::H_FULL + 8 * s2, (h_parity >> s2) & 1u, wait_ns);
                     }
                 }
             }
@@ -426,12 +503,16 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
         const uint32_t stages_per_tile = groups / RAW_GROUPS;
         const uint32_t n_stages = my_tiles * stages_per_tile;
         long long tw_raw = 0, tw_ae = 0, t_conv = 0, t_st = 0;
+        bool conv_gave_up = false;
         LM_T0();
         for (uint32_t i = 0; i < n_stages; ++i) {
             const uint32_t st = i % RAW_STAGES;
-            mbar_wait(base + Smem::RAW_FULL + 8 * st, (i / RAW_STAGES) & 1u, abort_word);
+            // (the vote takes the place of a __syncwarp: the lanes leave together)
+            if (__any_sync(0xFFFFFFFFu, mbar_wait(base + Smem::RAW_FULL + 8 * st, (i / RAW_STAGES) & 1u, abort_word,
+                                                  wait_ns))) {
+                break;
+            }
             LM_ACC(tw_raw);
-            __syncwarp();
             const uint32_t raw_row = base + Smem::RAW + st * RAW_STAGE_BYTES + trow * 128u;
 #pragma unroll 1
             for (uint32_t gg = 0; gg < RAW_GROUPS; ++gg) {
@@ -462,12 +543,16 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                     }
                 }
                 LM_ACC(t_conv);
+                bool gave_up = false;
                 if (q >= (uint32_t)A_SLOTS) {  // group q - 2, the slot's last user, has been multiplied
-                    mbar_wait(base + Smem::DONE + 8 * ((q - A_SLOTS) % DONE_SLOTS),
-                              ((q - A_SLOTS) / DONE_SLOTS) & 1u, abort_word);
+                    gave_up = mbar_wait(base + Smem::DONE + 8 * ((q - A_SLOTS) % DONE_SLOTS),
+                                        ((q - A_SLOTS) / DONE_SLOTS) & 1u, abort_word, wait_ns);
                 }
                 LM_ACC(tw_ae);
-                __syncwarp();
+                if (__any_sync(0xFFFFFFFFu, gave_up)) {
+                    conv_gave_up = true;
+                    break;
+                }
                 tc_fence_after();
                 const uint32_t a_addr = tmem + t_lane + A_COL0 + as * A_COLS + half * (A_COLS / 2);
                 tmem_st16(a_addr, o[0]);
@@ -480,6 +565,9 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                     mbar_arrive(base + Smem::A_FULL + 8 * as);
                 }
                 LM_ACC(t_st);
+            }
+            if (conv_gave_up) {
+                break;
             }
             // The stage's bytes are in registers or tensor memory: the slot may be refilled.
             __syncwarp();
@@ -534,9 +622,11 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                     const uint32_t b = q % ACC_BUFS;
                     const float s = __uint_as_float((gi & 1u) ? (sw[gi >> 1] & 0xFFFF0000u) : (sw[gi >> 1] << 16));
                     const uint64_t s2 = pack2(__float_as_uint(s), __float_as_uint(s));
-                    mbar_wait(base + Smem::DONE + 8 * (q % DONE_SLOTS), (q / DONE_SLOTS) & 1u, abort_word);
+                    if (__any_sync(0xFFFFFFFFu, mbar_wait(base + Smem::DONE + 8 * (q % DONE_SLOTS),
+                                                          (q / DONE_SLOTS) & 1u, abort_word, wait_ns))) {
+                        goto epilogue_out;  // the block has given up: nothing more is read or written
+                    }
                     LM_ACC(tw_af);
-                    __syncwarp();
                     tc_fence_after();
                     const uint32_t taddr = tmem + t_lane + b * ACC_COLS + half * TOK + tok0;
                     if (!(VARIANT & 1)) {
@@ -576,6 +666,7 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             }
             LM_ACC(t_store);
         }
+    epilogue_out:;
     }
 
     tc_fence_before();

@@ -281,3 +281,45 @@ def test_config5_full_size(cuda, lily):
     assert len(differ) <= 2
     for r, g, o, near, gap in differ:
         assert near or gap < 1e-5, f"row {r}: token {g} vs {o} with no boundary near"
+
+
+def test_a_wait_that_runs_out_returns_with_a_named_status(cuda, lily):
+    """Failure detection without a fault. The head kernel's roles wait on one
+    another through barriers in shared memory, every wait bounded on the device
+    (the reference bounds its waits on the host: src/metal.rs:856-861,
+    1276-1279). The test hook leaves out one weight copy of the first block, so
+    the wait of that stage's consumers runs out at a 2 ms limit: the launch has
+    to complete, the handle has to report LILY_ERR_TIMEOUT once and stay
+    usable, and the next launch (which needs the tensor memory the block that
+    gave up held) has to be bit-exact."""
+    torch = cuda
+    tokens, hidden, rows = 64, 1024, 16_384
+    rng = np.random.default_rng([73, tokens, hidden, rows])
+    h, w, s = _head_inputs(torch, rng, tokens, hidden, rows, exact=True)
+    want = oracle.lmhead_int8(h, w, s, 64, 0, rows)
+    scratch = lily.SamplerScratch(rows, max_rows=64)
+    wd, sd, hd = torch.from_numpy(w).cuda(), _bf16(torch, s), _bf16(torch, h)
+    out = torch.zeros((tokens, rows), dtype=torch.float32, device="cuda")
+
+    scratch.set_wait_limit(2_000_000)
+    scratch.inject_lost_copy(3)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    scratch.lmhead_logits(wd, sd, hd, out)
+    t1.record()
+    torch.cuda.synchronize()
+    assert 1.5 < t0.elapsed_time(t1) < 200.0, "the block gives up after its limit, not after a second"
+    assert scratch.status() == lily.ERR_TIMEOUT
+    assert scratch.status() == lily.OK, "reading the status clears it"
+    # The other blocks were not disturbed: their tiles of 256 rows are exact.
+    got = out.cpu().numpy()
+    assert np.array_equal(got[:, 256:].view(np.uint32), want[:, 256:].view(np.uint32))
+
+    # The hook was for one launch; the default limit is back with 0.
+    scratch.set_wait_limit(0)
+    out.zero_()
+    scratch.lmhead_logits(wd, sd, hd, out)
+    torch.cuda.synchronize()
+    assert scratch.status() == lily.OK
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    scratch.close()
