@@ -206,11 +206,13 @@ int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, 
     // and nothing special about the call: the kernel of one block per row (which runs
     // the general code itself, on the whole row, for the rows it does not take).
     // Below a block slot's worth of rows a block streams alone, and gets a deeper
-    // ring. (Short rows, unaligned logits, speculative and sharded calls: the
-    // general kernel, rows cut into slices.)
+    // ring. A vocabulary shard's candidate launch goes the same way and ends in the
+    // rows' records. (Short rows, unaligned logits, speculative calls and the merge
+    // of shards: the general kernel, rows cut into slices.)
     constexpr uint32_t round = lily::Geo<T>::ROUND;
-    const bool stream = VEC && a.vocab / round >= lily::STREAM_MIN_ROUNDS && a.cand_out == nullptr &&
-                        a.merge_in == nullptr && a.spec.n_spec == 0u && a.extra_len == 0u && rows >= 16u;
+    const bool stream = VEC && a.vocab / round >= lily::STREAM_MIN_ROUNDS && a.merge_in == nullptr &&
+                        a.spec.n_spec == 0u && a.extra_len == 0u && rows >= 16u &&
+                        (a.cand_out == nullptr || a.shard_k <= lily::STREAM_K_MAX);
     if (stream) {
         lily::KArgs whole = a;
         whole.n_slices = 1;

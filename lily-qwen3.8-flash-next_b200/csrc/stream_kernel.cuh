@@ -250,8 +250,22 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
         cp_async_commit();
     }
 
-    auto refuse = [&](uint32_t status) {
+    // A vocabulary shard's launch ends in a record per row, not in a draw.
+    auto empty_record = [&](uint32_t status) {
+        ShardRecord *rec = a.cand_out + row;
+        for (uint32_t i = tid; i < LILY_SHARD_CANDIDATES; i += NT) {
+            rec->cand[i] = make_uint2(0u, 0xFFFFFFFFu);
+        }
         if (tid == 0) {
+            rec->max_adj = neg_inf();
+            rec->sum_exp = 0.0f;
+            atomicOr(a.status_word, 1u << (status & 31u));
+        }
+    };
+    auto refuse = [&](uint32_t status) {
+        if (a.cand_out) {
+            empty_record(status);
+        } else if (tid == 0) {
             a.out_ids[row] = status == LILY_ROW_FORCED ? (uint32_t)forced : 0xFFFFFFFFu;
             if (a.out_status) {
                 a.out_status[row] = status;
@@ -292,7 +306,9 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     const bool greedy = P.temperature <= 0.0f || P.top_k == 1u;
     const bool use_pen = P.presence_penalty != 0.0f || P.frequency_penalty != 0.0f ||
                          P.repetition_penalty != 1.0f;
-    const uint32_t k = greedy ? 1u : (P.top_k == 0u ? KCAP : min(P.top_k, KCAP));
+    // (A shard keeps shard_k candidates of a sampled row, whatever its top_k: the
+    // host made sure that top_k fits.)
+    const uint32_t k = greedy ? 1u : a.cand_out ? a.shard_k : (P.top_k == 0u ? KCAP : min(P.top_k, KCAP));
     const bool monotone = P.repetition_penalty >= 1.0f && !(__float_as_uint(P.presence_penalty) >> 31) &&
                           !(__float_as_uint(P.frequency_penalty) >> 31);
     const bool need_counts = use_pen && P.frequency_penalty != 0.0f;
@@ -637,6 +653,28 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     const uint32_t n = small_select(sm, n_raw, k);
     if (stamps && tid == 0) {
         stamps[PH_LOCAL_SELECT] = global_ns();
+    }
+    if (a.cand_out) {
+        if (n == 0u) {
+            empty_record(sm->err ? sm->err : ROW_INTERNAL);
+        } else if (tid < 32u) {
+            // The sorted candidates are the row's record (ids in the whole vocabulary's numbering).
+            ShardRecord *rec = a.cand_out + row;
+            for (uint32_t i = tid; i < LILY_SHARD_CANDIDATES; i += 32u) {
+                rec->cand[i] = i < n ? make_uint2(sm->key[i], sm->id[i] + a.id_offset) : make_uint2(0u, 0xFFFFFFFFu);
+            }
+            if (tid == 0) {
+                rec->max_adj = float_of_key(sm->key[0]);
+                rec->sum_exp = 0.0f;
+                if (sm->err) {
+                    atomicOr(a.status_word, 1u << (sm->err & 31u));
+                }
+                if (stamps) {
+                    stamps[PH_END] = global_ns();
+                }
+            }
+        }
+        return;
     }
     if (n == 0u) {
         // Nothing reached the buffer (a bug, never expected): an error row.

@@ -146,6 +146,37 @@ def test_sharded_draw_equals_the_whole_row_draw(cuda, lily, n_shards, dtype):
     _check_against_oracle(lf, plist, u, got)
 
 
+@pytest.mark.parametrize("n_shards", [2, 4])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_sharded_draw_of_a_batch_the_one_block_per_row_kernel_takes(cuda, lily, n_shards, dtype):
+    """From 16 rows on, with shards of eight rounds and more, the candidate launch is
+    the kernel of one block per row, which ends in the rows' records; greedy rows,
+    a top-k of 64 and equal logits across the shards' borders included."""
+    torch = cuda
+    import workloads as wl
+
+    rows, vocab = 24, 262_144
+    rng = np.random.default_rng([74, n_shards])
+    x = wl.zipf_logits(rng, rows, vocab)
+    per = vocab // n_shards
+    for r in range(0, rows, 3):  # the row's largest value again, just across a border
+        x[r, per + (r % 5)] = x[r].max()
+    plist = [dict(temperature=[0.7, 1.0, 0.0, 0.9][r % 4], top_k=[40, 64, 1, 7][r % 4],
+                  top_p=[0.95, 1.0, 1.0, 0.8][r % 4], min_p=[0.0, 0.02, 0.0, 0.0][r % 4], seed=r)
+             for r in range(rows)]
+    u = np.array([oracle.uniform_for(700 + r, 5) for r in range(rows)], dtype=np.float32)
+    if dtype == "bf16":
+        bits = wl.to_bf16_bits(x)
+        logits = _bf16(torch, bits)
+        lf = oracle.widen_bf16(bits)
+    else:
+        logits = t_f32(torch, x)
+        lf = x
+    params = [lily.SamplingParams(**p) for p in plist]
+    got = _sharded_draw(cuda, lily, logits, params, u, n_shards)
+    _check_against_oracle(lf, plist, u, got)
+
+
 def test_sharded_draw_with_ties_across_shards(cuda, lily):
     """Equal logits in different shards: the lower id wins, as in one pass."""
     torch = cuda
