@@ -225,6 +225,16 @@ int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, 
             }
             return launch_serialised(h, stream_, kernel, dim3(rows, 1, 1), smem1, whole);
         }
+        // A block per SM at most: the deep ring, if the SM's shared memory holds it.
+        const size_t deep = ((smem1 + 15u) & ~size_t(15)) + lily::StreamDepth<7>::EXTRA_BYTES;
+        if (deep <= (size_t)h->max_smem) {
+            auto kernel = lily::stream_rows_kernel<T, 7>;
+            const int32_t st = raise_smem_limit(h, kernel, 1u << (sizeof(T) == 4 ? 10 : 11));
+            if (st != LILY_OK) {
+                return st;
+            }
+            return launch_serialised(h, stream_, kernel, dim3(rows, 1, 1), deep, whole);
+        }
         auto kernel = lily::stream_rows_kernel<T, 3>;
         const int32_t st = raise_smem_limit(h, kernel, 1u << (sizeof(T) == 4 ? 6 : 7));
         if (st != LILY_OK) {

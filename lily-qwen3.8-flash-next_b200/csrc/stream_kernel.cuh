@@ -39,7 +39,17 @@ constexpr uint32_t STREAM_K_MAX = 64;      // finalize_warp holds two candidates
 // three (33.4 against 34.0 us per 256-row launch; asking L2 for further rounds
 // ahead of the ring was slower still: the stream is not short of requests). With
 // fewer rows than SMs a block streams alone against the latency of its own
-// requests, and three are the better choice.
+// requests: it has the SM's shared memory to itself, and takes a ring of eight
+// stages with seven rounds in flight (112 KB per block) and four 16-byte loads of
+// history ids per thread and round instead of two.
+template <uint32_t AHEAD>
+struct StreamDepth {
+    static_assert(AHEAD == 2u || AHEAD == 3u || AHEAD == 7u, "a ring of four stages, or of eight");
+    static constexpr uint32_t STAGES = AHEAD <= 3u ? 4u : 8u;     // of the ring
+    static constexpr uint32_t HQ = AHEAD <= 3u ? 2u : 4u;         // 16-byte history loads per thread and round
+    static constexpr uint32_t BLOCKS = AHEAD <= 3u ? 2u : 1u;     // per SM
+    static constexpr uint32_t EXTRA_BYTES = (STAGES - 4u) * NT * FRAG_BYTES;  // stages beyond the four shared ones
+};
 
 __device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count) {
     const uint32_t at = (uint32_t)__cvta_generic_to_shared(bar);
@@ -172,8 +182,8 @@ __device__ __forceinline__ uint32_t small_select(SmemFixed *sm, uint32_t n, uint
 }
 
 template <typename T, uint32_t AHEAD>
-__global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constant__ KArgs a) {
-    static_assert(AHEAD == 2u || AHEAD == 3u, "the ring has four stages");
+__global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_kernel(const __grid_constant__ KArgs a) {
+    constexpr uint32_t NS = StreamDepth<AHEAD>::STAGES, HQ = StreamDepth<AHEAD>::HQ;
     extern __shared__ uint4 smem_raw[];
     SmemFixed *sm = reinterpret_cast<SmemFixed *>(smem_raw);
     uint4 *ring = reinterpret_cast<uint4 *>(sm + 1);
@@ -239,14 +249,21 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     // The ring: stages 0 and 1 behind the fixed block, stages 2 and 3 in the
     // (here unused) candidate arrays key and id, one round each.
     static_assert(CAP * 4u == NT * FRAG_BYTES && STAGES == 2, "key[] and id[] are one round each");
+    // (Stages 4 to 7 of the deep ring lie behind the seen bits, where the general
+    // row code, should the row go to it, has nothing.)
     const uint32_t slot_a = (uint32_t)__cvta_generic_to_shared(ring) + tid * FRAG_BYTES;
     const uint32_t slot_b = (uint32_t)__cvta_generic_to_shared(sm->key) + tid * FRAG_BYTES;
-    lean_copy_round(slot_a, src0);
-    cp_async_commit();
-    lean_copy_round(slot_a + ROUND_BYTES, src0 + ROUND_BYTES);
-    cp_async_commit();
-    if (AHEAD == 3u) {
-        lean_copy_round(slot_b, src0 + 2u * ROUND_BYTES);
+    const uint32_t slot_c = (uint32_t)__cvta_generic_to_shared(seen) +
+                            ((((a.vocab + 255u) & ~255u) + 31u) / 32u + 8u) * 4u + tid * FRAG_BYTES;
+    auto stage_at = [&](uint32_t st) -> uint32_t {
+        if (NS == 4u) {
+            return ((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES;
+        }
+        return (st < 2u ? slot_a : st < 4u ? slot_b - 2u * ROUND_BYTES : slot_c - 4u * ROUND_BYTES) + st * ROUND_BYTES;
+    };
+#pragma unroll
+    for (uint32_t j = 0; j < AHEAD; ++j) {
+        lean_copy_round(stage_at(j), src0 + j * ROUND_BYTES);
         cp_async_commit();
     }
 
@@ -331,8 +348,8 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     const bool hist_vec = (reinterpret_cast<uintptr_t>(hist) & 15u) == 0u;
     // 16-byte words of the history marked inside the stream, at most half of the
     // rounds' worth; the rest is marked before the stream starts.
-    const uint32_t n4 = hist_vec ? min(hist_len / 4u, (nfull / 2u) * 2u * (uint32_t)NT) : 0u;
-    const uint32_t mark_rounds = (n4 + 2u * NT - 1u) / (2u * NT);
+    const uint32_t n4 = hist_vec ? min(hist_len / 4u, (nfull / 2u) * HQ * (uint32_t)NT) : 0u;
+    const uint32_t mark_rounds = (n4 + HQ * NT - 1u) / (HQ * NT);
     const uint32_t r_check = max(mark_rounds, nfull / 2u);  // < nfull
 
     if (tid == 0) {
@@ -404,8 +421,7 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     // and waits for round rr.
     auto advance = [&](uint32_t rr) {
         if (rr + AHEAD < nproc) {
-            const uint32_t st = (rr + AHEAD) & 3u;
-            const uint32_t dst = ((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES;
+            const uint32_t dst = stage_at((rr + AHEAD) & (NS - 1u));
             if (rr + AHEAD < nfull) {
                 lean_copy_round(dst, src);
             } else {
@@ -425,8 +441,7 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
         cp_async_wait<AHEAD>();
     };
     auto read_round = [&](uint32_t rr, Frag &cur) -> bool {
-        const uint32_t st = rr & 3u;
-        lean_read_slot(((st & 2u) ? slot_b : slot_a) + (st & 1u) * ROUND_BYTES, cur);
+        lean_read_slot(stage_at(rr & (NS - 1u)), cur);
         if (rr == nfull) {
             frag_mask_tail<T>(cur, part_valid);
             return part_valid != 0u;
@@ -463,22 +478,31 @@ __global__ void __launch_bounds__(NT, 2) stream_rows_kernel(const __grid_constan
     };
 
     uint32_t rr = 0;
-    // Rounds that also mark history ids (two 16-byte loads ahead).
+    // Rounds that also mark history ids (HQ 16-byte loads per thread, one round ahead).
     if (mark_rounds != 0u) {
         const uint4 no_ids = make_uint4(NONE, NONE, NONE, NONE);
         uint32_t hnext = tid;
-        uint4 hq0 = hnext < n4 ? __ldg(h4 + hnext) : no_ids;
-        uint4 hq1 = hnext + NT < n4 ? __ldg(h4 + hnext + NT) : no_ids;
-        hnext += 2u * NT;
+        uint4 hq[HQ];
+#pragma unroll
+        for (uint32_t j = 0; j < HQ; ++j) {
+            hq[j] = hnext + j * NT < n4 ? __ldg(h4 + hnext + j * NT) : no_ids;
+        }
+        hnext += HQ * NT;
         for (; rr < mark_rounds; ++rr) {
             advance(rr);
             {
-                const uint32_t ids[8] = {hq0.x, hq0.y, hq0.z, hq0.w, hq1.x, hq1.y, hq1.z, hq1.w};
-                hq0 = hnext < n4 ? __ldg(h4 + hnext) : no_ids;
-                hq1 = hnext + NT < n4 ? __ldg(h4 + hnext + NT) : no_ids;
-                hnext += 2u * NT;
+                uint32_t ids[4u * HQ];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (uint32_t j = 0; j < HQ; ++j) {
+                    ids[4u * j] = hq[j].x;
+                    ids[4u * j + 1u] = hq[j].y;
+                    ids[4u * j + 2u] = hq[j].z;
+                    ids[4u * j + 3u] = hq[j].w;
+                    hq[j] = hnext + j * NT < n4 ? __ldg(h4 + hnext + j * NT) : no_ids;
+                }
+                hnext += HQ * NT;
+#pragma unroll
+                for (uint32_t i = 0; i < 4u * HQ; ++i) {
                     if (ids[i] < vocab) {
                         asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(seen_at + (ids[i] >> 5) * 4u),
                                      "r"(1u << (ids[i] & 31u))

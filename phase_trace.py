@@ -3,7 +3,7 @@ kernel leaves with LILY_FLAG_PHASE_CLOCKS (the counterpart of the reference's
 LILY_KERNEL_PROFILE, src/metal.rs:140-198).
 
     python phase_trace.py b4 [step ...]     # the 4-row server batch
-    python phase_trace.py b256              # the 256-row batch (summary)
+    python phase_trace.py b256 [rows]       # the 256-row batch, or its first rows (summary)
 
 Stamps are nanoseconds of the GPU's global timer, so stamps of different
 blocks of a launch can be compared with each other.
@@ -101,8 +101,9 @@ def main(argv) -> None:
                           f"{(last - t0) / 1e3:5.1f} us after the launch's first block | " +
                           " | ".join(f"{n} {us:.1f}" for n, us in segments(c, cluster)))
     else:
+        rows = int(argv[2]) if len(argv) > 2 else 256
         scratch = lily.SamplerScratch(w.VOCAB, max_rows=256, phase_clocks=True)
-        clk = trace(torch, lily, scratch, w.config4_batch(), launches=4)
+        clk = trace(torch, lily, scratch, w.config4_batch(rows=rows), launches=4)
         live = clk[clk[:, :, ENTRY] != 0].astype(np.float64)
         t0 = live[:, ENTRY].min()
         print("blocks", len(live))

@@ -98,4 +98,14 @@ def test_config4_large_batch(cuda, lily, W):
                        b.history[perm], b.history_len[perm])
     res2 = run_batch(cuda, lily, s, shuffled, want_kept=False)
     assert np.array_equal(res2.ids, res.ids[perm])
+    # A rank's share of the 256 rows when they are split over 2, 4 or 8 GPUs (and a
+    # ragged one): from 148 rows down a block has its SM to itself and streams
+    # through the deep ring. Same rows, same tokens and kept sets.
+    for lo, n in ((0, 128), (64, 64), (224, 32), (100, 17)):
+        part = W.Batch(b.logits[lo:lo + n], True, b.params[lo:lo + n], b.uniforms[lo:lo + n],
+                       b.history[lo:lo + n], b.history_len[lo:lo + n])
+        res3 = run_batch(cuda, lily, s, part)
+        assert np.array_equal(res3.ids, res.ids[lo:lo + n]), f"rows {lo}..{lo + n}"
+        assert np.array_equal(res3.kept_n, res.kept_n[lo:lo + n])
+        assert np.array_equal(res3.kept_ids, res.kept_ids[lo:lo + n])
     s.close()
