@@ -985,15 +985,22 @@ __device__ __noinline__ void finalize_warp(SmemFixed *sm, const KArgs &a, uint32
     const float u = sm->u_draw;
     const float p0 = lane < n ? exp_f32(__fsub_rn(float_of_key(k0), top)) : 0.0f;
     const float p1 = lane + 32u < n ? exp_f32(__fsub_rn(float_of_key(k1), top)) : 0.0f;
+    // The running sum in rank order, one add after the other as the reference's
+    // CPU sampler does it. Unrolled over all 32 lanes: the shuffles do not depend
+    // on the sum and go out back to back, the chain is the adds alone; ranks past
+    // n weigh 0, and s + 0 is s (s is never -0).
     float s = 0.0f, c0 = 0.0f, c1 = 0.0f;
-    const uint32_t n_lo = min(n, 32u);
-    for (uint32_t i = 0; i < n_lo; ++i) {
+#pragma unroll
+    for (uint32_t i = 0; i < 32u; ++i) {
         s = __fadd_rn(s, __shfl_sync(FULL, p0, (int)i));
         c0 = lane == i ? s : c0;
     }
-    for (uint32_t i = 32u; i < n; ++i) {
-        s = __fadd_rn(s, __shfl_sync(FULL, p1, (int)(i - 32u)));
-        c1 = lane == i - 32u ? s : c1;
+    if (n > 32u) {
+#pragma unroll
+        for (uint32_t i = 0; i < 32u; ++i) {
+            s = __fadd_rn(s, __shfl_sync(FULL, p1, (int)i));
+            c1 = lane == i ? s : c1;
+        }
     }
     // Keep rank i >= 1 while the mass before it is below top_p of the total and
     // its weight reaches min_p; the first rank that fails ends the kept set.

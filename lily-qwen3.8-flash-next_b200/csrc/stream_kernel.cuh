@@ -151,7 +151,8 @@ __device__ __forceinline__ void frag_mask_tail(Frag &f, uint32_t nvalid) {
 // End of the stream with at most one buffered candidate per thread (all raw):
 // adjusts them, drops what lies below the threshold key and leaves the best k
 // sorted by (key descending, id ascending) in key / id [0, result): every live
-// candidate counts how many come before it. Two block barriers.
+// candidate counts how many come before it (four threads share the count of a
+// candidate while there are at most 128). Two block barriers.
 __device__ __forceinline__ uint32_t small_select(SmemFixed *sm, uint32_t n, uint32_t k) {
     const uint32_t tid = threadIdx.x;
     unsigned long long *packed = reinterpret_cast<unsigned long long *>(sm->tkey);  // (key, ~id), 0 = dropped
@@ -166,7 +167,24 @@ __device__ __forceinline__ uint32_t small_select(SmemFixed *sm, uint32_t n, uint
         packed[tid] = mine;
     }
     const uint32_t live = (uint32_t)__syncthreads_count(alive);
-    if (alive) {
+    if (n <= NT / 4u) {
+        // Up to 128 candidates: four threads share a candidate's count.
+        const uint32_t c = tid >> 2, part = tid & 3u;
+        const unsigned long long cand = c < n ? packed[c] : 0ull;
+        uint32_t rank = 0;
+        if (cand != 0ull) {
+#pragma unroll 4
+            for (uint32_t j = part; j < n; j += 4u) {
+                rank += packed[j] > cand ? 1u : 0u;
+            }
+        }
+        rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
+        rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 2);
+        if (cand != 0ull && part == 0u && rank < k) {
+            sm->key[rank] = (uint32_t)(cand >> 32);
+            sm->id[rank] = ~(uint32_t)cand;
+        }
+    } else if (alive) {
         uint32_t rank = 0;
 #pragma unroll 4
         for (uint32_t j = 0; j < n; ++j) {
