@@ -506,6 +506,16 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
     bi = (-torch.rand((per, hidden // 64), device=dev, generator=g)).to(torch.bfloat16)
     affine_ms = timed(lambda i: scratch.lmhead_logits(ws[i % copies], sc, h, logits, stream=stream,
                                                       biases=bi), steps)
+    # And in MLX affine 4-bit storage: the same bytes read as twice as many columns
+    # (a head of 2 * hidden columns; its hidden states and groups are synthetic too).
+    h4 = torch.cat([h, h], dim=1).contiguous()
+    sc4 = torch.cat([sc, sc], dim=1).contiguous()
+    bi4 = torch.cat([bi, bi], dim=1).contiguous()
+    logits4 = torch.empty((tokens, per), dtype=torch.float32, device=dev)
+    q4_ms = None
+    if 2 * hidden <= 8192:
+        q4_ms = timed(lambda i: scratch.lmhead_logits(ws[i % copies].view(torch.uint8), sc4, h4, logits4,
+                                                      stream=stream, biases=bi4, code_bits=4), steps)
     assert scratch.status(stream) == lily.OK
     agree = True
     if world > 1:
@@ -525,6 +535,10 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
             "head_traffic_1gpu": ncu_traffic("lmhead_int8_kernel_dram_bytes_per_launch"),
             "affine_head_us": affine_ms * 1e3,
             "affine_head_frac_of_hbm": (head_bytes + per * (hidden // 64) * 2) / (affine_ms * 1e-3) / 1e9 / peak,
+            "affine4_head_us": None if q4_ms is None else q4_ms * 1e3,
+            "affine4_head_workload": f"the same {per} x {hidden} bytes as 4-bit codes of a head of {2 * hidden} columns",
+            "affine4_head_frac_of_hbm": None if q4_ms is None else
+            (per * hidden + per * (2 * hidden // 64) * 4 + tokens * 2 * hidden * 2) / (q4_ms * 1e-3) / 1e9 / peak,
             "allgather_bytes_per_rank": tokens * sh.RECORD_BYTES, "ranks_agree": agree,
             "l2": "one 1.07 GB shard" if copies == 1 else "two weight copies rotated"}
 

@@ -387,7 +387,11 @@ int32_t lily_spec_accept(lily_sampler_t *h, void *stream, const uint32_t *draws,
  *
  * which is sum_c (scale * q + bias) * hidden up to binary32 rounding (the
  * reference's own test allows 2e-2 + 2e-2 |x| against a dequantise-then-
- * multiply sum, tests/unit/kernels/quant.rs:418-434).
+ * multiply sum, tests/unit/kernels/quant.rs:418-434). With `code_bits` = 4 the
+ * codes are 4 bits wide (q in 0..15, widened as they are) and
+ *
+ *   logits[t, n] = sum_g ( scale[n, g] * sum_c q[n, c] * hidden[t, c]
+ *                          + bias[n, g] * sum_c hidden[t, c] ).
  */
 typedef struct lily_lmhead {
     uint32_t struct_size;        /* sizeof(lily_lmhead_t) */
@@ -404,6 +408,14 @@ typedef struct lily_lmhead {
                                     same memory), w = scale * q + bias, and
                                     this is device bf16 [rows, hidden / group];
                                     hidden <= 8192 */
+    uint32_t code_bits;          /* 0 or 8: a byte per weight, as above. 4 (with
+                                    biases set): MLX affine 4-bit storage, the
+                                    format gemv_q4_bf16 reads
+                                    (src/kernels/metal/quant.metal:44-66): `weights`
+                                    is QuantWeights::codes, U32 [rows, hidden / 8],
+                                    eight codes to a word, low nibble first;
+                                    w = scale * q + bias with q in 0..15 */
+    uint32_t reserved;
 } lily_lmhead_t;
 
 /* out_logits: device F32 [tokens, out_ld >= rows]. Needs no handle state

@@ -102,7 +102,7 @@ class LmHead(C.Structure):
 
     _fields_ = [("struct_size", C.c_uint32), ("rows", C.c_uint32), ("hidden", C.c_uint32),
                 ("group", C.c_uint32), ("weights", C.c_void_p), ("scales_bf16", C.c_void_p),
-                ("biases_bf16", C.c_void_p)]
+                ("biases_bf16", C.c_void_p), ("code_bits", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 SHARD_CANDIDATES = 64
@@ -424,10 +424,12 @@ class SamplerScratch:
 
     # -- 8-bit LM head and vocabulary shards
     @staticmethod
-    def _head(weights, scales, biases=None, group: int = 64) -> LmHead:
+    def _head(weights, scales, biases=None, group: int = 64, code_bits: int = 8) -> LmHead:
         hd = LmHead()
         hd.struct_size = C.sizeof(LmHead)
-        hd.rows, hd.hidden = int(weights.shape[0]), int(weights.shape[1])
+        # (`weights` as bytes: a row of 4-bit codes is hidden / 2 bytes long)
+        hd.rows, hd.hidden = int(weights.shape[0]), int(weights.shape[1]) * (2 if code_bits == 4 else 1)
+        hd.code_bits = code_bits
         hd.group = group
         hd.weights = _ptr(weights)
         hd.scales_bf16 = _ptr(scales)
@@ -447,12 +449,13 @@ class SamplerScratch:
             a.steps = C.cast(sarr, C.c_void_p)
         return a
 
-    def lmhead_logits(self, weights, scales, hidden, out_logits, stream=None, biases=None):
+    def lmhead_logits(self, weights, scales, hidden, out_logits, stream=None, biases=None, code_bits: int = 8):
         """lily_lmhead_logits: int8 `weights` [rows, hidden], bf16 `scales`
         [rows, hidden/64], bf16 `hidden` [tokens, hidden] -> F32 out [tokens, >= rows].
         With bf16 `biases` [rows, hidden/64] the head is in MLX affine 8-bit
-        storage: `weights` are unsigned bytes, w = scale * q + bias."""
-        hd = self._head(weights, scales, biases)
+        storage: `weights` are unsigned bytes, w = scale * q + bias; with
+        code_bits=4 they are the 4-bit codes as bytes [rows, hidden/2]."""
+        hd = self._head(weights, scales, biases, code_bits=code_bits)
         self._check(lib().lily_lmhead_logits(self._h, _stream_ptr(stream), C.byref(hd), _ptr(hidden),
                                              _ld(hidden), int(hidden.shape[0]), _ptr(out_logits),
                                              _ld(out_logits)))
@@ -468,13 +471,13 @@ class SamplerScratch:
                                                 int(want_sums), _ptr(records)))
 
     def lmhead_shard_candidates(self, weights, scales, hidden, params, records, first_id: int = 0,
-                                want_sums: bool = False, stream=None, biases=None):
+                                want_sums: bool = False, stream=None, biases=None, code_bits: int = 8):
         """lily_lmhead_shard_candidates: head projection into the handle's own
         logits, then this shard's records (needs lmhead=True at creation)."""
         rows = int(hidden.shape[0])
         keep = []
         a = self._shard_args(rows, params, None, keep)
-        hd = self._head(weights, scales, biases)
+        hd = self._head(weights, scales, biases, code_bits=code_bits)
         self._check(lib().lily_lmhead_shard_candidates(self._h, _stream_ptr(stream), C.byref(hd),
                                                        _ptr(hidden), _ld(hidden), C.byref(a),
                                                        first_id, int(want_sums), _ptr(records)))

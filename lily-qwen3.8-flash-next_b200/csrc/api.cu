@@ -80,7 +80,7 @@ struct lily_sampler {
     float *lm_logits = nullptr;  // LILY_FLAG_LMHEAD: F32 [64, lm_ld]
     uint64_t lm_ld = 0;
     float *lm_hsum = nullptr;    // affine heads: sums of hidden values, F32 [BIAS_MAX_GROUPS, 64]
-    bool lm_attr = false, lm_attr_affine = false, lm_attr_bias = false, merge_attr = false;
+    bool lm_attr = false, lm_attr_affine = false, lm_attr_q4 = false, lm_attr_bias = false, merge_attr = false;
 };
 
 namespace {
@@ -1007,9 +1007,17 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
     if (affine && head->hidden / lily_head::GROUP_K > lily_head::BIAS_MAX_GROUPS) {
         return fail(h, LILY_ERR_CAPACITY, "an affine head takes a hidden size of at most 8192");
     }
-    auto kernel = affine ? lily_head::lmhead_int8_kernel<lily_head::VARIANT_AFFINE>
-                         : lily_head::lmhead_int8_kernel<0>;
-    bool &attr_set = affine ? h->lm_attr_affine : h->lm_attr;
+    if (head->code_bits != 0u && head->code_bits != 8u && head->code_bits != 4u) {
+        return fail(h, LILY_ERR_ARG, "code_bits must be 0, 8 or 4");
+    }
+    const bool q4 = head->code_bits == 4u;
+    if (q4 && !affine) {
+        return fail(h, LILY_ERR_ARG, "4-bit codes are the affine storage: biases must be set");
+    }
+    auto kernel = q4 ? lily_head::lmhead_int8_kernel<lily_head::VARIANT_AFFINE | lily_head::VARIANT_Q4>
+                     : affine ? lily_head::lmhead_int8_kernel<lily_head::VARIANT_AFFINE>
+                              : lily_head::lmhead_int8_kernel<0>;
+    bool &attr_set = q4 ? h->lm_attr_q4 : affine ? h->lm_attr_affine : h->lm_attr;
     if (!attr_set) {
         CU(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)lily_head::Smem::BYTES));
@@ -1021,9 +1029,10 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
     }
     lily_head::Args a;
     {
-        // Weights: uint8 [rows, hidden], boxes of 256 rows x 128 bytes.
-        const cuuint64_t dims[2] = {head->hidden, head->rows};
-        const cuuint64_t strides[1] = {head->hidden};
+        // Weights: uint8 [rows, hidden] (4-bit codes: [rows, hidden / 2]), boxes of 256 rows x 128 bytes.
+        const cuuint64_t row_bytes = q4 ? head->hidden / 2u : head->hidden;
+        const cuuint64_t dims[2] = {row_bytes, head->rows};
+        const cuuint64_t strides[1] = {row_bytes};
         const cuuint32_t box[2] = {(cuuint32_t)(lily_head::GROUP_K * lily_head::RAW_GROUPS),
                                    (cuuint32_t)lily_head::TILE_ROWS};
         const cuuint32_t estr[2] = {1, 1};
@@ -1060,7 +1069,8 @@ int32_t lmhead_launch(lily_sampler *h, cudaStream_t stream, const lily_lmhead_t 
                                              lily_head::BIAS_THREADS, lily_head::bias_smem_bytes(head_groups),
                                              stream>>>(
             h->lm_hsum, tokens, static_cast<const __nv_bfloat16 *>(head->scales_bf16),
-            static_cast<const __nv_bfloat16 *>(head->biases_bf16), head_groups, head->rows, out, out_ld);
+            static_cast<const __nv_bfloat16 *>(head->biases_bf16), head_groups, head->rows, out, out_ld,
+            q4 ? 0.0f : 128.0f);
         CU(h, cudaGetLastError());
     }
     a.tokens = tokens;

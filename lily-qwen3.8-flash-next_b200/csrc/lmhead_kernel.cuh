@@ -328,9 +328,19 @@ __device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
 // copies (bit 3) or the weight copies (bit 4) to time the rest. Bit 5 selects
 // the affine storage (unsigned bytes, a bias per group).
 constexpr int VARIANT_AFFINE = 32;
+// Bit 6 (with bit 5): the affine storage in 4 bits, eight codes to a 32-bit word,
+// low nibble first (src/kernels/metal/quant.metal:44-66, src/weights.rs:20-36). A
+// stage's 128 bytes per row are then four groups, not two; a thread splits a word
+// into its low and high nibbles, interleaves them back into code order with two
+// byte permutes and widens the eight small bytes as it widens int8 (a code is at
+// most 15: no shift by 128, the bias term is bias * sum of the hidden values).
+constexpr int VARIANT_Q4 = 64;
 template <int VARIANT>
 __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_constant__ Args a) {
     constexpr bool AFFINE = (VARIANT & VARIANT_AFFINE) != 0;
+    constexpr bool Q4 = (VARIANT & VARIANT_Q4) != 0;
+    static_assert(!Q4 || AFFINE, "4-bit codes come with a bias per group");
+    constexpr uint32_t RG = Q4 ? 2u * RAW_GROUPS : (uint32_t)RAW_GROUPS;  // groups per stage
     extern __shared__ uint8_t smem_unaligned[];
     const uint32_t base = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_unaligned + (base - smem_u32(smem_unaligned));
@@ -426,7 +436,7 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
         // ---- one thread asks the copy engine for every stage of weights and
         // every group's slice of the hidden states, as far ahead as slots are free
         if (lane == 0) {
-            const uint32_t stages_per_tile = groups / RAW_GROUPS;
+            const uint32_t stages_per_tile = groups / RG;
             const uint32_t n_stages = my_tiles * stages_per_tile;
             long long tw_re = 0, tw_he = 0;
             // The copies asked for last, per slot (bit s: slot s has one; its phase's
@@ -437,7 +447,7 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             for (uint32_t i = 0; i < n_stages && !gave_up; ++i) {
                 const uint32_t st = i % RAW_STAGES;
                 const uint32_t tile = blockIdx.x + (i / stages_per_tile) * gridDim.x;
-                const uint32_t kb = (i % stages_per_tile) * (GROUP_K * RAW_GROUPS);
+                const uint32_t kb = (i % stages_per_tile) * (GROUP_K * RG);  // first column of the stage
                 if (mbar_wait(base + Smem::RAW_EMPTY + 8 * st, ((i / RAW_STAGES) & 1u) ^ 1u, abort_word, wait_ns)) {
                     break;
                 }
@@ -449,13 +459,13 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                     raw_parity = (raw_parity & ~(1u << st)) | (((i / RAW_STAGES) & 1u) << st);
                     mbar_expect_tx(base + Smem::RAW_FULL + 8 * st, RAW_STAGE_BYTES);
                     tma_load_2d(base + Smem::RAW + st * RAW_STAGE_BYTES, &a.w_map, base + Smem::RAW_FULL + 8 * st,
-                                (int32_t)kb, (int32_t)(tile * TILE_ROWS));
+                                (int32_t)(Q4 ? kb / 2u : kb), (int32_t)(tile * TILE_ROWS));  // (a byte offset)
                 } else {
                     mbar_arrive(base + Smem::RAW_FULL + 8 * st);
                 }
 #pragma unroll
-                for (uint32_t gg = 0; gg < RAW_GROUPS; ++gg) {
-                    const uint32_t q = i * RAW_GROUPS + gg;
+                for (uint32_t gg = 0; gg < RG; ++gg) {
+                    const uint32_t q = i * RG + gg;
                     const uint32_t hs = q % H_SLOTS;
                     if (q >= (uint32_t)H_SLOTS) {  // the slot's previous group has been multiplied
                         if (mbar_wait(base + Smem::DONE + 8 * hs, ((q / H_SLOTS) & 1u) ^ 1u, abort_word, wait_ns)) {
@@ -500,7 +510,7 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
         const uint32_t half = (warp - WARP_CONV0) >> 2;     // which 128 rows of the tile
         const uint32_t trow = half * 128u + quad * 32u + lane;
         const uint32_t t_lane = (quad * 32u) << 16;
-        const uint32_t stages_per_tile = groups / RAW_GROUPS;
+        const uint32_t stages_per_tile = groups / RG;
         const uint32_t n_stages = my_tiles * stages_per_tile;
         long long tw_raw = 0, tw_ae = 0, t_conv = 0, t_st = 0;
         bool conv_gave_up = false;
@@ -515,15 +525,29 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
             LM_ACC(tw_raw);
             const uint32_t raw_row = base + Smem::RAW + st * RAW_STAGE_BYTES + trow * 128u;
 #pragma unroll 1
-            for (uint32_t gg = 0; gg < RAW_GROUPS; ++gg) {
-                const uint32_t q = i * RAW_GROUPS + gg;
+            for (uint32_t gg = 0; gg < RG; ++gg) {
+                const uint32_t q = i * RG + gg;
                 const uint32_t as = q % A_SLOTS;
                 // Widen first (it needs no slot), then wait for the slot: the
                 // conversion overlaps the multiplies still reading the slot.
                 uint32_t o[2][16];
 #pragma unroll
                 for (uint32_t part = 0; part < 2; ++part) {
-                    if (!(VARIANT & 2)) {
+                    if (Q4) {
+                        // 16 bytes = 32 codes of the group's 64.
+                        uint32_t x[4];
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3])
+                                     : "r"(raw_row + (((gg * 2u + part) ^ (trow & 7u)) << 4)));
+#pragma unroll
+                        for (uint32_t w = 0; w < 4; ++w) {
+                            const uint32_t lo = x[w] & 0x0F0F0F0Fu, hi = (x[w] >> 4) & 0x0F0F0F0Fu;
+                            const uint32_t c0123 = __byte_perm(lo, hi, 0x5140);  // codes 0..3 of the word, a byte each
+                            const uint32_t c4567 = __byte_perm(lo, hi, 0x7362);
+                            widen4<false>(c0123, o[part][4 * w + 0], o[part][4 * w + 1]);
+                            widen4<false>(c4567, o[part][4 * w + 2], o[part][4 * w + 3]);
+                        }
+                    } else if (!(VARIANT & 2)) {
 #pragma unroll
                         for (uint32_t c = 0; c < 2; ++c) {
                             uint32_t x0, x1, x2, x3;
@@ -723,7 +747,7 @@ __host__ __device__ constexpr uint32_t bias_smem_bytes(uint32_t groups) {
 
 __global__ void __launch_bounds__(BIAS_THREADS) affine_bias_term_kernel(
     const float *group_sums, uint32_t tokens, const __nv_bfloat16 *scales, const __nv_bfloat16 *biases,
-    uint32_t groups, uint32_t rows, float *out, uint64_t ldo) {
+    uint32_t groups, uint32_t rows, float *out, uint64_t ldo, float code_offset) {
     extern __shared__ __align__(16) uint8_t bias_smem[];
     float *hsum = reinterpret_cast<float *>(bias_smem);  // [group][token]
     uint8_t *sc_s = bias_smem + groups * TOK * 4u;
@@ -789,7 +813,7 @@ __global__ void __launch_bounds__(BIAS_THREADS) affine_bias_term_kernel(
             for (int r = 0; r < 4; ++r) {
                 const float s = __uint_as_float((gi & 1u) ? (sw[r][gi >> 1] & 0xFFFF0000u) : (sw[r][gi >> 1] << 16));
                 const float b = __uint_as_float((gi & 1u) ? (bw[r][gi >> 1] & 0xFFFF0000u) : (bw[r][gi >> 1] << 16));
-                const float shift = fmaf(128.0f, s, b);
+                const float shift = fmaf(code_offset, s, b);  // (8-bit codes are widened less 128, 4-bit ones as they are)
                 const uint64_t shift2 = pack2(__float_as_uint(shift), __float_as_uint(shift));
 #pragma unroll
                 for (int m = 0; m < 4; ++m) {
