@@ -303,6 +303,15 @@ __device__ __forceinline__ void widen4(uint32_t x, uint32_t &lo, uint32_t &hi) {
     asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(a23), "r"(b23));
 }
 
+// The same for four bytes below 128 (4-bit codes): 0x4300 | b is 128 + b as it
+// stands, and one subtraction of 128 per pair is all that is left.
+__device__ __forceinline__ void widen4_small(uint32_t x, uint32_t &lo, uint32_t &hi) {
+    const uint32_t t01 = __byte_perm(x, 0x43434343u, 0x5140);
+    const uint32_t t23 = __byte_perm(x, 0x43434343u, 0x5342);
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(t01), "r"(0x43004300u));
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(t23), "r"(0x43004300u));
+}
+
 // Two binary32 values in one 64-bit register, and the packed fused
 // multiply-add on them (each half rounds as a scalar fma does).
 __device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
@@ -544,8 +553,8 @@ __global__ void __launch_bounds__(THREADS, 1) lmhead_int8_kernel(const __grid_co
                             const uint32_t lo = x[w] & 0x0F0F0F0Fu, hi = (x[w] >> 4) & 0x0F0F0F0Fu;
                             const uint32_t c0123 = __byte_perm(lo, hi, 0x5140);  // codes 0..3 of the word, a byte each
                             const uint32_t c4567 = __byte_perm(lo, hi, 0x7362);
-                            widen4<false>(c0123, o[part][4 * w + 0], o[part][4 * w + 1]);
-                            widen4<false>(c4567, o[part][4 * w + 2], o[part][4 * w + 3]);
+                            widen4_small(c0123, o[part][4 * w + 0], o[part][4 * w + 1]);
+                            widen4_small(c4567, o[part][4 * w + 2], o[part][4 * w + 3]);
                         }
                     } else if (!(VARIANT & 2)) {
 #pragma unroll
