@@ -472,6 +472,53 @@ int32_t lily_lmhead_shard_candidates(lily_sampler_t *h, void *stream, const lily
 int32_t lily_merge_draw(lily_sampler_t *h, void *stream, const void *gathered, uint32_t n_shards,
                         uint64_t shard_stride, const lily_sample_args_t *args, float *out_lse);
 
+/*
+ * The same exchange without a collective library: every rank writes its records
+ * straight into every rank's memory (peer stores over NVLink) and raises a
+ * flag there; the merge waits for the flags. No counterpart in the reference.
+ *
+ * A rank owns one exchange buffer (lily_peer_buffer_create: device memory of
+ * lily_peer_buffer_bytes, zeroed, and its 64-byte inter-process handle). The
+ * ranks pass the handles around by any means, open each other's buffers
+ * (lily_peer_buffer_open: the buffer as THIS process sees it; peer access is
+ * enabled on the way) and fill a lily_peer_exchange_t, own buffer included.
+ * Per step, with `step` counting 1, 2, 3, ... on every rank alike:
+ *
+ *   lily_shard_publish     one kernel: this rank's `rows` records into slot
+ *                          (step & 1, rank) of every buffer, a system-wide
+ *                          fence, then flag[rank] := step in every buffer;
+ *   lily_merge_draw_peer   one small kernel that waits until all n_shards flags
+ *                          of the OWN buffer have reached `step` (bounded by
+ *                          lily_sampler_set_wait_limit; on time-out the status
+ *                          becomes LILY_ERR_TIMEOUT and the draw is not valid),
+ *                          then lily_merge_draw on slot (step & 1).
+ *
+ * Two slots suffice: a rank cannot publish step n + 2 before it has merged step
+ * n + 1, which every rank publishes only after it has merged step n. All ranks
+ * must be single GPUs of one node with peer access to each other, one process
+ * per GPU; a rank must not skip a step.
+ */
+#define LILY_PEER_MAX 16u
+#define LILY_IPC_HANDLE_BYTES 64u
+typedef struct lily_peer_exchange {
+    uint32_t struct_size;             /* sizeof(lily_peer_exchange_t) */
+    uint32_t n_shards;                /* ranks, <= LILY_PEER_MAX */
+    uint32_t rank;                    /* this rank */
+    uint32_t max_rows;                /* as given to lily_peer_buffer_create, the same on every rank */
+    void *buffers[LILY_PEER_MAX];     /* rank r's exchange buffer as this process sees it */
+} lily_peer_exchange_t;
+
+uint64_t lily_peer_buffer_bytes(uint32_t n_shards, uint32_t max_rows);
+int32_t lily_peer_buffer_create(int32_t device, uint32_t n_shards, uint32_t max_rows, void **buffer,
+                                void *ipc_handle);
+int32_t lily_peer_buffer_open(int32_t device, const void *ipc_handle, void **buffer);
+int32_t lily_peer_buffer_close(int32_t device, void *buffer);
+int32_t lily_peer_buffer_destroy(int32_t device, void *buffer);
+int32_t lily_shard_publish(lily_sampler_t *h, void *stream, const lily_peer_exchange_t *x,
+                           const void *records, uint32_t rows, uint32_t step);
+int32_t lily_merge_draw_peer(lily_sampler_t *h, void *stream, const lily_peer_exchange_t *x, uint32_t step,
+                             const lily_sample_args_t *args, float *out_lse);
+
 /* ------------------------------------------------------------------ test -- */
 
 /*

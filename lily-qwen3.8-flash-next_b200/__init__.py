@@ -105,6 +105,15 @@ class LmHead(C.Structure):
                 ("biases_bf16", C.c_void_p), ("code_bits", C.c_uint32), ("reserved", C.c_uint32)]
 
 
+class PeerExchangeStruct(C.Structure):
+    """lily_peer_exchange_t: every rank's exchange buffer as this process sees it."""
+
+    _fields_ = [("struct_size", C.c_uint32), ("n_shards", C.c_uint32), ("rank", C.c_uint32),
+                ("max_rows", C.c_uint32), ("buffers", C.c_void_p * 16)]
+
+
+PEER_MAX = 16
+IPC_HANDLE_BYTES = 64
 SHARD_CANDIDATES = 64
 SHARD_RECORD_BYTES = 520
 FLAG_LMHEAD = 4
@@ -193,6 +202,17 @@ def lib():
                                                    C.c_uint32, C.c_int32, C.c_void_p]
         L.lily_merge_draw.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64,
                                       C.POINTER(SampleArgs), C.c_void_p]
+        L.lily_peer_buffer_bytes.restype = C.c_uint64
+        L.lily_peer_buffer_bytes.argtypes = [C.c_uint32, C.c_uint32]
+        L.lily_peer_buffer_create.argtypes = [C.c_int32, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p),
+                                              C.c_void_p]
+        L.lily_peer_buffer_open.argtypes = [C.c_int32, C.c_void_p, C.POINTER(C.c_void_p)]
+        L.lily_peer_buffer_close.argtypes = [C.c_int32, C.c_void_p]
+        L.lily_peer_buffer_destroy.argtypes = [C.c_int32, C.c_void_p]
+        L.lily_shard_publish.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(PeerExchangeStruct), C.c_void_p,
+                                         C.c_uint32, C.c_uint32]
+        L.lily_merge_draw_peer.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(PeerExchangeStruct), C.c_uint32,
+                                           C.POINTER(SampleArgs), C.c_void_p]
         _lib = L
     return _lib
 
@@ -496,6 +516,27 @@ class SamplerScratch:
             a.kept_ld = _ld(kept_ids)
         self._check(lib().lily_merge_draw(self._h, _stream_ptr(stream), _ptr(gathered), n_shards,
                                           rows, C.byref(a), _ptr(out_lse)))
+
+    def shard_publish(self, exchange: "PeerExchangeStruct", records, step: int, stream=None):
+        """lily_shard_publish: this rank's records (uint8 [rows, 520]) into every rank's buffer."""
+        self._check(lib().lily_shard_publish(self._h, _stream_ptr(stream), C.byref(exchange), _ptr(records),
+                                             int(records.shape[0]), step))
+
+    def merge_draw_peer(self, exchange: "PeerExchangeStruct", step: int, params, out_ids, *, uniforms=None,
+                        steps=None, out_status=None, kept_n=None, kept_ids=None, kept_probs=None, out_lse=None,
+                        stream=None):
+        """lily_merge_draw_peer: waits for every rank's flag of `step`, then merges."""
+        rows = len(params)
+        keep = []
+        a = self._shard_args(rows, params, steps, keep)
+        a.uniforms = _ptr(uniforms)
+        a.out_ids = _ptr(out_ids)
+        a.out_status = _ptr(out_status)
+        if kept_n is not None:
+            a.kept_n, a.kept_ids, a.kept_probs = _ptr(kept_n), _ptr(kept_ids), _ptr(kept_probs)
+            a.kept_ld = _ld(kept_ids)
+        self._check(lib().lily_merge_draw_peer(self._h, _stream_ptr(stream), C.byref(exchange), step,
+                                               C.byref(a), _ptr(out_lse)))
 
     def argmax_batch(self, logits, out_ids, stream=None):
         """src/kernels/elementwise.rs:297-308 argmax_f32 for each row."""

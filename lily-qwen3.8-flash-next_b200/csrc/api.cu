@@ -647,7 +647,8 @@ int32_t lily_sampler_status(lily_sampler_t *h, void *stream_) {
     CU(h, cudaMemsetAsync(h->status_word, 0, 4, stream));
     CU(h, cudaStreamSynchronize(stream));
     if (*h->h_status & (1u << lily_head::STATUS_TIMEOUT_BIT)) {
-        return fail(h, LILY_ERR_TIMEOUT, "a wait inside the LM-head kernel ran out; its logits are not valid");
+        return fail(h, LILY_ERR_TIMEOUT,
+                    "a bounded wait ran out (inside the LM-head kernel, or for a peer's records): the results are not valid");
     }
     if (*h->h_status != 0u) {
         char buf[96];
@@ -1319,6 +1320,130 @@ int32_t lily_merge_draw(lily_sampler_t *h, void *stream_, const void *gathered, 
     CU(h, cudaGetLastError());
     CU(h, cudaEventRecord(h->ev[slot], stream));
     return LILY_OK;
+}
+
+// ------------------------------------------------- records over peer memory --
+
+namespace {
+
+int32_t peer_args(lily_sampler *h, const lily_peer_exchange_t *x, lily::PeerArgs *p) {
+    if (x == nullptr || x->struct_size != sizeof(lily_peer_exchange_t)) {
+        return fail(h, LILY_ERR_ARG, "exchange is null or of another ABI version");
+    }
+    if (x->n_shards == 0u || x->n_shards > LILY_PEER_MAX || x->rank >= x->n_shards || x->max_rows == 0u) {
+        return fail(h, LILY_ERR_ARG, "1..16 shards, rank below them, max_rows set");
+    }
+    for (uint32_t r = 0; r < x->n_shards; ++r) {
+        if (x->buffers[r] == nullptr) {
+            return fail(h, LILY_ERR_ARG, "every rank's buffer must be set");
+        }
+        p->buffers[r] = x->buffers[r];
+    }
+    p->n_shards = x->n_shards;
+    p->rank = x->rank;
+    p->max_rows = x->max_rows;
+    p->status_word = h->status_word;
+    p->wait_ns = h->wait_ns;
+    return LILY_OK;
+}
+
+}  // namespace
+
+uint64_t lily_peer_buffer_bytes(uint32_t n_shards, uint32_t max_rows) {
+    return (uint64_t)lily::PEER_FLAG_BYTES + 2ull * n_shards * max_rows * sizeof(lily::ShardRecord);
+}
+
+int32_t lily_peer_buffer_create(int32_t device, uint32_t n_shards, uint32_t max_rows, void **buffer,
+                                void *ipc_handle) {
+    if (buffer == nullptr || ipc_handle == nullptr || n_shards == 0u || n_shards > LILY_PEER_MAX ||
+        max_rows == 0u) {
+        return LILY_ERR_ARG;
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == LILY_IPC_HANDLE_BYTES, "the handle travels as 64 bytes");
+    DeviceGuard guard(device);
+    const size_t bytes = lily_peer_buffer_bytes(n_shards, max_rows);
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        return LILY_ERR_CUDA;
+    }
+    cudaIpcMemHandle_t handle;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaIpcGetMemHandle(&handle, p) != cudaSuccess) {
+        cudaFree(p);
+        return LILY_ERR_CUDA;
+    }
+    std::memcpy(ipc_handle, &handle, sizeof handle);
+    *buffer = p;
+    return LILY_OK;
+}
+
+int32_t lily_peer_buffer_open(int32_t device, const void *ipc_handle, void **buffer) {
+    if (buffer == nullptr || ipc_handle == nullptr) {
+        return LILY_ERR_ARG;
+    }
+    DeviceGuard guard(device);
+    cudaIpcMemHandle_t handle;
+    std::memcpy(&handle, ipc_handle, sizeof handle);
+    return cudaIpcOpenMemHandle(buffer, handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? LILY_OK
+                                                                                                : LILY_ERR_CUDA;
+}
+
+int32_t lily_peer_buffer_close(int32_t device, void *buffer) {
+    DeviceGuard guard(device);
+    return buffer != nullptr && cudaIpcCloseMemHandle(buffer) == cudaSuccess ? LILY_OK : LILY_ERR_CUDA;
+}
+
+int32_t lily_peer_buffer_destroy(int32_t device, void *buffer) {
+    DeviceGuard guard(device);
+    return cudaFree(buffer) == cudaSuccess ? LILY_OK : LILY_ERR_CUDA;
+}
+
+int32_t lily_shard_publish(lily_sampler_t *h, void *stream_, const lily_peer_exchange_t *x,
+                           const void *records, uint32_t rows, uint32_t step) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    lily::PeerArgs p;
+    if ((st = peer_args(h, x, &p)) != LILY_OK) {
+        return st;
+    }
+    if (records == nullptr || rows == 0u || rows > x->max_rows || reinterpret_cast<uintptr_t>(records) % 8u) {
+        return fail(h, LILY_ERR_ARG, "records set and 8-byte aligned, 1 <= rows <= max_rows");
+    }
+    DeviceGuard guard(h->device);
+    p.records = static_cast<const lily::ShardRecord *>(records);
+    p.rows = rows;
+    p.step = step;
+    lily::shard_publish_kernel<<<x->n_shards, 256, 0, static_cast<cudaStream_t>(stream_)>>>(p);
+    CU(h, cudaGetLastError());
+    return LILY_OK;
+}
+
+int32_t lily_merge_draw_peer(lily_sampler_t *h, void *stream_, const lily_peer_exchange_t *x, uint32_t step,
+                             const lily_sample_args_t *args, float *out_lse) {
+    int32_t st = check_handle(h);
+    if (st != LILY_OK) {
+        return st;
+    }
+    lily::PeerArgs p;
+    if ((st = peer_args(h, x, &p)) != LILY_OK) {
+        return st;
+    }
+    if (args == nullptr || args->struct_size != sizeof(lily_sample_args_t) || args->rows > x->max_rows) {
+        return fail(h, LILY_ERR_ARG, "args is null, of another ABI version, or has more rows than max_rows");
+    }
+    {
+        DeviceGuard guard(h->device);
+        p.records = nullptr;
+        p.rows = args->rows;
+        p.step = step;
+        lily::peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(p);
+        CU(h, cudaGetLastError());
+    }
+    const char *slot = static_cast<const char *>(x->buffers[x->rank]) + lily::PEER_FLAG_BYTES +
+                       (size_t)(step & 1u) * x->n_shards * x->max_rows * sizeof(lily::ShardRecord);
+    return lily_merge_draw(h, stream_, slot, x->n_shards, x->max_rows, args, out_lse);
 }
 
 // ----------------------------------------------------------- speculation --

@@ -2936,6 +2936,71 @@ __global__ void __launch_bounds__(1024) shard_sums_kernel(const T *logits, uint6
     }
 }
 
+// ---- records over peer memory ------------------------------------------------
+//
+// A rank's exchange buffer: 64 flag words, then two slots of n_shards x max_rows
+// records (see lily_sampler.h). `buffers` are the ranks' buffers as this
+// process sees them: the own one in this GPU's memory, the others across NVLink.
+constexpr uint32_t PEER_MAX = 16;
+constexpr uint32_t PEER_FLAG_BYTES = 256;
+
+struct PeerArgs {
+    void *buffers[PEER_MAX];
+    const ShardRecord *records;  // publish: this rank's records of the step
+    uint32_t *status_word;
+    unsigned long long wait_ns;
+    uint32_t n_shards, rank, max_rows, rows, step;
+};
+
+__device__ __forceinline__ ShardRecord *peer_slot(void *buffer, const PeerArgs &p, uint32_t shard) {
+    return reinterpret_cast<ShardRecord *>(static_cast<char *>(buffer) + PEER_FLAG_BYTES) +
+           ((size_t)(p.step & 1u) * p.n_shards + shard) * p.max_rows;
+}
+
+// Grid (n_shards): block b writes this rank's records into rank b's buffer with
+// plain stores, fences them system-wide and then raises this rank's flag there.
+__global__ void __launch_bounds__(256) shard_publish_kernel(const __grid_constant__ PeerArgs p) {
+    void *buffer = p.buffers[blockIdx.x];
+    const uint2 *src = reinterpret_cast<const uint2 *>(p.records);
+    uint2 *dst = reinterpret_cast<uint2 *>(peer_slot(buffer, p, p.rank));
+    const uint32_t n8 = p.rows * (uint32_t)(sizeof(ShardRecord) / 8u);
+    for (uint32_t i = threadIdx.x; i < n8; i += 256u) {
+        dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t *flag = static_cast<uint32_t *>(buffer) + p.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.step) : "memory");
+    }
+}
+
+// One warp: lane s waits until rank s has raised its flag in the own buffer to
+// this step, for at most wait_ns; a wait that runs out sets bit 30 of the
+// status word (the merge that follows then reads what is there).
+__global__ void __launch_bounds__(32) peer_wait_kernel(const __grid_constant__ PeerArgs p) {
+    const uint32_t s = threadIdx.x;
+    bool late = false;
+    if (s < p.n_shards) {
+        const uint32_t *flag = static_cast<const uint32_t *>(p.buffers[p.rank]) + s;
+        const unsigned long long t0 = (unsigned long long)global_ns();
+        for (uint32_t spin = 0;; ++spin) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if ((int32_t)(v - p.step) >= 0) {
+                break;
+            }
+            if ((spin & 63u) == 63u && (unsigned long long)global_ns() - t0 > p.wait_ns) {
+                late = true;
+                break;
+            }
+        }
+    }
+    if (__any_sync(0xFFFFFFFFu, late) && s == 0) {
+        atomicOr(p.status_word, 1u << 30);
+    }
+}
+
 // src/kernels/metal/spec.metal:14-38, one thread.
 __global__ void spec_accept_kernel(const uint32_t *draws, const uint32_t *ids, uint32_t id_offset,
                                    uint32_t m, uint32_t *ctrl, uint32_t pos0, uint32_t ratio,

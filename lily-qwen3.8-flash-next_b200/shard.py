@@ -83,12 +83,13 @@ def gather_records(local_records, group=None):
 
 def sharded_lmhead_draw(scratch, weights, scales, hidden, params, out_ids, first_id: int, *,
                         uniforms=None, steps=None, records=None, want_sums: bool = False,
-                        out_lse=None, group=None, stream=None, **kept):
+                        out_lse=None, group=None, stream=None, exchange=None, **kept):
     """One vocab-sharded step on this rank: the 8-bit head over this rank's
     rows and its candidate records (lily_lmhead_shard_candidates), the
     all-gather of the records, the merged draw (lily_merge_draw). Every rank
     ends with the same token ids in `out_ids`. `scratch` was created with
-    lmhead=True for this rank's shard size."""
+    lmhead=True for this rank's shard size. With `exchange` (a PeerExchange) the
+    all-gather is the ranks' own stores into each other's memory instead."""
     import contextlib
 
     import torch
@@ -96,6 +97,14 @@ def sharded_lmhead_draw(scratch, weights, scales, hidden, params, out_ids, first
     rows = hidden.shape[0]
     if records is None:
         records = torch.empty((rows, RECORD_BYTES), dtype=torch.uint8, device=hidden.device)
+    if exchange is not None:
+        # No collective library on the data path: the records go straight into the
+        # other ranks' memory, and the merge waits for their flags.
+        scratch.lmhead_shard_candidates(weights, scales, hidden, params, records, first_id=first_id,
+                                        want_sums=want_sums, stream=stream)
+        exchange.publish_and_merge(scratch, records, params, out_ids, uniforms=uniforms, steps=steps,
+                                   out_lse=out_lse, stream=stream, **kept)
+        return None
     # The collective is ordered against torch's CURRENT stream only: a stream
     # that is given is made current for the whole step, so that the records are
     # written before the all-gather reads them and gathered before the merge.
@@ -107,3 +116,85 @@ def sharded_lmhead_draw(scratch, weights, scales, hidden, params, out_ids, first
         scratch.merge_draw(gathered, params, out_ids, uniforms=uniforms, steps=steps, out_lse=out_lse,
                            stream=stream, **kept)
     return gathered
+
+
+class PeerExchange:
+    """The exchange of the shards' records over peer memory (lily_shard_publish /
+    lily_merge_draw_peer): one buffer per rank, opened by every other rank through
+    its inter-process handle, which travels once through torch.distributed (any
+    backend) when the exchange is set up. One process per GPU, all on one node.
+
+    `emulate` > 0: no process group; this process plays that many ranks on one GPU
+    with one buffer (for tests: the ranks publish one after the other, then merge)."""
+
+    def __init__(self, device: int, max_rows: int, group=None, emulate: int = 0):
+        import ctypes as C
+
+        import lily_b200 as lily
+
+        self._lily, self._C, self.device, self.max_rows, self.step = lily, C, device, max_rows, 0
+        self._opened = []
+        L = lily.lib()
+        if emulate:
+            self.world, self.rank = emulate, 0
+        else:
+            import torch.distributed as dist
+
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > lily.PEER_MAX:
+            raise ValueError("at most 16 ranks")
+        own = C.c_void_p()
+        handle = (C.c_ubyte * lily.IPC_HANDLE_BYTES)()
+        st = L.lily_peer_buffer_create(device, self.world, max_rows, C.byref(own), handle)
+        if st != lily.OK:
+            raise lily.LilyError(st, "lily_peer_buffer_create failed")
+        self._own = own
+        x = lily.PeerExchangeStruct()
+        x.struct_size = C.sizeof(lily.PeerExchangeStruct)
+        x.n_shards, x.rank, x.max_rows = self.world, self.rank, max_rows
+        if emulate:
+            for r in range(self.world):
+                x.buffers[r] = own.value
+        else:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            for r in range(self.world):
+                if r == self.rank:
+                    x.buffers[r] = own.value
+                    continue
+                theirs = C.c_void_p()
+                raw = (C.c_ubyte * lily.IPC_HANDLE_BYTES).from_buffer_copy(handles[r])
+                st = L.lily_peer_buffer_open(device, raw, C.byref(theirs))
+                if st != lily.OK:
+                    raise lily.LilyError(st, f"lily_peer_buffer_open failed for rank {r} (no peer access?)")
+                self._opened.append(theirs)
+                x.buffers[r] = theirs.value
+            dist.barrier(group=group)
+        self.x = x
+        self._group = group
+
+    def as_rank(self, rank: int):
+        """(emulation) the exchange as rank `rank` sees it."""
+        self.x.rank = rank
+        return self.x
+
+    def publish_and_merge(self, scratch, records, params, out_ids, *, stream=None, **kw):
+        self.step += 1
+        scratch.shard_publish(self.x, records, self.step, stream=stream)
+        scratch.merge_draw_peer(self.x, self.step, params, out_ids, stream=stream, **kw)
+
+    def close(self):
+        L = self._lily.lib()
+        if self._own is None:
+            return
+        if self._opened:
+            import torch
+            import torch.distributed as dist
+
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self._group)  # nobody writes into a buffer that is going away
+            for p in self._opened:
+                L.lily_peer_buffer_close(self.device, p)
+            dist.barrier(group=self._group)
+        L.lily_peer_buffer_destroy(self.device, self._own)
+        self._own = None

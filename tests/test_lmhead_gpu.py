@@ -354,3 +354,57 @@ def test_a_wait_that_runs_out_returns_with_a_named_status(cuda, lily):
     assert scratch.status() == lily.OK
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
     scratch.close()
+
+
+@pytest.mark.parametrize("n_shards", [2, 8])
+def test_records_through_peer_memory_one_gpu_playing_every_rank(cuda, lily, n_shards):
+    """lily_shard_publish / lily_merge_draw_peer with one GPU in the part of every
+    rank (one exchange buffer, the ranks publish one after the other): three steps,
+    so that both slots and the step counter are used; each has to give what
+    lily_merge_draw gives on the same records handed over as one tensor."""
+    torch = cuda
+    import workloads as wl
+    from lily_b200.shard import PeerExchange
+
+    rows, vocab = 12, 65_536
+    per = vocab // n_shards
+    rng = np.random.default_rng([75, n_shards])
+    plist = [dict(temperature=[0.7, 1.0, 0.0, 0.9][r % 4], top_k=[40, 64, 1, 7][r % 4],
+                  top_p=[0.95, 1.0, 1.0, 0.8][r % 4], seed=r) for r in range(rows)]
+    params = [lily.SamplingParams(**p) for p in plist]
+    shard = lily.SamplerScratch(per, max_rows=rows)
+    ex = PeerExchange(torch.cuda.current_device(), max_rows=16, emulate=n_shards)
+    for step in range(3):
+        logits = t_f32(torch, wl.zipf_logits(rng, rows, vocab))
+        u = t_f32(torch, np.array([oracle.uniform_for(800 + r, step) for r in range(rows)], dtype=np.float32))
+        rec = _records(torch, n_shards, rows)
+        for s in range(n_shards):
+            shard.shard_candidates(logits[:, s * per:(s + 1) * per].contiguous(), params, rec[s],
+                                   first_id=s * per, want_sums=True)
+        want, want_lse = (torch.zeros(rows, dtype=torch.int32, device="cuda"),
+                          torch.zeros(rows, dtype=torch.float32, device="cuda"))
+        shard.merge_draw(rec, params, want, uniforms=u, out_lse=want_lse)
+        got, got_lse = torch.full_like(want, -1), torch.zeros_like(want_lse)
+        ex.step += 1
+        for s in range(n_shards):
+            shard.shard_publish(ex.as_rank(s), rec[s], ex.step)
+        shard.merge_draw_peer(ex.as_rank(n_shards - 1), ex.step, params, got, uniforms=u, out_lse=got_lse)
+        torch.cuda.synchronize()
+        assert shard.status() == lily.OK
+        assert torch.equal(got, want) and torch.equal(got_lse, want_lse), f"step {step}"
+    # A rank that never publishes: the wait runs out at its limit, the call returns,
+    # and the status says so (failure detection without a fault).
+    shard.set_wait_limit(2_000_000)
+    ex.step += 1
+    for s in range(n_shards - 1):
+        shard.shard_publish(ex.as_rank(s), rec[s], ex.step)
+    shard.merge_draw_peer(ex.as_rank(0), ex.step, params, got, uniforms=u)
+    torch.cuda.synchronize()
+    assert shard.status() == lily.ERR_TIMEOUT
+    shard.set_wait_limit(0)
+    shard.shard_publish(ex.as_rank(n_shards - 1), rec[n_shards - 1], ex.step)
+    shard.merge_draw_peer(ex.as_rank(0), ex.step, params, got, uniforms=u, out_lse=got_lse)
+    torch.cuda.synchronize()
+    assert shard.status() == lily.OK and torch.equal(got, want)
+    ex.close()
+    shard.close()
