@@ -473,7 +473,16 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
     out = torch.zeros(tokens, dtype=torch.int32, device=dev)
     logits = torch.empty((tokens, per), dtype=torch.float32, device=dev)
 
+    # More than one rank: the records travel by the ranks' own stores into each
+    # other's memory (lily_shard_publish / lily_merge_draw_peer); the all-gather
+    # through NCCL is timed beside it.
+    exchange = sh.PeerExchange(dev.index, max_rows=tokens) if world > 1 else None
+
     def step(i):
+        sh.sharded_lmhead_draw(scratch, ws[i % copies], sc, h, params, out, first_id=rank * per,
+                               uniforms=u, records=rec, want_sums=True, stream=stream, exchange=exchange)
+
+    def step_nccl(i):
         sh.sharded_lmhead_draw(scratch, ws[i % copies], sc, h, params, out, first_id=rank * per,
                                uniforms=u, records=rec, want_sums=True, stream=stream)
 
@@ -500,6 +509,15 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
         return ms / n
 
     step_ms = timed(step, steps)
+    nccl_ms, same = None, True
+    if world > 1:
+        step(0)
+        torch.cuda.synchronize()
+        by_peer = out.clone()
+        nccl_ms = timed(step_nccl, steps)
+        step_nccl(0)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(by_peer, out))
     head_ms = timed(lambda i: scratch.lmhead_logits(ws[i % copies], sc, h, logits, stream=stream), steps)
     # The same head read as the reference's MLX affine 8-bit storage (the
     # bytes as unsigned codes, plus a bias per 64 columns).
@@ -522,6 +540,8 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
         every = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(every, out)
         agree = all(bool(torch.equal(every[0], e)) for e in every)
+    if exchange is not None:
+        exchange.close()
     scratch.close()
     head_bytes = per * hidden + per * (hidden // 64) * 2 + tokens * hidden * 2
     peak, peak_kind = peaks()
@@ -529,6 +549,9 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
     return {"workload": "hidden bf16 [64,4096] x int8 head [262144,4096], bf16 scales per 64 columns, "
                         f"{world} vocabulary shard(s); top-k 40, top-p 0.95, T 0.7",
             "n_gpus": world, "scaling": "strong", "us_per_step": step_ms * 1e3,
+            "exchange": "one rank" if world == 1 else "peer stores + flags (lily_shard_publish, lily_merge_draw_peer)",
+            "us_per_step_nccl_allgather": None if nccl_ms is None else nccl_ms * 1e3,
+            "peer_equals_nccl": same,
             "rows_per_s": tokens / (step_ms * 1e-3), "steps": steps,
             "head_kernel_us": head_ms * 1e3, "head_bytes_per_gpu": head_bytes,
             "head_gbs_per_gpu": gbs, "head_frac_of_hbm": gbs / peak, "peak_kind": peak_kind,
