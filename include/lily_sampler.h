@@ -478,20 +478,23 @@ int32_t lily_merge_draw(lily_sampler_t *h, void *stream, const void *gathered, u
  * flag there; the merge waits for the flags. No counterpart in the reference.
  *
  * A rank owns one exchange buffer (lily_peer_buffer_create: device memory of
- * lily_peer_buffer_bytes, zeroed, and its 64-byte inter-process handle). The
+ * lily_peer_buffer_bytes, zeroed, and its 64-byte inter-process handle): a flag
+ * word per (rank, row), then two slots of n_shards x max_rows records. The
  * ranks pass the handles around by any means, open each other's buffers
  * (lily_peer_buffer_open: the buffer as THIS process sees it; peer access is
  * enabled on the way) and fill a lily_peer_exchange_t, own buffer included.
- * Per step, with `step` counting 1, 2, 3, ... on every rank alike:
- *
- *   lily_shard_publish     one kernel: this rank's `rows` records into slot
- *                          (step & 1, rank) of every buffer, a system-wide
- *                          fence, then flag[rank] := step in every buffer;
- *   lily_merge_draw_peer   one small kernel that waits until all n_shards flags
- *                          of the OWN buffer have reached `step` (bounded by
- *                          lily_sampler_set_wait_limit; on time-out the status
- *                          becomes LILY_ERR_TIMEOUT and the draw is not valid),
- *                          then lily_merge_draw on slot (step & 1).
+ * Per step, with `step` counting 1, 2, 3, ... on every rank alike, ONE call and
+ * one kernel, lily_merge_draw_peer: the block of row r writes this rank's record
+ * of the row (`records`, as lily_shard_candidates left them) into slot
+ * (step & 1, rank) of every buffer, fences system-wide and sets flag[rank][r] :=
+ * step there; then it waits until the n_shards flags of row r in the OWN buffer
+ * have reached `step` (bounded by lily_sampler_set_wait_limit; on time-out the
+ * status becomes LILY_ERR_TIMEOUT and the draw is not valid) and merges the
+ * row as lily_merge_draw does. Rows wait for nothing but their own records, so
+ * the exchange of one row overlaps the merge of another.
+ * lily_shard_publish does the first half alone, for all rows at once (a rank
+ * that publishes apart from its merge then passes records = NULL to
+ * lily_merge_draw_peer).
  *
  * Two slots suffice: a rank cannot publish step n + 2 before it has merged step
  * n + 1, which every rank publishes only after it has merged step n. All ranks
@@ -516,8 +519,9 @@ int32_t lily_peer_buffer_close(int32_t device, void *buffer);
 int32_t lily_peer_buffer_destroy(int32_t device, void *buffer);
 int32_t lily_shard_publish(lily_sampler_t *h, void *stream, const lily_peer_exchange_t *x,
                            const void *records, uint32_t rows, uint32_t step);
-int32_t lily_merge_draw_peer(lily_sampler_t *h, void *stream, const lily_peer_exchange_t *x, uint32_t step,
-                             const lily_sample_args_t *args, float *out_lse);
+int32_t lily_merge_draw_peer(lily_sampler_t *h, void *stream, const lily_peer_exchange_t *x,
+                             const void *records, uint32_t step, const lily_sample_args_t *args,
+                             float *out_lse);
 
 /* ------------------------------------------------------------------ test -- */
 

@@ -211,8 +211,8 @@ def lib():
         L.lily_peer_buffer_destroy.argtypes = [C.c_int32, C.c_void_p]
         L.lily_shard_publish.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(PeerExchangeStruct), C.c_void_p,
                                          C.c_uint32, C.c_uint32]
-        L.lily_merge_draw_peer.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(PeerExchangeStruct), C.c_uint32,
-                                           C.POINTER(SampleArgs), C.c_void_p]
+        L.lily_merge_draw_peer.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(PeerExchangeStruct), C.c_void_p,
+                                           C.c_uint32, C.POINTER(SampleArgs), C.c_void_p]
         _lib = L
     return _lib
 
@@ -522,10 +522,12 @@ class SamplerScratch:
         self._check(lib().lily_shard_publish(self._h, _stream_ptr(stream), C.byref(exchange), _ptr(records),
                                              int(records.shape[0]), step))
 
-    def merge_draw_peer(self, exchange: "PeerExchangeStruct", step: int, params, out_ids, *, uniforms=None,
-                        steps=None, out_status=None, kept_n=None, kept_ids=None, kept_probs=None, out_lse=None,
-                        stream=None):
-        """lily_merge_draw_peer: waits for every rank's flag of `step`, then merges."""
+    def merge_draw_peer(self, exchange: "PeerExchangeStruct", step: int, params, out_ids, *, records=None,
+                        uniforms=None, steps=None, out_status=None, kept_n=None, kept_ids=None, kept_probs=None,
+                        out_lse=None, stream=None):
+        """lily_merge_draw_peer: a row's block publishes this rank's record of the row
+        (`records`, uint8 [rows, 520]; None: published already), waits for every
+        rank's flag of the row, then merges."""
         rows = len(params)
         keep = []
         a = self._shard_args(rows, params, steps, keep)
@@ -535,8 +537,8 @@ class SamplerScratch:
         if kept_n is not None:
             a.kept_n, a.kept_ids, a.kept_probs = _ptr(kept_n), _ptr(kept_ids), _ptr(kept_probs)
             a.kept_ld = _ld(kept_ids)
-        self._check(lib().lily_merge_draw_peer(self._h, _stream_ptr(stream), C.byref(exchange), step,
-                                               C.byref(a), _ptr(out_lse)))
+        self._check(lib().lily_merge_draw_peer(self._h, _stream_ptr(stream), C.byref(exchange), _ptr(records),
+                                               step, C.byref(a), _ptr(out_lse)))
 
     def argmax_batch(self, logits, out_ids, stream=None):
         """src/kernels/elementwise.rs:297-308 argmax_f32 for each row."""

@@ -1264,8 +1264,23 @@ int32_t lily_lmhead_shard_candidates(lily_sampler_t *h, void *stream_, const lil
     return shard_candidates(h, stream, g, first_id, want_sums, records);
 }
 
+namespace {
+int32_t merge_draw(lily_sampler_t *h, void *stream_, const void *gathered, uint32_t n_shards,
+                   uint64_t shard_stride, const lily_sample_args_t *args, float *out_lse,
+                   const lily::KArgs::PeerLink *peer);
+
+}  // namespace
+
 int32_t lily_merge_draw(lily_sampler_t *h, void *stream_, const void *gathered, uint32_t n_shards,
                         uint64_t shard_stride, const lily_sample_args_t *args, float *out_lse) {
+    return merge_draw(h, stream_, gathered, n_shards, shard_stride, args, out_lse, nullptr);
+}
+
+namespace {
+
+int32_t merge_draw(lily_sampler_t *h, void *stream_, const void *gathered, uint32_t n_shards,
+                   uint64_t shard_stride, const lily_sample_args_t *args, float *out_lse,
+                   const lily::KArgs::PeerLink *peer) {
     int32_t st = check_handle(h);
     if (st != LILY_OK) {
         return st;
@@ -1316,17 +1331,22 @@ int32_t lily_merge_draw(lily_sampler_t *h, void *stream_, const void *gathered, 
     a.merge_shards = n_shards;
     a.merge_stride = shard_stride;
     a.out_lse = out_lse;
+    if (peer != nullptr) {
+        a.peer = *peer;
+    }
     lily::merge_rows_kernel<<<g.rows, lily::NT, sizeof(lily::SmemFixed), stream>>>(a);
     CU(h, cudaGetLastError());
     CU(h, cudaEventRecord(h->ev[slot], stream));
     return LILY_OK;
 }
 
+}  // namespace
+
 // ------------------------------------------------- records over peer memory --
 
 namespace {
 
-int32_t peer_args(lily_sampler *h, const lily_peer_exchange_t *x, lily::PeerArgs *p) {
+int32_t peer_check(lily_sampler *h, const lily_peer_exchange_t *x) {
     if (x == nullptr || x->struct_size != sizeof(lily_peer_exchange_t)) {
         return fail(h, LILY_ERR_ARG, "exchange is null or of another ABI version");
     }
@@ -1337,20 +1357,15 @@ int32_t peer_args(lily_sampler *h, const lily_peer_exchange_t *x, lily::PeerArgs
         if (x->buffers[r] == nullptr) {
             return fail(h, LILY_ERR_ARG, "every rank's buffer must be set");
         }
-        p->buffers[r] = x->buffers[r];
     }
-    p->n_shards = x->n_shards;
-    p->rank = x->rank;
-    p->max_rows = x->max_rows;
-    p->status_word = h->status_word;
-    p->wait_ns = h->wait_ns;
     return LILY_OK;
 }
 
 }  // namespace
 
 uint64_t lily_peer_buffer_bytes(uint32_t n_shards, uint32_t max_rows) {
-    return (uint64_t)lily::PEER_FLAG_BYTES + 2ull * n_shards * max_rows * sizeof(lily::ShardRecord);
+    return (uint64_t)lily::peer_flag_bytes(n_shards, max_rows) +
+           2ull * n_shards * max_rows * sizeof(lily::ShardRecord);
 }
 
 int32_t lily_peer_buffer_create(int32_t device, uint32_t n_shards, uint32_t max_rows, void **buffer,
@@ -1404,14 +1419,21 @@ int32_t lily_shard_publish(lily_sampler_t *h, void *stream_, const lily_peer_exc
     if (st != LILY_OK) {
         return st;
     }
-    lily::PeerArgs p;
-    if ((st = peer_args(h, x, &p)) != LILY_OK) {
+    if ((st = peer_check(h, x)) != LILY_OK) {
         return st;
     }
     if (records == nullptr || rows == 0u || rows > x->max_rows || reinterpret_cast<uintptr_t>(records) % 8u) {
         return fail(h, LILY_ERR_ARG, "records set and 8-byte aligned, 1 <= rows <= max_rows");
     }
     DeviceGuard guard(h->device);
+    lily::PeerArgs p;
+    std::memset(&p, 0, sizeof p);
+    for (uint32_t r = 0; r < x->n_shards; ++r) {
+        p.buffers[r] = x->buffers[r];
+    }
+    p.n_shards = x->n_shards;
+    p.rank = x->rank;
+    p.max_rows = x->max_rows;
     p.records = static_cast<const lily::ShardRecord *>(records);
     p.rows = rows;
     p.step = step;
@@ -1420,30 +1442,37 @@ int32_t lily_shard_publish(lily_sampler_t *h, void *stream_, const lily_peer_exc
     return LILY_OK;
 }
 
-int32_t lily_merge_draw_peer(lily_sampler_t *h, void *stream_, const lily_peer_exchange_t *x, uint32_t step,
-                             const lily_sample_args_t *args, float *out_lse) {
+int32_t lily_merge_draw_peer(lily_sampler_t *h, void *stream_, const lily_peer_exchange_t *x,
+                             const void *records, uint32_t step, const lily_sample_args_t *args,
+                             float *out_lse) {
     int32_t st = check_handle(h);
     if (st != LILY_OK) {
         return st;
     }
-    lily::PeerArgs p;
-    if ((st = peer_args(h, x, &p)) != LILY_OK) {
+    if ((st = peer_check(h, x)) != LILY_OK) {
         return st;
     }
     if (args == nullptr || args->struct_size != sizeof(lily_sample_args_t) || args->rows > x->max_rows) {
         return fail(h, LILY_ERR_ARG, "args is null, of another ABI version, or has more rows than max_rows");
     }
-    {
-        DeviceGuard guard(h->device);
-        p.records = nullptr;
-        p.rows = args->rows;
-        p.step = step;
-        lily::peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(p);
-        CU(h, cudaGetLastError());
+    if (reinterpret_cast<uintptr_t>(records) % 8u) {
+        return fail(h, LILY_ERR_ARG, "records must be 8-byte aligned");
     }
-    const char *slot = static_cast<const char *>(x->buffers[x->rank]) + lily::PEER_FLAG_BYTES +
+    lily::KArgs::PeerLink peer;
+    std::memset(&peer, 0, sizeof peer);
+    for (uint32_t r = 0; r < x->n_shards; ++r) {
+        peer.buffers[r] = x->buffers[r];
+    }
+    peer.own = records;
+    peer.wait_ns = h->wait_ns;
+    peer.n = x->n_shards;
+    peer.rank = x->rank;
+    peer.max_rows = x->max_rows;
+    peer.step = step;
+    const char *slot = static_cast<const char *>(x->buffers[x->rank]) +
+                       lily::peer_flag_bytes(x->n_shards, x->max_rows) +
                        (size_t)(step & 1u) * x->n_shards * x->max_rows * sizeof(lily::ShardRecord);
-    return lily_merge_draw(h, stream_, slot, x->n_shards, x->max_rows, args, out_lse);
+    return merge_draw(h, stream_, slot, x->n_shards, x->max_rows, args, out_lse, &peer);
 }
 
 // ----------------------------------------------------------- speculation --

@@ -136,6 +136,16 @@ struct KArgs {
     const ShardRecord *merge_in;   // [merge_shards, merge_stride >= rows]
     uint32_t merge_shards;
     uint64_t merge_stride;         // records between two shards
+    // The merge of a step whose records travel over peer memory (n == 0: not so):
+    // a row's block first writes this rank's record of the row into every rank's
+    // buffer and raises the row's flag there, then waits for the row's flags of
+    // all ranks in its own buffer.
+    struct PeerLink {
+        void *buffers[16];         // rank r's exchange buffer as this process sees it
+        const void *own;           // this rank's records of the step (null: already published)
+        unsigned long long wait_ns;
+        uint32_t n, rank, max_rows, step;
+    } peer;
     float *out_lse;                // optional [rows]: log of the sum over the vocabulary of exp(adjusted)
     SpecArgs spec;
 };
@@ -2759,11 +2769,16 @@ __device__ __noinline__ void sample_whole_row(const KArgs &a, uint32_t row) {
 // candidate the row's top-k can contain (each shard kept its own best
 // shard_k >= k), so selecting, cutting and drawing over their union gives
 // what one pass over the whole vocabulary gives. One block per row.
+__device__ __forceinline__ void peer_exchange_row(const KArgs &a, uint32_t row);
+
 __global__ void __launch_bounds__(NT, 2) merge_rows_kernel(const __grid_constant__ KArgs a) {
     extern __shared__ uint4 smem_raw[];
     SmemFixed *sm = reinterpret_cast<SmemFixed *>(smem_raw);
     const uint32_t tid = threadIdx.x;
     const uint32_t row = a.row0 + blockIdx.x;
+    if (a.peer.n != 0u) {
+        peer_exchange_row(a, row);  // the row's records of all ranks are in the own buffer after this
+    }
     const lily_sampling_params_t P = a.params[row];
     const bool greedy = P.temperature <= 0.0f || P.top_k == 1u;
     if (tid == 0) {
@@ -2938,67 +2953,96 @@ __global__ void __launch_bounds__(1024) shard_sums_kernel(const T *logits, uint6
 
 // ---- records over peer memory ------------------------------------------------
 //
-// A rank's exchange buffer: 64 flag words, then two slots of n_shards x max_rows
-// records (see lily_sampler.h). `buffers` are the ranks' buffers as this
-// process sees them: the own one in this GPU's memory, the others across NVLink.
+// A rank's exchange buffer: a flag word per (rank, row), then two slots of
+// n_shards x max_rows records (see lily_sampler.h). `buffers` are the ranks'
+// buffers as this process sees them: the own one in this GPU's memory, the
+// others across NVLink. Only plain loads and stores go there.
 constexpr uint32_t PEER_MAX = 16;
-constexpr uint32_t PEER_FLAG_BYTES = 256;
+
+__host__ __device__ inline uint32_t peer_flag_bytes(uint32_t n_shards, uint32_t max_rows) {
+    return (n_shards * max_rows * 4u + 255u) & ~255u;
+}
 
 struct PeerArgs {
     void *buffers[PEER_MAX];
-    const ShardRecord *records;  // publish: this rank's records of the step
-    uint32_t *status_word;
-    unsigned long long wait_ns;
+    const ShardRecord *records;  // this rank's records of the step
     uint32_t n_shards, rank, max_rows, rows, step;
 };
 
-__device__ __forceinline__ ShardRecord *peer_slot(void *buffer, const PeerArgs &p, uint32_t shard) {
-    return reinterpret_cast<ShardRecord *>(static_cast<char *>(buffer) + PEER_FLAG_BYTES) +
-           ((size_t)(p.step & 1u) * p.n_shards + shard) * p.max_rows;
+__device__ __forceinline__ ShardRecord *peer_slot(void *buffer, uint32_t n_shards, uint32_t max_rows,
+                                                  uint32_t step, uint32_t shard) {
+    return reinterpret_cast<ShardRecord *>(static_cast<char *>(buffer) + peer_flag_bytes(n_shards, max_rows)) +
+           ((size_t)(step & 1u) * n_shards + shard) * max_rows;
+}
+
+__device__ __forceinline__ void peer_raise(void *buffer, uint32_t max_rows, uint32_t rank, uint32_t row,
+                                           uint32_t step) {
+    uint32_t *flag = static_cast<uint32_t *>(buffer) + (size_t)rank * max_rows + row;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
 }
 
 // Grid (n_shards): block b writes this rank's records into rank b's buffer with
-// plain stores, fences them system-wide and then raises this rank's flag there.
+// plain stores, fences them system-wide and then raises this rank's flag of
+// every row there. (The merge kernel does the same for its own row when it is
+// given the records; this kernel serves a rank that publishes apart from its
+// merge, and one GPU that plays several ranks in a test.)
 __global__ void __launch_bounds__(256) shard_publish_kernel(const __grid_constant__ PeerArgs p) {
     void *buffer = p.buffers[blockIdx.x];
     const uint2 *src = reinterpret_cast<const uint2 *>(p.records);
-    uint2 *dst = reinterpret_cast<uint2 *>(peer_slot(buffer, p, p.rank));
+    uint2 *dst = reinterpret_cast<uint2 *>(peer_slot(buffer, p.n_shards, p.max_rows, p.step, p.rank));
     const uint32_t n8 = p.rows * (uint32_t)(sizeof(ShardRecord) / 8u);
     for (uint32_t i = threadIdx.x; i < n8; i += 256u) {
         dst[i] = src[i];
     }
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t *flag = static_cast<uint32_t *>(buffer) + p.rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.step) : "memory");
+    for (uint32_t r = threadIdx.x; r < p.rows; r += 256u) {
+        peer_raise(buffer, p.max_rows, p.rank, r, p.step);
     }
 }
 
-// One warp: lane s waits until rank s has raised its flag in the own buffer to
-// this step, for at most wait_ns; a wait that runs out sets bit 30 of the
-// status word (the merge that follows then reads what is there).
-__global__ void __launch_bounds__(32) peer_wait_kernel(const __grid_constant__ PeerArgs p) {
-    const uint32_t s = threadIdx.x;
-    bool late = false;
-    if (s < p.n_shards) {
-        const uint32_t *flag = static_cast<const uint32_t *>(p.buffers[p.rank]) + s;
-        const unsigned long long t0 = (unsigned long long)global_ns();
-        for (uint32_t spin = 0;; ++spin) {
-            uint32_t v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if ((int32_t)(v - p.step) >= 0) {
-                break;
-            }
-            if ((spin & 63u) == 63u && (unsigned long long)global_ns() - t0 > p.wait_ns) {
-                late = true;
-                break;
-            }
+// A row's block of the merge kernel, before it merges: publishes this rank's
+// record of the row (if given), then waits, for at most wait_ns, until every
+// rank's flag of the row in the own buffer has reached the step. A wait that
+// runs out sets bit 30 of the status word; the merge then reads what is there.
+__device__ __forceinline__ void peer_exchange_row(const KArgs &a, uint32_t row) {
+    const KArgs::PeerLink &p = a.peer;
+    const uint32_t tid = threadIdx.x;
+    constexpr uint32_t W = (uint32_t)(sizeof(ShardRecord) / 8u);  // 8-byte words of a record
+    if (p.own != nullptr) {
+        const uint2 *src = reinterpret_cast<const uint2 *>(static_cast<const ShardRecord *>(p.own) + row);
+        for (uint32_t i = tid; i < p.n * W; i += NT) {
+            const uint32_t to = i / W, w = i % W;
+            reinterpret_cast<uint2 *>(peer_slot(p.buffers[to], p.n, p.max_rows, p.step, p.rank) + row)[w] = src[w];
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid < p.n) {
+            peer_raise(p.buffers[tid], p.max_rows, p.rank, row, p.step);
         }
     }
-    if (__any_sync(0xFFFFFFFFu, late) && s == 0) {
-        atomicOr(p.status_word, 1u << 30);
+    if (tid < 32u) {
+        bool late = false;
+        if (tid < p.n) {
+            const uint32_t *flag = static_cast<const uint32_t *>(p.buffers[p.rank]) + (size_t)tid * p.max_rows + row;
+            const unsigned long long t0 = (unsigned long long)global_ns();
+            for (uint32_t spin = 0;; ++spin) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                if ((int32_t)(v - p.step) >= 0) {
+                    break;
+                }
+                if ((spin & 63u) == 63u && (unsigned long long)global_ns() - t0 > p.wait_ns) {
+                    late = true;
+                    break;
+                }
+            }
+        }
+        if (__any_sync(0xFFFFFFFFu, late) && tid == 0) {
+            atomicOr(a.status_word, 1u << 30);
+        }
     }
+    __syncthreads();
 }
 
 // src/kernels/metal/spec.metal:14-38, one thread.

@@ -180,8 +180,7 @@ class PeerExchange:
 
     def publish_and_merge(self, scratch, records, params, out_ids, *, stream=None, **kw):
         self.step += 1
-        scratch.shard_publish(self.x, records, self.step, stream=stream)
-        scratch.merge_draw_peer(self.x, self.step, params, out_ids, stream=stream, **kw)
+        scratch.merge_draw_peer(self.x, self.step, params, out_ids, records=records, stream=stream, **kw)
 
     def close(self):
         L = self._lily.lib()

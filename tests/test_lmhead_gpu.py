@@ -385,10 +385,13 @@ def test_records_through_peer_memory_one_gpu_playing_every_rank(cuda, lily, n_sh
                           torch.zeros(rows, dtype=torch.float32, device="cuda"))
         shard.merge_draw(rec, params, want, uniforms=u, out_lse=want_lse)
         got, got_lse = torch.full_like(want, -1), torch.zeros_like(want_lse)
+        # The other ranks publish apart from their merge; the last one in one call.
         ex.step += 1
-        for s in range(n_shards):
+        last = n_shards - 1
+        for s in range(last):
             shard.shard_publish(ex.as_rank(s), rec[s], ex.step)
-        shard.merge_draw_peer(ex.as_rank(n_shards - 1), ex.step, params, got, uniforms=u, out_lse=got_lse)
+        shard.merge_draw_peer(ex.as_rank(last), ex.step, params, got, records=rec[last], uniforms=u,
+                              out_lse=got_lse)
         torch.cuda.synchronize()
         assert shard.status() == lily.OK
         assert torch.equal(got, want) and torch.equal(got_lse, want_lse), f"step {step}"
@@ -396,14 +399,14 @@ def test_records_through_peer_memory_one_gpu_playing_every_rank(cuda, lily, n_sh
     # and the status says so (failure detection without a fault).
     shard.set_wait_limit(2_000_000)
     ex.step += 1
-    for s in range(n_shards - 1):
+    for s in range(1, last):
         shard.shard_publish(ex.as_rank(s), rec[s], ex.step)
-    shard.merge_draw_peer(ex.as_rank(0), ex.step, params, got, uniforms=u)
+    shard.merge_draw_peer(ex.as_rank(last), ex.step, params, got, records=rec[last], uniforms=u)
     torch.cuda.synchronize()
     assert shard.status() == lily.ERR_TIMEOUT
     shard.set_wait_limit(0)
-    shard.shard_publish(ex.as_rank(n_shards - 1), rec[n_shards - 1], ex.step)
-    shard.merge_draw_peer(ex.as_rank(0), ex.step, params, got, uniforms=u, out_lse=got_lse)
+    shard.shard_publish(ex.as_rank(0), rec[0], ex.step)
+    shard.merge_draw_peer(ex.as_rank(last), ex.step, params, got, uniforms=u, out_lse=got_lse)
     torch.cuda.synchronize()
     assert shard.status() == lily.OK and torch.equal(got, want)
     ex.close()
