@@ -198,6 +198,15 @@ int32_t raise_smem_limit(lily_sampler *h, Kernel kernel, uint32_t bit) {
     return LILY_OK;
 }
 
+// Whether a call goes to the kernel of one block per row (see launch_one).
+bool stream_route(const lily::KArgs &a, uint32_t rows, uint32_t dtype) {
+    const size_t esize = dtype == LILY_F32 ? 4 : 2;
+    const bool vec = (reinterpret_cast<uintptr_t>(a.logits) % 16u == 0u) && ((a.logits_ld * esize) % 16u == 0u);
+    const uint32_t round = dtype == LILY_F32 ? lily::Geo<float>::ROUND : lily::Geo<__nv_bfloat16>::ROUND;
+    return vec && a.vocab / round >= lily::STREAM_MIN_ROUNDS && a.merge_in == nullptr && a.spec.n_spec == 0u &&
+           a.extra_len == 0u && rows >= 16u && (a.cand_out == nullptr || a.shard_k <= lily::STREAM_K_MAX);
+}
+
 template <typename T, bool VEC>
 int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, uint32_t rows,
                    size_t smem) {
@@ -209,10 +218,7 @@ int32_t launch_one(lily_sampler *h, cudaStream_t stream_, const lily::KArgs &a, 
     // ring. A vocabulary shard's candidate launch goes the same way and ends in the
     // rows' records. (Short rows, unaligned logits, speculative calls and the merge
     // of shards: the general kernel, rows cut into slices.)
-    constexpr uint32_t round = lily::Geo<T>::ROUND;
-    const bool stream = VEC && a.vocab / round >= lily::STREAM_MIN_ROUNDS && a.merge_in == nullptr &&
-                        a.spec.n_spec == 0u && a.extra_len == 0u && rows >= 16u &&
-                        (a.cand_out == nullptr || a.shard_k <= lily::STREAM_K_MAX);
+    const bool stream = VEC && stream_route(a, rows, sizeof(T) == 4 ? LILY_F32 : LILY_BF16);
     if (stream) {
         lily::KArgs whole = a;
         whole.n_slices = 1;
@@ -1179,8 +1185,10 @@ int32_t shard_candidates(lily_sampler *h, cudaStream_t stream, const lily_sample
     a.id_offset = first_id;
     a.cand_out = static_cast<lily::ShardRecord *>(records);
     a.n_slices = choose_slices(h, g.rows);
+    // (The kernel of one block per row sums the exponentials in the same pass.)
+    a.shard_sums = want_sums && stream_route(a, g.rows, g.logits_dtype) ? 1u : 0u;
     st = launch(h, stream, a, g.rows, g.logits_dtype);
-    if (st == LILY_OK && want_sums) {
+    if (st == LILY_OK && want_sums && a.shard_sums == 0u) {
         // The candidate launch has left the slice counters and the tickets (all
         // zero again) free: the sums use them for their pieces.
         uint32_t pieces = (2u * (uint32_t)h->sm_count + g.rows - 1u) / g.rows;

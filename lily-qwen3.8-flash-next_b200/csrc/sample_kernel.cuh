@@ -133,6 +133,7 @@ struct KArgs {
     uint32_t shard_k;              // candidates a sampled row keeps per shard (greedy rows keep 1)
     uint32_t id_offset;            // vocabulary id of this shard's logit 0
     ShardRecord *cand_out;         // [rows]
+    uint32_t shard_sums;           // stream_rows_kernel: sum_exp of the record too, in the same pass
     const ShardRecord *merge_in;   // [merge_shards, merge_stride >= rows]
     uint32_t merge_shards;
     uint64_t merge_stride;         // records between two shards

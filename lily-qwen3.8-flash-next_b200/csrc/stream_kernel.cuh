@@ -148,6 +148,63 @@ __device__ __forceinline__ void frag_mask_tail(Frag &f, uint32_t nvalid) {
     }
 }
 
+// A shard's record also carries sum exp(adjusted - largest adjusted) over the
+// shard (a reported statistic: the log-sum-exp of the whole vocabulary). In the
+// kernel of one block per row a thread keeps it for its own logits as it reads
+// them, in the base-2 domain and relative to its own running maximum:
+// sum_t = sum exp2(x * scale - ref_t). A fragment whose maximum beats the
+// reference rescales the sum first.
+struct RunningSum {
+    float ref, sum;
+};
+
+template <typename T>
+__device__ __forceinline__ void running_sum_add(RunningSum &rs, const Frag &cur, float m, float scale) {
+    const float y = m * scale;
+    if (y > rs.ref) {
+        rs.sum *= exp2f(rs.ref - y);
+        rs.ref = y;
+    }
+#pragma unroll
+    for (int e = 0; e < (int)Geo<T>::GROUP; ++e) {
+        rs.sum += exp2f(fmaf(frag_get<T>(cur, e), scale, -rs.ref));  // (a masked -inf adds 0)
+    }
+}
+
+// The block's total relative to `top2` (the record's largest adjusted logit, base
+// 2), in a fixed order: the lanes' tree, then the warps one after the other.
+__device__ __forceinline__ float running_sum_total(SmemFixed *sm, const RunningSum &rs, float top2) {
+    float v = rs.sum * exp2f(rs.ref - top2);
+    v = v == v ? v : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    }
+    float *part = reinterpret_cast<float *>(sm->thist);  // (the pool is no longer needed)
+    __syncthreads();
+    if ((threadIdx.x & 31u) == 0u) {
+        part[threadIdx.x >> 5] = v;
+    }
+    __syncthreads();
+    float total = 0.0f;
+    for (uint32_t w = 0; w < NT / 32u; ++w) {
+        total += part[w];
+    }
+    return total;
+}
+
+// The same sum by a second look at the row, for a row that went to the general
+// code (which leaves sum_exp at 0): every thread its strided share.
+template <typename T>
+__device__ __noinline__ float reread_sum(SmemFixed *sm, const T *row_ptr, uint32_t vocab, float scale, float top2) {
+    RunningSum rs{top2, 0.0f};
+    for (uint32_t i = threadIdx.x; i < vocab; i += NT) {
+        const float t = exp2f(fmaf(widen(row_ptr[i]), scale, -top2));
+        rs.sum += t == t ? t : 0.0f;
+    }
+    return running_sum_total(sm, rs, top2);
+}
+
 // End of the stream with at most one buffered candidate per thread (all raw):
 // adjusts them, drops what lies below the threshold key and leaves the best k
 // sorted by (key descending, id ascending) in key / id [0, result): every live
@@ -344,6 +401,9 @@ __global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_ke
     // (A shard keeps shard_k candidates of a sampled row, whatever its top_k: the
     // host made sure that top_k fits.)
     const uint32_t k = greedy ? 1u : a.cand_out ? a.shard_k : (P.top_k == 0u ? KCAP : min(P.top_k, KCAP));
+    // (A shard's record: the sum of exponentials in the same pass, if asked for.)
+    const bool sums = a.cand_out != nullptr && a.shard_sums != 0u;
+    const float sum_scale = 1.4426950408889634f / (greedy ? 1.0f : P.temperature);
     const bool monotone = P.repetition_penalty >= 1.0f && !(__float_as_uint(P.presence_penalty) >> 31) &&
                           !(__float_as_uint(P.frequency_penalty) >> 31);
     const bool need_counts = use_pen && P.frequency_penalty != 0.0f;
@@ -353,6 +413,8 @@ __global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_ke
     bool mine = !(k > STREAM_K_MAX || bias_len_row + ban_len_row != 0u || (use_pen && !monotone) ||
                   (need_counts && !table_mode) || a.extra_len != 0u);
     uint32_t n_raw = 0;
+    // (-3e38, not -inf: a first fragment of nothing but -inf must not give inf - inf)
+    RunningSum rs{-3.0e38f, 0.0f};
     if (mine) {
     const uint32_t vocab = a.vocab;
     const uint32_t nfull = vocab / ROUND;  // >= STREAM_MIN_ROUNDS: the host launches this kernel only then
@@ -469,6 +531,9 @@ __global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_ke
     auto track = [&](const Frag &cur, uint32_t rr) {
         const float m = frag_max<T>(cur);
         saw_nan |= m != m ? 1u : 0u;
+        if (sums) {
+            running_sum_add<T>(rs, cur, m, sum_scale);
+        }
         // The three best fragments by maximum (rounds best_r, r2, r3) and the
         // largest maximum among all the others (m4).
         if (best_r == NONE || m > best) {
@@ -664,6 +729,9 @@ __global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_ke
             if (read_round(rr, cur)) {
                 const float m = frag_max<T>(cur);
                 saw_nan |= m != m ? 1u : 0u;
+                if (sums) {
+                    running_sum_add<T>(rs, cur, m, sum_scale);
+                }
                 if (!(m <= c_fix)) {
                     lean_take<T>(sm, cur, rr * ROUND + tid * GROUP, valid_of(rr), c_fix);
                 }
@@ -688,6 +756,14 @@ __global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_ke
         cp_async_wait<0>();
         __syncthreads();
         sample_whole_row<T>(a, row);
+        if (sums) {
+            __syncthreads();
+            const float top = a.cand_out[row].max_adj;  // (written by this block, by thread 0 among others)
+            const float total = reread_sum<T>(sm, row_ptr, a.vocab, sum_scale, top * 1.4426950408889634f);
+            if (tid == 0) {
+                a.cand_out[row].sum_exp = total;
+            }
+        }
         return;
     }
 
@@ -697,6 +773,10 @@ __global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_ke
         stamps[PH_LOCAL_SELECT] = global_ns();
     }
     if (a.cand_out) {
+        float total = 0.0f;
+        if (sums && n != 0u) {
+            total = running_sum_total(sm, rs, float_of_key(sm->key[0]) * 1.4426950408889634f);
+        }
         if (n == 0u) {
             empty_record(sm->err ? sm->err : ROW_INTERNAL);
         } else if (tid < 32u) {
@@ -707,7 +787,7 @@ __global__ void __launch_bounds__(NT, StreamDepth<AHEAD>::BLOCKS) stream_rows_ke
             }
             if (tid == 0) {
                 rec->max_adj = float_of_key(sm->key[0]);
-                rec->sum_exp = 0.0f;
+                rec->sum_exp = total;
                 if (sm->err) {
                     atomicOr(a.status_word, 1u << (sm->err & 31u));
                 }
