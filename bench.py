@@ -476,7 +476,18 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
     # More than one rank: the records travel by the ranks' own stores into each
     # other's memory (lily_shard_publish / lily_merge_draw_peer); the all-gather
     # through NCCL is timed beside it.
-    exchange = sh.PeerExchange(dev.index, max_rows=tokens) if world > 1 else None
+    exchange, exchange_note = None, "one rank"
+    if world > 1:
+        exchange_note = "peer stores + flags (lily_merge_draw_peer)"
+        try:
+            exchange = sh.PeerExchange(dev.index, max_rows=tokens)
+        except Exception as e:  # no peer access between the GPUs of this box: every rank alike
+            exchange_note = f"NCCL all-gather (peer memory unavailable: {e})"
+        ok = torch.tensor([1 if exchange is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0 and exchange is not None:
+            exchange.close()
+            exchange, exchange_note = None, "NCCL all-gather (peer memory unavailable on another rank)"
 
     def step(i):
         sh.sharded_lmhead_draw(scratch, ws[i % copies], sc, h, params, out, first_id=rank * per,
@@ -549,7 +560,7 @@ def lmhead_sharded(torch, dist, lily, dev, stream, world, rank, steps):
     return {"workload": "hidden bf16 [64,4096] x int8 head [262144,4096], bf16 scales per 64 columns, "
                         f"{world} vocabulary shard(s); top-k 40, top-p 0.95, T 0.7",
             "n_gpus": world, "scaling": "strong", "us_per_step": step_ms * 1e3,
-            "exchange": "one rank" if world == 1 else "peer stores + flags (lily_shard_publish, lily_merge_draw_peer)",
+            "exchange": exchange_note,
             "us_per_step_nccl_allgather": None if nccl_ms is None else nccl_ms * 1e3,
             "peer_equals_nccl": same,
             "rows_per_s": tokens / (step_ms * 1e-3), "steps": steps,
