@@ -158,6 +158,7 @@ class PeerExchange:
         else:
             handles = [None] * self.world
             dist.all_gather_object(handles, bytes(handle), group=group)
+            failed = None
             for r in range(self.world):
                 if r == self.rank:
                     x.buffers[r] = own.value
@@ -166,10 +167,22 @@ class PeerExchange:
                 raw = (C.c_ubyte * lily.IPC_HANDLE_BYTES).from_buffer_copy(handles[r])
                 st = L.lily_peer_buffer_open(device, raw, C.byref(theirs))
                 if st != lily.OK:
-                    raise lily.LilyError(st, f"lily_peer_buffer_open failed for rank {r} (no peer access?)")
+                    failed = f"rank {self.rank} cannot open rank {r}'s buffer (no peer access?)"
+                    break
                 self._opened.append(theirs)
                 x.buffers[r] = theirs.value
-            dist.barrier(group=group)
+            # Every rank learns of a failure anywhere before any of them goes on
+            # (this also keeps a buffer alive until everybody has opened it).
+            verdicts = [None] * self.world
+            dist.all_gather_object(verdicts, failed, group=group)
+            if any(v is not None for v in verdicts):
+                for p in self._opened:
+                    L.lily_peer_buffer_close(device, p)
+                self._opened = []
+                dist.barrier(group=group)
+                L.lily_peer_buffer_destroy(device, own)
+                self._own = None
+                raise lily.LilyError(lily.ERR_CUDA, "; ".join(v for v in verdicts if v is not None))
         self.x = x
         self._group = group
 
