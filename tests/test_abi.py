@@ -36,6 +36,24 @@ def test_struct_layouts_match_the_header(lily):
     assert lily.lib().lily_abi_version() == 1
 
 
+def test_layouts_of_the_later_structs(lily):
+    """lily_lmhead_t with its code width, lily_peer_exchange_t, and the size of an
+    exchange buffer: a flag word per (rank, row) rounded up to 256 bytes, then two
+    slots of n_shards x max_rows records of 520 bytes."""
+    assert C.sizeof(lily.LmHead) == 48 and lily.LmHead.code_bits.offset == 40
+    assert C.sizeof(lily.PeerExchangeStruct) == 16 + 16 * 8
+    assert lily.PeerExchangeStruct.buffers.offset == 16
+    L = lily.lib()
+    for n, rows in ((1, 1), (2, 24), (8, 64), (16, 64)):
+        flags = (n * rows * 4 + 255) // 256 * 256
+        assert L.lily_peer_buffer_bytes(n, rows) == flags + 2 * n * rows * 520
+    # Host-side refusals need no GPU.
+    buf, handle = C.c_void_p(), (C.c_ubyte * 64)()
+    assert L.lily_peer_buffer_create(0, 0, 8, C.byref(buf), handle) == lily.ERR_ARG
+    assert L.lily_peer_buffer_create(0, 17, 8, C.byref(buf), handle) == lily.ERR_ARG
+    assert L.lily_peer_buffer_open(0, None, C.byref(buf)) == lily.ERR_ARG
+
+
 def test_uniform_for_matches_the_oracle(lily):
     for seed in (0, 7, 0xDEADBEEF, (1 << 64) - 1):
         for step in (0, 1, 77, 0x40000001, 0x80000002):
